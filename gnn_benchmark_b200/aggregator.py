@@ -1,0 +1,212 @@
+"""Aggregator: the autograd aggregation op of the GNN layers, on CUDA kernels.
+
+Same call as the reference (self_benchmark/a64fx/model/layers/aggregator.py:15-208):
+    out = Aggregator.apply(graph, local_nodes_feat, layer, num_bits, is_pre_delay, is_training)
+
+forward  out = A_local @ x  +  A_remote @ halo(x)          (aggregator.py:17-119)
+backward grad = A_local^T @ g + scatter(halo^T(A_remote^T @ g))   (aggregator.py:121-208)
+
+Per call, on the current (compute) stream unless noted:
+  1. fill the send side: pre-aggregation SpMM (pre/post path), row gather, or -- quantised
+     plain path -- gather fused into the quantise+pack kernel (no fp32 send buffer is written);
+  2. start the exchange (Communicator; runs on the NCCL stream);
+  3. local SpMM, overlapping the exchange;
+  4. make the compute stream wait for the exchange, unpack + dequantise if it was packed;
+  5. remote / post-aggregation SpMM accumulating onto the local result (forward), or
+     the transposed pre-aggregation SpMM / deterministic scatter-add (backward).
+The output tensors are written by the first SpMM (accumulate off), so no zero fill is needed.
+"""
+import torch
+import torch.distributed as dist
+
+from . import _lib
+from .communicator import Communicator
+from .quantizer import Quantizer_for_all_procs
+from .spmm_kernel import SPMM_backward, SPMM_forward
+from .time_recorder import TimeRecorder
+
+
+def _world_size() -> int:
+    return dist.get_world_size() if dist.is_available() and dist.is_initialized() else 1
+
+
+def gather_rows(x: torch.Tensor, idx_i32: torch.Tensor, out: torch.Tensor) -> None:
+    """out[i, :] = x[idx[i], :] (replaces torch.index_select(..., out=send_buf), aggregator.py:51)."""
+    _lib.require_cuda(x, idx_i32, out)
+    rows, F = idx_i32.numel(), x.size(1)
+    if rows == 0:
+        return
+    rc = _lib.lib().gnnagg_gather_rows_f32(x.data_ptr(), x.stride(0), idx_i32.data_ptr(), rows, F, out.data_ptr(),
+                                           out.stride(0), _lib.stream_ptr(x.device))
+    _lib.check(rc, "gather_rows_f32")
+
+
+def _packed(num_bits: int, graph) -> bool:
+    comm = Communicator.ctx
+    bits = comm.num_bits if comm is not None else num_bits
+    return bits in (2, 4, 8) and graph.comm_buf_for_quantization is not None
+
+
+def _resize(graph, feat_len: int, num_bits: int) -> None:
+    graph.comm_buf.resize_buffer(graph.comm_splits, feat_len, num_bits)
+    if num_bits != 32 and num_bits != 16 and graph.comm_buf_for_quantization is not None:
+        graph.comm_buf_for_quantization.resize_buffer(graph.comm_splits, feat_len, num_bits)
+
+
+def _rec():
+    return TimeRecorder.ctx
+
+
+class Aggregator(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, graph, local_nodes_feat, layer, num_bits: int, is_pre_delay: bool, is_training: bool):
+        ctx.graph = graph
+        ctx.num_bits = num_bits
+        ctx.is_pre_delay = is_pre_delay
+        ctx.layer = layer
+
+        world_size = _world_size()
+        rec = _rec()
+        t_total = rec.start() if rec else None
+        x = local_nodes_feat.contiguous()
+        feat_len = x.size(-1)
+        packed = world_size > 1 and is_training and _packed(num_bits, graph)
+
+        comm_handle = None
+        if world_size > 1:
+            t = rec.start() if rec else None
+            _resize(graph, feat_len, num_bits)
+            send_buf = graph.comm_buf.send_buf
+            q = graph.comm_buf_for_quantization
+            fused_pack = False
+            if is_pre_delay:  # pre-aggregation: partial sums for remote destinations, raw rows for post sources
+                SPMM_forward(graph.adj_t_pre_post_aggr_to, x, send_buf, accumulate=False)
+            elif packed:      # gather fused into quantise + pack
+                Quantizer_for_all_procs.ctx.quantize_fp32_to_intX(
+                    x, q.quantized_send_data_buf, q.quantized_send_params_buf_fp32, q.quantized_work_range_per_proc,
+                    params_bf16=q.quantized_send_params_buf_bf16, gather_idx=_send_idx(graph))
+                fused_pack = True
+            else:
+                gather_rows(x, _send_idx(graph), send_buf)
+            if rec:
+                rec.record_prepare_comm_time(t)
+            if fused_pack:
+                comm_handle = Communicator.ctx.comm_with_int2_quantization_for_all_procs(
+                    graph.comm_splits, graph.comm_buf, q, "forward", already_quantized=True)
+            else:
+                comm_handle = Communicator.ctx.comm(graph.comm_splits, graph.comm_buf, q, f"forward{layer}",
+                                                    is_training, "forward")
+
+        t = rec.start() if rec else None
+        out = torch.empty([graph.local_adj_t.sparse_size(0), feat_len], dtype=torch.float32, device=x.device)
+        SPMM_forward(graph.local_adj_t, x, out, accumulate=False)
+        if rec:
+            rec.record_local_aggregate_time(t)
+
+        if comm_handle is not None:
+            comm_handle.wait()
+
+        num_recv_nodes = sum(graph.comm_splits.recv_splits) if world_size > 1 else 0
+        if packed and num_recv_nodes != 0:
+            t = rec.start() if rec else None
+            q = graph.comm_buf_for_quantization
+            Quantizer_for_all_procs.ctx.dequantize_intX_to_fp32(
+                q.quantized_recv_data_buf, graph.comm_buf.recv_buf, q.quantized_recv_params_buf_fp32,
+                q.dequantized_work_range_per_proc, params_bf16=q.quantized_recv_params_buf_bf16)
+            if rec:
+                rec.record_dequantization_time(t)
+
+        if world_size > 1 and num_recv_nodes != 0:
+            t = rec.start() if rec else None
+            remote_nodes_feat = graph.comm_buf.recv_buf
+            if is_pre_delay:  # post-aggregation
+                SPMM_forward(graph.adj_t_pre_post_aggr_from, remote_nodes_feat, out)
+            else:
+                SPMM_forward(graph.remote_adj_t, remote_nodes_feat, out)
+            if rec:
+                rec.record_remote_aggregate_time(t)
+
+        if rec:
+            rec.record_total_convolution_time(t_total)
+            rec.next_layer()
+        return out
+
+    @staticmethod
+    def backward(ctx, local_out_grad):
+        graph = ctx.graph
+        num_bits = ctx.num_bits
+        is_pre_delay = ctx.is_pre_delay
+        layer = f"backward{ctx.layer}"
+
+        world_size = _world_size()
+        rec = _rec()
+        t_total = rec.start() if rec else None
+        g = local_out_grad.contiguous()
+        feat_len = g.size(-1)
+        packed = world_size > 1 and _packed(num_bits, graph)
+
+        comm_handle = None
+        if world_size > 1:
+            _resize(graph, feat_len, num_bits)
+            # the two buffers swap roles: recv_buf is sent, send_buf receives
+            remote_nodes_grad_buf = graph.comm_buf.recv_buf
+            t = rec.start() if rec else None
+            if remote_nodes_grad_buf.size(0) != 0:
+                if is_pre_delay:
+                    SPMM_backward(graph.adj_t_pre_post_aggr_from, g, remote_nodes_grad_buf, accumulate=False)
+                else:
+                    SPMM_backward(graph.remote_adj_t, g, remote_nodes_grad_buf, accumulate=False)
+            if rec:
+                rec.record_pre_aggregate_time(t)
+            comm_handle = Communicator.ctx.comm(graph.comm_splits, graph.comm_buf, graph.comm_buf_for_quantization,
+                                                layer, True, "backward")
+
+        t = rec.start() if rec else None
+        local_nodes_grad = torch.empty([graph.local_adj_t.sparse_size(-1), feat_len], dtype=torch.float32,
+                                       device=g.device)
+        SPMM_backward(graph.local_adj_t, g, local_nodes_grad, accumulate=False)
+        if rec:
+            rec.record_local_aggregate_time(t)
+
+        if comm_handle is not None:
+            comm_handle.wait()
+
+        num_recv_nodes = sum(graph.comm_splits.send_splits) if world_size > 1 else 0
+        if packed and num_recv_nodes != 0:
+            t = rec.start() if rec else None
+            q = graph.comm_buf_for_quantization
+            Quantizer_for_all_procs.ctx.dequantize_intX_to_fp32(
+                q.quantized_send_data_buf, graph.comm_buf.send_buf, q.quantized_send_params_buf_fp32,
+                q.quantized_work_range_per_proc, params_bf16=q.quantized_send_params_buf_bf16)
+            if rec:
+                rec.record_dequantization_time(t)
+
+        if world_size > 1 and num_recv_nodes != 0:
+            t = rec.start() if rec else None
+            local_nodes_grad_buf = graph.comm_buf.send_buf
+            if is_pre_delay:
+                SPMM_backward(graph.adj_t_pre_post_aggr_to, local_nodes_grad_buf, local_nodes_grad)
+            else:
+                # grad.index_add_(0, idx_nodes_send_to_others, buf) as an accumulating SpMM with the
+                # unit scatter matrix: same additions, fixed order, no atomics
+                SPMM_forward(_scatter_adj(graph), local_nodes_grad_buf, local_nodes_grad)
+            if rec:
+                rec.record_remote_aggregate_time(t)
+
+        if rec:
+            rec.record_total_convolution_time(t_total)
+            rec.next_layer()
+        return None, local_nodes_grad, None, None, None, None
+
+
+def _send_idx(graph) -> torch.Tensor:
+    if getattr(graph, "idx_nodes_send_to_others_i32", None) is None:
+        graph.idx_nodes_send_to_others_i32 = graph.idx_nodes_send_to_others.to(torch.int32)
+    return graph.idx_nodes_send_to_others_i32
+
+
+def _scatter_adj(graph):
+    if getattr(graph, "scatter_adj_t", None) is None:
+        from .data_manager.DataLoader import _scatter_matrix
+        graph.scatter_adj_t = _scatter_matrix(graph.idx_nodes_send_to_others, graph.local_adj_t.sparse_size(0))
+    return graph.scatter_adj_t

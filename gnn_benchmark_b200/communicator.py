@@ -1,0 +1,199 @@
+"""Communicator: the halo exchange, with the reference's class and method names
+(self_benchmark/a64fx/communicator.py:19-325).
+
+The reference runs MPI / oneCCL all-to-alls between CPU ranks.  Here every rank drives one GPU
+and the exchanges are `torch.distributed` all_to_all_single calls on the NCCL backend (grouped
+ncclSend/ncclRecv over NVLink): with async_op=True they run on the process group's own stream,
+ordered after the work already queued on the caller's stream, and `handle.wait()` makes the
+caller's stream (not the host) wait for them -- which is how the exchange overlaps the local
+SpMM launched in between.  The blocking barrier the reference puts before every exchange
+(communicator.py:98,292) is not needed for correctness and is off by default.
+
+With CPU tensors and the gloo backend the same code runs as host-side plumbing (used by the
+world_size-2 CPU tests); the quantised mode needs the CUDA codec and therefore CUDA tensors.
+"""
+import os
+
+import torch
+import torch.distributed as dist
+
+from .data_manager import CommBuffer, CommBufferForQuantization, CommSplits
+from .quantizer import Quantizer_for_all_procs
+from .time_recorder import TimeRecorder
+from . import _lib
+
+
+class _Handles(object):
+    """Several async works behind one .wait()."""
+
+    def __init__(self, works):
+        self.works = [w for w in works if w is not None]
+
+    def wait(self):
+        for w in self.works:
+            w.wait()
+
+
+class Communicator(object):
+    ctx = None
+
+    def __init__(self, num_bits=32, is_async=True, use_barrier=False) -> None:
+        self.num_bits = num_bits
+        self.is_async = is_async
+        self.use_barrier = use_barrier
+        self.world_size = -1
+        self.rank = -1
+        Communicator.ctx = self
+
+    def init_dist_group(self, backend=None):
+        """One process per GPU, launched by torchrun (RANK / WORLD_SIZE / LOCAL_RANK / MASTER_* in
+        the environment).  NCCL when CUDA is available, else gloo (communicator.py:28-53 picks
+        MPI or oneCCL instead)."""
+        if not dist.is_initialized():
+            if backend is None:
+                backend = "nccl" if torch.cuda.is_available() else "gloo"
+            if backend == "nccl":
+                local_rank = int(os.environ.get("LOCAL_RANK", 0))
+                torch.cuda.set_device(local_rank)
+                dist.init_process_group(backend="nccl", device_id=torch.device("cuda", local_rank))
+            else:
+                dist.init_process_group(backend=backend)
+        self.world_size = dist.get_world_size()
+        self.rank = dist.get_rank()
+        return (self.rank, self.world_size)
+
+    # ---------------------------------------------------------------------------------------
+    def comm(self, comm_splits, comm_buf, comm_buf_for_quantization, layer, is_training, direction):
+        """Dispatch on the bit width (communicator.py:55-83): fp32 when num_bits == 32 or outside
+        training, bf16 for 16, packed codes for 2 (and here 4 and 8).  Returns an object with
+        .wait() or None."""
+        comm_handle = None
+        if self.num_bits == 32 or is_training is False:
+            comm_handle = self.comm_with_fp32(comm_splits, comm_buf, direction)
+        elif self.num_bits == 16:
+            comm_handle = self.comm_with_fp16(comm_splits, comm_buf, direction)
+        elif self.num_bits in (2, 4, 8):
+            comm_handle = self.comm_with_int2_quantization_for_all_procs(
+                comm_splits, comm_buf, comm_buf_for_quantization, direction)
+        return comm_handle
+
+    def _barrier(self):
+        if self.use_barrier:
+            t = TimeRecorder.ctx.start() if TimeRecorder.ctx else None
+            dist.barrier()
+            if TimeRecorder.ctx:
+                TimeRecorder.ctx.record_barrier_time(t)
+
+    def comm_with_fp32(self, comm_splits: CommSplits, comm_buf: CommBuffer, direction: str):
+        """communicator.py:85-109."""
+        if direction == "forward":
+            recv_buf, send_buf = comm_buf.recv_buf, comm_buf.send_buf
+            recv_splits, send_splits = comm_splits.recv_splits, comm_splits.send_splits
+        else:
+            recv_buf, send_buf = comm_buf.send_buf, comm_buf.recv_buf
+            recv_splits, send_splits = comm_splits.send_splits, comm_splits.recv_splits
+        self._barrier()
+        t = TimeRecorder.ctx.start() if TimeRecorder.ctx else None
+        handle = dist.all_to_all_single(recv_buf, send_buf, recv_splits, send_splits, async_op=self.is_async)
+        if TimeRecorder.ctx:
+            TimeRecorder.ctx.record_communication_time(t)
+        return handle
+
+    def comm_with_fp16(self, comm_splits: CommSplits, comm_buf: CommBuffer, direction: str):
+        """bf16 on the wire (communicator.py:111-143).  The reference widens the received buffer
+        before waiting for the exchange (:137, a race when async); here the widening is queued
+        behind the exchange and the returned handle covers both."""
+        if direction == "forward":
+            recv_buf, send_buf = comm_buf.recv_buf, comm_buf.send_buf
+            recv_buf_fp16, send_buf_fp16 = comm_buf.recv_buf_fp16, comm_buf.send_buf_fp16
+            recv_splits, send_splits = comm_splits.recv_splits, comm_splits.send_splits
+        else:
+            recv_buf, send_buf = comm_buf.send_buf, comm_buf.recv_buf
+            recv_buf_fp16, send_buf_fp16 = comm_buf.send_buf_fp16, comm_buf.recv_buf_fp16
+            recv_splits, send_splits = comm_splits.send_splits, comm_splits.recv_splits
+        rec = TimeRecorder.ctx
+        t = rec.start() if rec else None
+        _cast(send_buf, send_buf_fp16)
+        if rec:
+            rec.record_quantization_time(t)
+        t = rec.start() if rec else None
+        handle = dist.all_to_all_single(recv_buf_fp16, send_buf_fp16, recv_splits, send_splits,
+                                        async_op=self.is_async)
+        if rec:
+            rec.record_communication_time(t)
+        return _CastAfter(handle, recv_buf_fp16, recv_buf)
+
+    def comm_with_int2_quantization_for_all_procs(self, comm_splits: CommSplits, comm_buf: CommBuffer,
+                                                  comm_buf_for_quantization: CommBufferForQuantization,
+                                                  direction: str, already_quantized: bool = False):
+        """Quantise + pack the send buffer, exchange the bf16 parameters, then the packed codes
+        (communicator.py:231-325).  The fp32 -> bf16 cast of the parameters (:297) is done by the
+        pack kernel; the bf16 -> fp32 widening (:303) by the unpack kernel on the receive side.
+        `already_quantized`: the caller filled the code / parameter buffers itself (fused
+        gather + pack)."""
+        q = comm_buf_for_quantization
+        if direction == "forward":
+            recv_splits, send_splits = comm_splits.recv_splits, comm_splits.send_splits
+            recv_splits_int2, send_splits_int2 = comm_splits.recv_splits_int2, comm_splits.send_splits_int2
+            send_buf = comm_buf.send_buf
+            quantized_recv_data_buf, quantized_send_data_buf = q.quantized_recv_data_buf, q.quantized_send_data_buf
+            recv_params_bf16, send_params_bf16 = q.quantized_recv_params_buf_bf16, q.quantized_send_params_buf_bf16
+            send_params_fp32 = q.quantized_send_params_buf_fp32
+            quantized_work_range_per_proc = q.quantized_work_range_per_proc
+        else:
+            recv_splits, send_splits = comm_splits.send_splits, comm_splits.recv_splits
+            recv_splits_int2, send_splits_int2 = comm_splits.send_splits_int2, comm_splits.recv_splits_int2
+            send_buf = comm_buf.recv_buf
+            quantized_recv_data_buf, quantized_send_data_buf = q.quantized_send_data_buf, q.quantized_recv_data_buf
+            recv_params_bf16, send_params_bf16 = q.quantized_send_params_buf_bf16, q.quantized_recv_params_buf_bf16
+            send_params_fp32 = q.quantized_recv_params_buf_fp32
+            quantized_work_range_per_proc = q.dequantized_work_range_per_proc
+
+        rec = TimeRecorder.ctx
+        if not already_quantized:
+            t = rec.start() if rec else None
+            Quantizer_for_all_procs.ctx.quantize_fp32_to_intX(
+                send_buf, quantized_send_data_buf, send_params_fp32, quantized_work_range_per_proc,
+                params_bf16=send_params_bf16)
+            if rec:
+                rec.record_quantization_time(t)
+        self._barrier()
+        t = rec.start() if rec else None
+        h_params = dist.all_to_all_single(recv_params_bf16, send_params_bf16, recv_splits, send_splits,
+                                          async_op=self.is_async)
+        h_data = dist.all_to_all_single(quantized_recv_data_buf, quantized_send_data_buf, recv_splits_int2,
+                                        send_splits_int2, async_op=self.is_async)
+        if rec:
+            rec.record_communication_time(t)
+        return _Handles([h_params, h_data])
+
+
+def _cast(src: torch.Tensor, dst: torch.Tensor) -> None:
+    """fp32 <-> bf16 buffer copy (communicator.py:128,137) through the C ABI on CUDA tensors;
+    torch's copy_ for the CPU plumbing tests."""
+    if not src.is_cuda:
+        dst.copy_(src)
+        return
+    n = src.numel()
+    if n == 0:
+        return
+    lib = _lib.lib()
+    if src.dtype == torch.float32:
+        rc = lib.gnnagg_cast_f32_to_bf16(src.data_ptr(), dst.data_ptr(), n, _lib.stream_ptr(src.device))
+    else:
+        rc = lib.gnnagg_cast_bf16_to_f32(src.data_ptr(), dst.data_ptr(), n, _lib.stream_ptr(src.device))
+    _lib.check(rc, "cast")
+
+
+class _CastAfter(object):
+    def __init__(self, work, src, dst):
+        self.work, self.src, self.dst = work, src, dst
+
+    def wait(self):
+        if self.work is not None:
+            self.work.wait()
+        rec = TimeRecorder.ctx
+        t = rec.start() if rec else None
+        _cast(self.src, self.dst)
+        if rec:
+            rec.record_dequantization_time(t)

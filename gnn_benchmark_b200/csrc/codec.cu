@@ -1,0 +1,481 @@
+// K3: per-row min/max quantise + pack, unpack + dequantise (halo exchange codec), sm_100a.
+//
+// Row-packed layout (live int2 path and the generic 2/4/8-bit variant): EPB = 8/bits
+// consecutive rows of one peer segment share one byte per column, first row in the high
+// bits; a segment's packed rows start at base_p = sum_{q<p} ceil(n_q/EPB)
+// (model/ops/src/quantization_arm.cpp:21-78,158-166).  One warp owns one packed row:
+// it reads its <= EPB input rows once with 128-bit loads, keeps them in registers, finds
+// min/max with shuffles, encodes from registers and writes F bytes + the parameters.
+// HBM traffic per input row: 4F read, F*bits/8 + 8 (+4 for the bf16 copy) written.
+//
+// Arithmetic is written with explicit IEEE intrinsics so that codes are bit-identical to
+// the reference: subtract, true divide, round-half-even, (x - zp) / scale with
+// scale = (max - min) / (2^bits - 1) and scale == 0 -> 1; decode is one fma.
+#include <cuda_bf16.h>
+
+#include "common.cuh"
+
+namespace gnnagg {
+
+constexpr int kCodecWarps = 4;
+constexpr int kMaxSeg = 1024;  // peer segments per call
+
+// Packed-row prefix of the segments into shared memory: pbase[p] = sum_{q<p} ceil(n_q/epb).
+__device__ __forceinline__ void build_packed_prefix(const int32_t *__restrict__ seg, int P, int epb, int *pbase) {
+    if (threadIdx.x < 32) {
+        const int lane = threadIdx.x;
+        int running = 0;
+        for (int p0 = 0; p0 < P; p0 += 32) {
+            const int p = p0 + lane;
+            int cnt = 0;
+            if (p < P) cnt = (seg[p + 1] - seg[p] + epb - 1) / epb;
+            int incl = cnt;
+#pragma unroll
+            for (int off = 1; off < 32; off <<= 1) {
+                const int t = __shfl_up_sync(kFullMask, incl, off);
+                if (lane >= off) incl += t;
+            }
+            if (p < P) pbase[p] = running + incl - cnt;
+            running += __shfl_sync(kFullMask, incl, 31);
+        }
+        if (lane == 0) pbase[P] = running;
+    }
+    __syncthreads();
+}
+
+// Packed row R -> segment p with pbase[p] <= R < pbase[p+1] (empty segments skipped).
+__device__ __forceinline__ int find_segment(const int *pbase, int P, int R) {
+    int lo = 0, hi = P - 1;
+    while (lo < hi) {
+        const int mid = (lo + hi + 1) >> 1;
+        if (pbase[mid] <= R)
+            lo = mid;
+        else
+            hi = mid - 1;
+    }
+    // several empty segments may share pbase[lo]; the owner is the last one with pbase <= R,
+    // which the search above returns because it moves right on equality.
+    return lo;
+}
+
+__device__ __forceinline__ float warp_min(float v) {
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) v = fminf(v, __shfl_xor_sync(kFullMask, v, off));
+    return v;
+}
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) v = fmaxf(v, __shfl_xor_sync(kFullMask, v, off));
+    return v;
+}
+__device__ __forceinline__ int warp_min_int(int v) {
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) v = min(v, __shfl_xor_sync(kFullMask, v, off));
+    return v;
+}
+
+// The reference scans a row from column 0 and replaces min/max only on a strict compare
+// (quantization_arm.cpp:93-104): a NaN never replaces, a NaN in column 0 sticks, and of
+// several zeros of either sign the first one met is kept.  fminf/fmaxf already skip
+// NaNs; the two corrections below restore the rest.  `first_zero_key` is
+// (column << 1 | sign bit) of this lane's first element equal to zero, INT_MAX if none.
+__device__ __forceinline__ float fix_extreme(float m, float x0, int first_zero_key) {
+    if (x0 != x0) return x0;
+    if (m == 0.0f) {
+        const int key = warp_min_int(first_zero_key);
+        return (key & 1) ? -0.0f : 0.0f;
+    }
+    return m;
+}
+
+__device__ __forceinline__ uint32_t encode(float x, float zp, float scale, bool signed_cvt) {
+    const float q = __fdiv_rn(__fsub_rn(x, zp), scale);
+    // own parameters: unsigned saturating convert (SVE FCVTZU after FRINTN);
+    // caller's parameters: signed convert (x86 cvt_roundps_epi32), negative codes keep
+    // their two's-complement bits as in the reference.
+    return signed_cvt ? (uint32_t)__float2int_rn(q) : __float2uint_rn(q);
+}
+
+__device__ __forceinline__ uint32_t bf16_bits(float v) {
+    return (uint32_t)__bfloat16_as_ushort(__float2bfloat16_rn(v));
+}
+
+// ---- fast path: F % 4 == 0, F <= 128*NV, 16-byte aligned rows ------------------------
+template <int BITS, int NV>
+__global__ void __launch_bounds__(kCodecWarps * 32)
+    quant_pack_vec_kernel(const float *__restrict__ X, int64_t ldx, const int32_t *__restrict__ idx, int F,
+                          const int32_t *__restrict__ seg, int P, int params_given, float *__restrict__ params,
+                          uint32_t *__restrict__ params_bf16, uint8_t *__restrict__ codes) {
+    constexpr int EPB = 8 / BITS;
+    constexpr float LEVELS = (float)((1 << BITS) - 1);
+    __shared__ int pbase[kMaxSeg + 1];
+    build_packed_prefix(seg, P, EPB, pbase);
+    const int lane = threadIdx.x & 31;
+    const int64_t R = (int64_t)blockIdx.x * kCodecWarps + (threadIdx.x >> 5);
+    if (R >= pbase[P]) return;
+    const int p = find_segment(pbase, P, (int)R);
+    const int i0 = seg[p] + ((int)R - pbase[p]) * EPB;
+    const int cnt = min(EPB, seg[p + 1] - i0);
+    const int FV = F >> 2;
+
+    float4 xv[EPB][NV];
+    float zp[EPB], sc[EPB];
+#pragma unroll
+    for (int t = 0; t < EPB; ++t) {
+        zp[t] = 0.f;
+        sc[t] = 1.f;
+        if (t < cnt) {
+            const int64_t src = idx ? (int64_t)idx[i0 + t] : (int64_t)(i0 + t);
+            const float *xp = X + src * ldx;
+            float mn = __int_as_float(0x7f800000), mx = __int_as_float(0xff800000);  // +inf, -inf
+            int zkey = INT_MAX;
+#pragma unroll
+            for (int k = 0; k < NV; ++k) {
+                const int vi = lane + 32 * k;
+                if (vi < FV) {
+                    const float4 v = __ldcs(reinterpret_cast<const float4 *>(xp) + vi);
+                    xv[t][k] = v;
+                    const float e[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) {
+                        mn = fminf(mn, e[i]), mx = fmaxf(mx, e[i]);
+                        if (e[i] == 0.0f && zkey == INT_MAX)
+                            zkey = ((vi * 4 + i) << 1) | (int)(__float_as_uint(e[i]) >> 31);
+                    }
+                } else {
+                    xv[t][k] = make_float4(0.f, 0.f, 0.f, 0.f);
+                }
+            }
+            if (!params_given) {
+                // lanes past the row's end hold +inf/-inf and drop out of the reduction;
+                // a row that starts with a NaN is handled by fix_extreme
+                mn = warp_min(mn);
+                mx = warp_max(mx);
+                const float x0 = __shfl_sync(kFullMask, xv[t][0].x, 0);
+                mn = fix_extreme(mn, x0, zkey);
+                mx = fix_extreme(mx, x0, zkey);
+                float s = __fdiv_rn(__fsub_rn(mx, mn), LEVELS);
+                if (s == 0.0f) s = 1.0f;
+                zp[t] = mn;
+                sc[t] = s;
+                if (lane == 0) {
+                    params[(int64_t)(i0 + t) * 2] = mn;
+                    params[(int64_t)(i0 + t) * 2 + 1] = s;
+                    if (params_bf16) params_bf16[i0 + t] = bf16_bits(mn) | (bf16_bits(s) << 16);
+                }
+            } else {
+                zp[t] = params[(int64_t)(i0 + t) * 2];
+                sc[t] = params[(int64_t)(i0 + t) * 2 + 1];
+                if (lane == 0 && params_bf16) params_bf16[i0 + t] = bf16_bits(zp[t]) | (bf16_bits(sc[t]) << 16);
+            }
+        }
+    }
+
+    uint32_t *out = reinterpret_cast<uint32_t *>(codes + R * (int64_t)F);
+#pragma unroll
+    for (int k = 0; k < NV; ++k) {
+        const int vi = lane + 32 * k;
+        if (vi < FV) {
+            uint32_t b0 = 0, b1 = 0, b2 = 0, b3 = 0;
+#pragma unroll
+            for (int t = 0; t < EPB; ++t) {
+                if (t < cnt) {
+                    const int sh = (EPB - 1 - t) * BITS;
+                    b0 |= encode(xv[t][k].x, zp[t], sc[t], params_given) << sh;
+                    b1 |= encode(xv[t][k].y, zp[t], sc[t], params_given) << sh;
+                    b2 |= encode(xv[t][k].z, zp[t], sc[t], params_given) << sh;
+                    b3 |= encode(xv[t][k].w, zp[t], sc[t], params_given) << sh;
+                }
+            }
+            __stcs(out + vi, (b0 & 255u) | ((b1 & 255u) << 8) | ((b2 & 255u) << 16) | ((b3 & 255u) << 24));
+        }
+    }
+}
+
+// ---- generic path: any F, any alignment; rows are read twice (second pass hits L1/L2) ----
+__global__ void __launch_bounds__(kCodecWarps * 32)
+    quant_pack_generic_kernel(const float *__restrict__ X, int64_t ldx, const int32_t *__restrict__ idx, int F,
+                              const int32_t *__restrict__ seg, int P, int bits, int params_given,
+                              float *__restrict__ params, __nv_bfloat16 *__restrict__ params_bf16,
+                              uint8_t *__restrict__ codes) {
+    const int epb = 8 / bits;
+    const float levels = (float)((1 << bits) - 1);
+    __shared__ int pbase[kMaxSeg + 1];
+    build_packed_prefix(seg, P, epb, pbase);
+    const int lane = threadIdx.x & 31;
+    const int64_t R = (int64_t)blockIdx.x * kCodecWarps + (threadIdx.x >> 5);
+    if (R >= pbase[P]) return;
+    const int p = find_segment(pbase, P, (int)R);
+    const int i0 = seg[p] + ((int)R - pbase[p]) * epb;
+    const int cnt = min(epb, seg[p + 1] - i0);
+
+    float zp[8], sc[8];
+    const float *xp[8];
+#pragma unroll
+    for (int t = 0; t < 8; ++t) {
+        zp[t] = 0.f, sc[t] = 1.f, xp[t] = X;
+        if (t < cnt) {
+            const int64_t src = idx ? (int64_t)idx[i0 + t] : (int64_t)(i0 + t);
+            xp[t] = X + src * ldx;
+            if (!params_given) {
+                float mn = __int_as_float(0x7f800000), mx = __int_as_float(0xff800000);
+                int zkey = INT_MAX;
+                for (int k = lane; k < F; k += 32) {
+                    const float e = xp[t][k];
+                    mn = fminf(mn, e), mx = fmaxf(mx, e);
+                    if (e == 0.0f && zkey == INT_MAX) zkey = (k << 1) | (int)(__float_as_uint(e) >> 31);
+                }
+                mn = warp_min(mn), mx = warp_max(mx);
+                const float x0 = xp[t][0];
+                mn = fix_extreme(mn, x0, zkey);
+                mx = fix_extreme(mx, x0, zkey);
+                float s = __fdiv_rn(__fsub_rn(mx, mn), levels);
+                if (s == 0.0f) s = 1.0f;
+                zp[t] = mn, sc[t] = s;
+                if (lane == 0) {
+                    params[(int64_t)(i0 + t) * 2] = mn;
+                    params[(int64_t)(i0 + t) * 2 + 1] = s;
+                }
+            } else {
+                zp[t] = params[(int64_t)(i0 + t) * 2];
+                sc[t] = params[(int64_t)(i0 + t) * 2 + 1];
+            }
+            if (lane == 0 && params_bf16) {
+                params_bf16[(int64_t)(i0 + t) * 2] = __float2bfloat16_rn(zp[t]);
+                params_bf16[(int64_t)(i0 + t) * 2 + 1] = __float2bfloat16_rn(sc[t]);
+            }
+        }
+    }
+    uint8_t *out = codes + R * (int64_t)F;
+    for (int k = lane; k < F; k += 32) {
+        uint32_t b = 0;
+#pragma unroll
+        for (int t = 0; t < 8; ++t)
+            if (t < cnt) b |= encode(xp[t][k], zp[t], sc[t], params_given) << ((epb - 1 - t) * bits);
+        out[k] = (uint8_t)b;
+    }
+}
+
+// ---- unpack + dequantise -----------------------------------------------------------------
+template <int BITS, bool VEC>
+__global__ void __launch_bounds__(kCodecWarps * 32)
+    unpack_dequant_kernel(const uint8_t *__restrict__ codes, int F, const int32_t *__restrict__ seg, int P,
+                          float *__restrict__ params, const __nv_bfloat16 *__restrict__ params_bf16,
+                          float *__restrict__ OUT, int64_t ldo) {
+    constexpr int EPB = 8 / BITS;
+    constexpr uint32_t MASK = (1u << BITS) - 1u;
+    __shared__ int pbase[kMaxSeg + 1];
+    build_packed_prefix(seg, P, EPB, pbase);
+    const int lane = threadIdx.x & 31;
+    const int64_t R = (int64_t)blockIdx.x * kCodecWarps + (threadIdx.x >> 5);
+    if (R >= pbase[P]) return;
+    const int p = find_segment(pbase, P, (int)R);
+    const int i0 = seg[p] + ((int)R - pbase[p]) * EPB;
+    const int cnt = min(EPB, seg[p + 1] - i0);
+
+    float zp[EPB], sc[EPB];
+#pragma unroll
+    for (int t = 0; t < EPB; ++t) {
+        zp[t] = 0.f, sc[t] = 0.f;
+        if (t < cnt) {
+            if (params_bf16) {
+                zp[t] = __bfloat162float(params_bf16[(int64_t)(i0 + t) * 2]);
+                sc[t] = __bfloat162float(params_bf16[(int64_t)(i0 + t) * 2 + 1]);
+                if (params && lane == 0) {
+                    params[(int64_t)(i0 + t) * 2] = zp[t];
+                    params[(int64_t)(i0 + t) * 2 + 1] = sc[t];
+                }
+            } else {
+                zp[t] = params[(int64_t)(i0 + t) * 2];
+                sc[t] = params[(int64_t)(i0 + t) * 2 + 1];
+            }
+        }
+    }
+    const uint8_t *in = codes + R * (int64_t)F;
+    if (VEC) {
+        const uint32_t *in4 = reinterpret_cast<const uint32_t *>(in);
+        for (int vi = lane; vi < (F >> 2); vi += 32) {
+            const uint32_t w = __ldcs(in4 + vi);
+#pragma unroll
+            for (int t = 0; t < EPB; ++t) {
+                if (t < cnt) {
+                    const int sh = (EPB - 1 - t) * BITS;
+                    float4 o;
+                    o.x = fmaf((float)((w >> sh) & MASK), sc[t], zp[t]);
+                    o.y = fmaf((float)((w >> (8 + sh)) & MASK), sc[t], zp[t]);
+                    o.z = fmaf((float)((w >> (16 + sh)) & MASK), sc[t], zp[t]);
+                    o.w = fmaf((float)((w >> (24 + sh)) & MASK), sc[t], zp[t]);
+                    *(reinterpret_cast<float4 *>(OUT + (int64_t)(i0 + t) * ldo) + vi) = o;
+                }
+            }
+        }
+    } else {
+        for (int k = lane; k < F; k += 32) {
+            const uint32_t w = in[k];
+#pragma unroll
+            for (int t = 0; t < EPB; ++t)
+                if (t < cnt)
+                    OUT[(int64_t)(i0 + t) * ldo + k] = fmaf((float)((w >> ((EPB - 1 - t) * BITS)) & MASK), sc[t], zp[t]);
+        }
+    }
+}
+
+// ---- mixed-bit column-packed codec: one warp per row ------------------------------------
+__global__ void __launch_bounds__(kCodecWarps * 32)
+    quant_v1_kernel(const float *__restrict__ X, int64_t ldx, int64_t rows, int F, const int64_t *__restrict__ range,
+                    float *__restrict__ params, uint8_t *__restrict__ codes) {
+    const int lane = threadIdx.x & 31;
+    const int64_t i = (int64_t)blockIdx.x * kCodecWarps + (threadIdx.x >> 5);
+    if (i >= rows) return;
+    const float *xp = X + i * ldx;
+    const int bits = (int)params[i * 3];
+    if (bits != 8 && bits != 4 && bits != 2) return;  // the reference prints an error and skips the row
+    float mn = __int_as_float(0x7f800000), mx = __int_as_float(0xff800000);
+    int zkey = INT_MAX;
+    for (int k = lane; k < F; k += 32) {
+        const float e = xp[k];
+        mn = fminf(mn, e), mx = fmaxf(mx, e);
+        if (e == 0.0f && zkey == INT_MAX) zkey = (k << 1) | (int)(__float_as_uint(e) >> 31);
+    }
+    mn = warp_min(mn), mx = warp_max(mx);
+    const float x0 = xp[0];
+    mn = fix_extreme(mn, x0, zkey);
+    mx = fix_extreme(mx, x0, zkey);
+    float s = __fdiv_rn(__fsub_rn(mx, mn), (float)((1 << bits) - 1));
+    if (s == 0.0f) s = 1.0f;
+    if (lane == 0) {
+        params[i * 3 + 1] = mn;
+        params[i * 3 + 2] = s;
+    }
+    const int epb = 8 / bits;
+    uint8_t *out = codes + range[i];
+    const int nbytes = (F + epb - 1) / epb;
+    for (int j = lane; j < nbytes; j += 32) {
+        uint32_t b = 0;
+        for (int k = 0; k < epb && j * epb + k < F; ++k)
+            b |= ((uint32_t)__float2int_rn(__fdiv_rn(__fsub_rn(xp[j * epb + k], mn), s))) << ((epb - 1 - k) * bits);
+        out[j] = (uint8_t)b;
+    }
+}
+
+__global__ void __launch_bounds__(kCodecWarps * 32)
+    dequant_v1_kernel(const uint8_t *__restrict__ codes, int64_t rows, int F, const int64_t *__restrict__ range,
+                      const float *__restrict__ params, float *__restrict__ OUT, int64_t ldo) {
+    const int lane = threadIdx.x & 31;
+    const int64_t i = (int64_t)blockIdx.x * kCodecWarps + (threadIdx.x >> 5);
+    if (i >= rows) return;
+    const int bits = (int)params[i * 3];
+    if (bits != 8 && bits != 4 && bits != 2) return;
+    const float zp = params[i * 3 + 1], s = params[i * 3 + 2];
+    const int epb = 8 / bits;
+    const uint32_t mask = (1u << bits) - 1u;
+    const uint8_t *in = codes + range[i];
+    const int64_t plen = range[i + 1] - range[i];
+    for (int k = lane; k < F; k += 32) {
+        const int j = k / epb;
+        if (j < plen) {
+            const uint32_t b = in[j];
+            // val*scale + zp: one fma under the reference's build flags (GCC contracts it)
+            OUT[i * ldo + k] = fmaf((float)((b >> ((epb - 1 - (k % epb)) * bits)) & mask), s, zp);
+        }
+    }
+}
+
+}  // namespace gnnagg
+
+using namespace gnnagg;
+
+static int check_seg_args(const char *who, const int32_t *seg, int32_t P, int64_t rows, int32_t bits, int32_t F) {
+    if (seg == nullptr || P < 1 || rows < 0 || F < 0) return fail(GNNAGG_ERR_ARG, "%s: bad seg / P / rows / F", who);
+    if (bits != 2 && bits != 4 && bits != 8) return fail(GNNAGG_ERR_ARG, "%s: bits must be 2, 4 or 8", who);
+    if (P > kMaxSeg) return fail(GNNAGG_ERR_UNSUPPORTED, "%s: more than %d segments", who, kMaxSeg);
+    if (rows > INT32_MAX) return fail(GNNAGG_ERR_UNSUPPORTED, "%s: rows must fit int32", who);
+    return GNNAGG_OK;
+}
+
+// Upper bound of the number of packed rows: the exact count lives on the device (seg), the
+// launch only needs a grid that covers it.
+static int64_t packed_rows_bound(int64_t rows, int32_t P, int epb) { return div_up(rows, epb) + P; }
+
+extern "C" int gnnagg_quant_pack_rows(const float *X, int64_t ldx, const int32_t *idx, int32_t F, const int32_t *seg,
+                                      int32_t P, int64_t rows, int32_t bits, int32_t params_given, float *params,
+                                      void *params_bf16, uint8_t *codes, void *stream) {
+    int rc = check_seg_args("quant_pack_rows", seg, P, rows, bits, F);
+    if (rc != GNNAGG_OK) return rc;
+    if (rows == 0 || F == 0) return GNNAGG_OK;
+    if (X == nullptr || params == nullptr || codes == nullptr || ldx < F)
+        return fail(GNNAGG_ERR_ARG, "quant_pack_rows: null pointer or ldx < F");
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    const int epb = 8 / bits;
+    const unsigned blocks = (unsigned)div_up(packed_rows_bound(rows, P, epb), kCodecWarps);
+    const bool vec = (F % 4 == 0) && (ldx % 4 == 0) && aligned16(X) && F <= 512 &&
+                     (reinterpret_cast<uintptr_t>(codes) % 4 == 0) &&
+                     (params_bf16 == nullptr || reinterpret_cast<uintptr_t>(params_bf16) % 4 == 0);
+    if (vec) {
+        uint32_t *pb = static_cast<uint32_t *>(params_bf16);
+#define GNNAGG_QP(B, NV)                                                                                      \
+    quant_pack_vec_kernel<B, NV><<<blocks, kCodecWarps * 32, 0, st>>>(X, ldx, idx, F, seg, P, params_given, params, \
+                                                                       pb, codes)
+        const int nv = (F + 127) / 128;
+        if (bits == 2) {
+            if (nv == 1) GNNAGG_QP(2, 1); else if (nv == 2) GNNAGG_QP(2, 2); else GNNAGG_QP(2, 4);
+        } else if (bits == 4) {
+            if (nv == 1) GNNAGG_QP(4, 1); else if (nv == 2) GNNAGG_QP(4, 2); else GNNAGG_QP(4, 4);
+        } else {
+            if (nv == 1) GNNAGG_QP(8, 1); else if (nv == 2) GNNAGG_QP(8, 2); else GNNAGG_QP(8, 4);
+        }
+#undef GNNAGG_QP
+        return check_launch("quant_pack_vec_kernel");
+    }
+    quant_pack_generic_kernel<<<blocks, kCodecWarps * 32, 0, st>>>(X, ldx, idx, F, seg, P, bits, params_given, params,
+                                                                  static_cast<__nv_bfloat16 *>(params_bf16), codes);
+    return check_launch("quant_pack_generic_kernel");
+}
+
+extern "C" int gnnagg_unpack_dequant_rows(const uint8_t *codes, int32_t F, const int32_t *seg, int32_t P, int64_t rows,
+                                          int32_t bits, float *params, const void *params_bf16, float *OUT,
+                                          int64_t ldo, void *stream) {
+    int rc = check_seg_args("unpack_dequant_rows", seg, P, rows, bits, F);
+    if (rc != GNNAGG_OK) return rc;
+    if (rows == 0 || F == 0) return GNNAGG_OK;
+    if (codes == nullptr || OUT == nullptr || (params == nullptr && params_bf16 == nullptr) || ldo < F)
+        return fail(GNNAGG_ERR_ARG, "unpack_dequant_rows: null pointer or ldo < F");
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    const int epb = 8 / bits;
+    const unsigned blocks = (unsigned)div_up(packed_rows_bound(rows, P, epb), kCodecWarps);
+    const __nv_bfloat16 *pb = static_cast<const __nv_bfloat16 *>(params_bf16);
+    const bool vec = (F % 4 == 0) && (ldo % 4 == 0) && aligned16(OUT) && (reinterpret_cast<uintptr_t>(codes) % 4 == 0);
+#define GNNAGG_UD(B, V) \
+    unpack_dequant_kernel<B, V><<<blocks, kCodecWarps * 32, 0, st>>>(codes, F, seg, P, params, pb, OUT, ldo)
+    if (bits == 2) {
+        if (vec) GNNAGG_UD(2, true); else GNNAGG_UD(2, false);
+    } else if (bits == 4) {
+        if (vec) GNNAGG_UD(4, true); else GNNAGG_UD(4, false);
+    } else {
+        if (vec) GNNAGG_UD(8, true); else GNNAGG_UD(8, false);
+    }
+#undef GNNAGG_UD
+    return check_launch("unpack_dequant_kernel");
+}
+
+extern "C" int gnnagg_quant_v1_rows(const float *X, int64_t ldx, int64_t rows, int32_t F, const int64_t *range,
+                                    float *params, uint8_t *codes, void *stream) {
+    if (rows < 0 || F < 0) return fail(GNNAGG_ERR_ARG, "quant_v1_rows: negative size");
+    if (rows == 0 || F == 0) return GNNAGG_OK;
+    if (X == nullptr || range == nullptr || params == nullptr || codes == nullptr || ldx < F)
+        return fail(GNNAGG_ERR_ARG, "quant_v1_rows: null pointer or ldx < F");
+    quant_v1_kernel<<<(unsigned)div_up(rows, kCodecWarps), kCodecWarps * 32, 0, static_cast<cudaStream_t>(stream)>>>(
+        X, ldx, rows, F, range, params, codes);
+    return check_launch("quant_v1_kernel");
+}
+
+extern "C" int gnnagg_dequant_v1_rows(const uint8_t *codes, int64_t rows, int32_t F, const int64_t *range,
+                                      const float *params, float *OUT, int64_t ldo, void *stream) {
+    if (rows < 0 || F < 0) return fail(GNNAGG_ERR_ARG, "dequant_v1_rows: negative size");
+    if (rows == 0 || F == 0) return GNNAGG_OK;
+    if (codes == nullptr || range == nullptr || params == nullptr || OUT == nullptr || ldo < F)
+        return fail(GNNAGG_ERR_ARG, "dequant_v1_rows: null pointer or ldo < F");
+    dequant_v1_kernel<<<(unsigned)div_up(rows, kCodecWarps), kCodecWarps * 32, 0, static_cast<cudaStream_t>(stream)>>>(
+        codes, rows, F, range, params, OUT, ldo);
+    return check_launch("dequant_v1_kernel");
+}

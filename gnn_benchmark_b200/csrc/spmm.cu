@@ -1,0 +1,516 @@
+// K1: merge-path CSR SpMM for sm_100a,  Y[M,F] (+)= A[M,K] * X[K,F], fp32.
+//
+// Work decomposition (the "plan", built once per sparsity pattern):
+//   the M row-end events and the nnz nonzeros are merged into one list of M+nnz items
+//   (merge-path); the list is cut every kItems items and one WARP owns one chunk.  A cut
+//   that lands inside a row no longer than a chunk is moved forward to the end of that
+//   row, so only hub rows (longer than a chunk) are ever shared between warps.
+// Per chunk a warp
+//   - streams its slice of col/val with coalesced 128-byte loads (one nonzero per lane),
+//     broadcasts them with shuffles,
+//   - gathers feature rows with 128-bit loads: G = min(32, F/4 rounded up to a power of
+//     two) lanes cover one feature row, so S = 32/G nonzeros are fetched per warp load
+//     instruction and U such instructions are issued back to back before any is consumed
+//     (U*NV independent 16-byte loads in flight per lane),
+//   - applies one fused multiply-add per nonzero in CSR order (the reference's order,
+//     model/ops/src/spmm.cpp:97-126); when accumulating, the chain starts from the old
+//     output row (fetched one row ahead), exactly as the reference loads `out` first
+//     (spmm.cpp:79-95); at every row end it folds the S lane groups with xor-shuffles and
+//     writes the row once with streaming stores.
+// A row cut across chunks is finished by the chunk that holds its row end; the earlier
+// chunks park their partial sums in `scratch` and a second small kernel adds them in chunk
+// order -- deterministic, no float atomics.
+//
+// HBM traffic per launch: nnz*(4+4) index/value bytes + one 4F-byte gather per nonzero
+// (less what L2 catches) + (M+1)*8 rowptr + M*F*4 output (+ the same again when
+// accumulating).
+#include <limits.h>
+#include <stdlib.h>
+
+#include "common.cuh"
+
+namespace gnnagg {
+
+constexpr int kWarpsPerBlock = 4;
+constexpr uint32_t kPlanMagic = 0x4d50534eu;  // "NSPM"
+constexpr int kDefaultItems = 512;
+
+struct PlanHeader {
+    uint32_t magic;
+    int32_t items;
+    int64_t M;
+    int64_t nnz;
+    int64_t nchunks;
+    int64_t pad[4];
+};
+static_assert(sizeof(PlanHeader) == 64, "plan header is 64 bytes");
+
+static int chunk_items() {
+    static int cached = 0;
+    if (cached == 0) {
+        int v = kDefaultItems;
+        const char *s = getenv("GNNAGG_SPMM_CHUNK_ITEMS");  // tuning knob
+        if (s != nullptr) {
+            const int t = atoi(s);
+            if (t >= 32 && t <= (1 << 20)) v = t;
+        }
+        cached = v;
+    }
+    return cached;
+}
+
+static int64_t num_chunks(int64_t M, int64_t nnz, int items) {
+    const int64_t n = div_up(M + nnz, items);
+    return n > 0 ? n : 1;
+}
+
+static const int64_t *plan_chunk_nz(const void *plan) {
+    return reinterpret_cast<const int64_t *>(static_cast<const char *>(plan) + sizeof(PlanHeader));
+}
+static const int32_t *plan_chunk_row(const void *plan, int64_t nchunks) { return reinterpret_cast<const int32_t *>(plan_chunk_nz(plan) + (nchunks + 1)); }
+
+// One thread per chunk boundary: merge-path diagonal search, then snap to a row end.
+__global__ void spmm_plan_kernel(const int64_t *__restrict__ rowptr, int64_t M, int64_t nnz, int items,
+                                 int64_t nchunks, PlanHeader *hdr, int64_t *__restrict__ chunk_nz,
+                                 int32_t *__restrict__ chunk_row) {
+    const int64_t c = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (c == 0) {
+        hdr->magic = kPlanMagic;
+        hdr->items = items;
+        hdr->M = M;
+        hdr->nnz = nnz;
+        hdr->nchunks = nchunks;
+    }
+    if (c > nchunks) return;
+    int64_t diag = c * (int64_t)items;
+    if (diag > M + nnz || c == nchunks) diag = M + nnz;
+    int64_t lo = diag > nnz ? diag - nnz : 0;
+    int64_t hi = diag < M ? diag : M;
+    while (lo < hi) {
+        const int64_t mid = (lo + hi) >> 1;
+        // row-end event of row `mid` precedes nonzero number (diag-1-mid)?
+        if (rowptr[mid + 1] <= diag - 1 - mid)
+            lo = mid + 1;
+        else
+            hi = mid;
+    }
+    int64_t r = lo, e = diag - lo;
+    if (r < M) {
+        const int64_t rs = rowptr[r], re = rowptr[r + 1];
+        if (e > rs && re - rs <= items) {  // inside a short row: give the whole row to the earlier chunk
+            e = re;
+            r = r + 1;
+        }
+    }
+    chunk_nz[c] = e;
+    chunk_row[c] = (int32_t)r;
+}
+
+template <int VW>
+struct Vec {
+    float v[VW];
+};
+
+template <int VW>
+__device__ __forceinline__ Vec<VW> vload(const float *p);
+template <>
+__device__ __forceinline__ Vec<4> vload<4>(const float *p) {
+    const float4 t = ld_nc_v4(p);
+    Vec<4> r;
+    r.v[0] = t.x, r.v[1] = t.y, r.v[2] = t.z, r.v[3] = t.w;
+    return r;
+}
+template <>
+__device__ __forceinline__ Vec<1> vload<1>(const float *p) {
+    Vec<1> r;
+    r.v[0] = ld_nc(p);
+    return r;
+}
+template <int VW>
+__device__ __forceinline__ Vec<VW> vload_plain(const float *p);
+template <>
+__device__ __forceinline__ Vec<4> vload_plain<4>(const float *p) {
+    const float4 t = *reinterpret_cast<const float4 *>(p);
+    Vec<4> r;
+    r.v[0] = t.x, r.v[1] = t.y, r.v[2] = t.z, r.v[3] = t.w;
+    return r;
+}
+template <>
+__device__ __forceinline__ Vec<1> vload_plain<1>(const float *p) {
+    Vec<1> r;
+    r.v[0] = *p;
+    return r;
+}
+template <int VW>
+__device__ __forceinline__ void vstore_stream(float *p, const Vec<VW> &a);
+template <>
+__device__ __forceinline__ void vstore_stream<4>(float *p, const Vec<4> &a) {
+    st_stream_v4(p, make_float4(a.v[0], a.v[1], a.v[2], a.v[3]));
+}
+template <>
+__device__ __forceinline__ void vstore_stream<1>(float *p, const Vec<1> &a) {
+    st_stream(p, a.v[0]);
+}
+template <int VW>
+__device__ __forceinline__ void vstore_plain(float *p, const Vec<VW> &a);
+template <>
+__device__ __forceinline__ void vstore_plain<4>(float *p, const Vec<4> &a) {
+    *reinterpret_cast<float4 *>(p) = make_float4(a.v[0], a.v[1], a.v[2], a.v[3]);
+}
+template <>
+__device__ __forceinline__ void vstore_plain<1>(float *p, const Vec<1> &a) {
+    *p = a.v[0];
+}
+
+// G lanes per feature row, NV vectors of VW floats per lane, U gather instructions in flight.
+template <int G, int NV, int VW, int U>
+__global__ void __launch_bounds__(kWarpsPerBlock * 32)
+    spmm_chunk_kernel(const int64_t *__restrict__ rowptr, const int32_t *__restrict__ col,
+                      const float *__restrict__ val, int64_t M, const float *__restrict__ X, int64_t ldx,
+                      float *__restrict__ Y, int64_t ldy, int FV, int accumulate,
+                      const int64_t *__restrict__ chunk_nz, const int32_t *__restrict__ chunk_row, int64_t nchunks,
+                      float *__restrict__ carry, int carry_ld) {
+    constexpr int S = 32 / G;  // nonzeros fetched per warp-wide gather instruction
+    const int lane = threadIdx.x & 31;
+    const int64_t c = (int64_t)blockIdx.x * kWarpsPerBlock + (threadIdx.x >> 5);
+    if (c >= nchunks) return;
+    const int gl = lane % G, grp = lane / G;
+
+    const int64_t e0 = chunk_nz[c], e1 = chunk_nz[c + 1];
+    int r = chunk_row[c];
+    const int r1 = chunk_row[c + 1];
+    const int n = (int)(e1 - e0);
+
+    int voff[NV];
+    bool vok[NV];
+#pragma unroll
+    for (int k = 0; k < NV; ++k) {
+        voff[k] = (gl + k * G) * VW;
+        vok[k] = (gl + k * G) < FV;
+    }
+
+    const bool acc_mode = accumulate != 0;
+    Vec<VW> acc[NV];    // running sum of the current row (lane group 0 starts from the old Y when accumulating)
+    Vec<VW> ynext[NV];  // accumulate mode: old Y of the row after the current one, fetched one row ahead
+
+    // Old output row `row` into dst (lane group 0; zeros elsewhere and when not accumulating).
+    auto load_y = [&](int row, Vec<VW>(&dst)[NV]) {
+#pragma unroll
+        for (int k = 0; k < NV; ++k) {
+            if (acc_mode && grp == 0 && vok[k] && row < M) {
+                dst[k] = vload_plain<VW>(Y + (int64_t)row * ldy + voff[k]);
+            } else {
+#pragma unroll
+                for (int i = 0; i < VW; ++i) dst[k].v[i] = 0.f;
+            }
+        }
+    };
+
+    // Row ends of the next 32 rows, relative to e0, one per lane.
+    auto load_row_ends = [&](int base) -> int {
+        const int row = base + lane;
+        if (row < r1) return (int)(rowptr[row + 1] - e0);
+        return INT_MAX;
+    };
+    int rbase = r;
+    int row_ends = load_row_ends(rbase);
+    int next_end = __shfl_sync(kFullMask, row_ends, 0);
+    // Where the current row's nonzeros start, relative to e0: negative when the row began in an
+    // earlier chunk.
+    int row_start = 0;
+    if (r < M) {
+        const int64_t d = rowptr[r] - e0;
+        row_start = d < 0 ? -1 : (int)d;
+    }
+    // The reference adds a row's terms onto the old output in order (old + a1*x1 + a2*x2 ...):
+    // start the chain from the old row.  Only the chunk that FINISHES a row (r < r1) reads and
+    // writes its Y, so a hub row cut across chunks has one reader/writer and no race; the chunks
+    // before it start from zero and park their sums.
+    load_y(r < r1 ? r : (int)M, acc);
+    load_y(r + 1 < r1 ? r + 1 : (int)M, ynext);
+
+    auto advance_row = [&]() {
+        row_start = next_end;
+        ++r;
+        if (r - rbase == 32) {
+            rbase = r;
+            row_ends = load_row_ends(rbase);
+        }
+        next_end = __shfl_sync(kFullMask, row_ends, r - rbase);
+#pragma unroll
+        for (int k = 0; k < NV; ++k) acc[k] = ynext[k];
+        load_y(r + 1 < r1 ? r + 1 : (int)M, ynext);
+    };
+
+    // Fold the S lane groups and write row r (its last nonzero is in this chunk).
+    auto flush_row = [&]() {
+        if (S > 1) {
+#pragma unroll
+            for (int off = G; off < 32; off <<= 1)
+#pragma unroll
+                for (int k = 0; k < NV; ++k)
+#pragma unroll
+                    for (int i = 0; i < VW; ++i) acc[k].v[i] += __shfl_xor_sync(kFullMask, acc[k].v[i], off);
+        }
+        // accumulating onto an empty row changes nothing: skip the store
+        const bool untouched = acc_mode && row_start >= 0 && next_end == row_start;
+        if (grp == 0 && !untouched) {
+            float *yp = Y + (int64_t)r * ldy;
+#pragma unroll
+            for (int k = 0; k < NV; ++k)
+                if (vok[k]) vstore_stream<VW>(yp + voff[k], acc[k]);
+        }
+    };
+
+    for (int eb = 0; eb < n; eb += 32) {
+        int my_col = 0;
+        float my_val = 0.f;
+        if (eb + lane < n) {
+            my_col = ld_stream(col + e0 + eb + lane);
+            my_val = ld_stream(val + e0 + eb + lane);
+        }
+        const int in_batch = (n - eb) < 32 ? (n - eb) : 32;
+        const int nsteps = (in_batch + S - 1) / S;
+        for (int s0 = 0; s0 < nsteps; s0 += U) {
+            Vec<VW> xr[U][NV];
+            float av[U];
+            bool ok[U];
+#pragma unroll
+            for (int u = 0; u < U; ++u) {
+                const int j = (s0 + u) * S + grp;  // position inside the 32-nonzero batch
+                const int cc = __shfl_sync(kFullMask, my_col, j & 31);
+                av[u] = __shfl_sync(kFullMask, my_val, j & 31);
+                ok[u] = j < in_batch;
+                const float *xp = X + (int64_t)cc * ldx;
+#pragma unroll
+                for (int k = 0; k < NV; ++k) {
+                    if (ok[u] && vok[k]) {
+                        xr[u][k] = vload<VW>(xp + voff[k]);
+                    } else {
+#pragma unroll
+                        for (int i = 0; i < VW; ++i) xr[u][k].v[i] = 0.f;
+                    }
+                }
+            }
+#pragma unroll
+            for (int u = 0; u < U; ++u) {
+                if (s0 + u < nsteps) {  // warp-uniform
+                    const int step_end = eb + (s0 + u + 1) * S;
+                    const int eg = eb + (s0 + u) * S + grp;
+                    bool pending = ok[u];
+                    while (next_end < step_end) {  // a row ends before this step's last nonzero
+                        if (pending && eg < next_end) {
+#pragma unroll
+                            for (int k = 0; k < NV; ++k)
+#pragma unroll
+                                for (int i = 0; i < VW; ++i)
+                                    acc[k].v[i] = fmaf(av[u], xr[u][k].v[i], acc[k].v[i]);
+                            pending = false;
+                        }
+                        flush_row();
+                        advance_row();
+                    }
+                    if (pending) {
+#pragma unroll
+                        for (int k = 0; k < NV; ++k)
+#pragma unroll
+                            for (int i = 0; i < VW; ++i) acc[k].v[i] = fmaf(av[u], xr[u][k].v[i], acc[k].v[i]);
+                    }
+                }
+            }
+        }
+    }
+    // Row ends that follow the chunk's last nonzero (including empty rows).
+    while (r < r1) {
+        flush_row();
+        advance_row();
+    }
+    // A hub row continues in the next chunk: park the partial sum.
+    if (r1 < M && e1 > rowptr[r1]) {
+        if (S > 1) {
+#pragma unroll
+            for (int off = G; off < 32; off <<= 1)
+#pragma unroll
+                for (int k = 0; k < NV; ++k)
+#pragma unroll
+                    for (int i = 0; i < VW; ++i) acc[k].v[i] += __shfl_xor_sync(kFullMask, acc[k].v[i], off);
+        }
+        if (grp == 0) {
+            float *cp = carry + c * (int64_t)carry_ld;
+#pragma unroll
+            for (int k = 0; k < NV; ++k)
+                if (vok[k]) vstore_plain<VW>(cp + voff[k], acc[k]);
+        }
+    }
+}
+
+// One warp per chunk; only the first chunk of a run of chunks that park partial sums for
+// the same row does anything: it adds the run, in chunk order, onto the row.
+__global__ void __launch_bounds__(kWarpsPerBlock * 32)
+    spmm_fixup_kernel(const int64_t *__restrict__ rowptr, int64_t M, float *__restrict__ Y, int64_t ldy, int F,
+                      const int64_t *__restrict__ chunk_nz, const int32_t *__restrict__ chunk_row, int64_t nchunks,
+                      const float *__restrict__ carry, int carry_ld) {
+    const int lane = threadIdx.x & 31;
+    const int64_t c = (int64_t)blockIdx.x * kWarpsPerBlock + (threadIdx.x >> 5);
+    if (c >= nchunks) return;
+    const int row = chunk_row[c + 1];
+    if (row >= M) return;
+    const int64_t rs = rowptr[row];
+    if (chunk_nz[c + 1] <= rs) return;                              // chunk c parks nothing
+    if (c > 0 && chunk_row[c] == row && chunk_nz[c] > rs) return;  // chunk c-1 leads this run
+    int64_t last = c;
+    while (last + 1 < nchunks && chunk_row[last + 2] == row) ++last;  // chunks c..last all park into `row`
+    float *yp = Y + (int64_t)row * ldy;
+    for (int f = lane; f < F; f += 32) {
+        float s = 0.f;
+        for (int64_t j = c; j <= last; ++j) s += carry[j * (int64_t)carry_ld + f];
+        yp[f] += s;
+    }
+}
+
+__global__ void csr_validate_kernel(const int64_t *__restrict__ rowptr, const int32_t *__restrict__ col, int64_t M,
+                                    int64_t K, int64_t nnz, int32_t *status) {
+    const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+    int bad = 0;
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i <= M; i += stride) {
+        const int64_t v = rowptr[i];
+        if (i == 0 && v != 0) bad |= 1;
+        if (i == M && v != nnz) bad |= 1;
+        if (i < M && (v > rowptr[i + 1] || v < 0)) bad |= 1;
+    }
+    for (int64_t e = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; e < nnz; e += stride) {
+        const int32_t cidx = col[e];
+        if (cidx < 0 || cidx >= K) bad |= 2;
+    }
+    if (bad) atomicOr(status, bad);
+}
+
+template <int G, int NV, int VW, int U>
+static void launch_chunks(const int64_t *rowptr, const int32_t *col, const float *val, int64_t M, const float *X,
+                          int64_t ldx, float *Y, int64_t ldy, int FV, int accumulate, const int64_t *chunk_nz,
+                          const int32_t *chunk_row, int64_t nchunks, float *carry, int carry_ld, cudaStream_t st) {
+    const unsigned blocks = (unsigned)div_up(nchunks, kWarpsPerBlock);
+    spmm_chunk_kernel<G, NV, VW, U><<<blocks, kWarpsPerBlock * 32, 0, st>>>(
+        rowptr, col, val, M, X, ldx, Y, ldy, FV, accumulate, chunk_nz, chunk_row, nchunks, carry, carry_ld);
+}
+
+template <int VW>
+static void dispatch_width(int FV, const int64_t *rowptr, const int32_t *col, const float *val, int64_t M,
+                           const float *X, int64_t ldx, float *Y, int64_t ldy, int accumulate,
+                           const int64_t *chunk_nz, const int32_t *chunk_row, int64_t nchunks, float *carry,
+                           int carry_ld, cudaStream_t st) {
+#define GNNAGG_LAUNCH(G, NV, U)                                                                                 \
+    launch_chunks<G, NV, VW, U>(rowptr, col, val, M, X, ldx, Y, ldy, FV, accumulate, chunk_nz, chunk_row, nchunks, \
+                                carry, carry_ld, st)
+    if (FV <= 2)
+        GNNAGG_LAUNCH(2, 1, 2);
+    else if (FV <= 4)
+        GNNAGG_LAUNCH(4, 1, 4);
+    else if (FV <= 8)
+        GNNAGG_LAUNCH(8, 1, 8);
+    else if (FV <= 16)
+        GNNAGG_LAUNCH(16, 1, 8);
+    else if (FV <= 32)
+        GNNAGG_LAUNCH(32, 1, 8);
+    else if (FV <= 64)
+        GNNAGG_LAUNCH(32, 2, 4);
+    else if (FV <= 96)
+        GNNAGG_LAUNCH(32, 3, 2);
+    else
+        GNNAGG_LAUNCH(32, 4, 2);
+#undef GNNAGG_LAUNCH
+}
+
+}  // namespace gnnagg
+
+using namespace gnnagg;
+
+extern "C" size_t gnnagg_spmm_plan_bytes(int64_t M, int64_t nnz) {
+    if (M < 0 || nnz < 0) return 0;
+    const int64_t nc = num_chunks(M, nnz, chunk_items());
+    size_t b = sizeof(PlanHeader) + (size_t)(nc + 1) * (sizeof(int64_t) + sizeof(int32_t));
+    return (b + 255) & ~(size_t)255;
+}
+
+extern "C" int gnnagg_spmm_plan_build(const int64_t *rowptr, int64_t M, int64_t nnz, void *plan, size_t plan_bytes,
+                                      void *stream) {
+    if (rowptr == nullptr || plan == nullptr || M < 0 || nnz < 0)
+        return fail(GNNAGG_ERR_ARG, "spmm_plan_build: null pointer or negative size");
+    if (M > INT32_MAX - 64) return fail(GNNAGG_ERR_UNSUPPORTED, "spmm_plan_build: M must fit int32");
+    if (plan_bytes < gnnagg_spmm_plan_bytes(M, nnz) || (reinterpret_cast<uintptr_t>(plan) & 7u))
+        return fail(GNNAGG_ERR_SCRATCH, "spmm_plan_build: plan buffer too small or not 8-byte aligned");
+    const int items = chunk_items();
+    const int64_t nc = num_chunks(M, nnz, items);
+    char *base = static_cast<char *>(plan);
+    int64_t *cnz = reinterpret_cast<int64_t *>(base + sizeof(PlanHeader));
+    int32_t *crow = reinterpret_cast<int32_t *>(cnz + (nc + 1));
+    const int threads = 256;
+    const unsigned blocks = (unsigned)div_up(nc + 1, threads);
+    spmm_plan_kernel<<<blocks, threads, 0, static_cast<cudaStream_t>(stream)>>>(
+        rowptr, M, nnz, items, nc, reinterpret_cast<PlanHeader *>(base), cnz, crow);
+    return check_launch("spmm_plan_kernel");
+}
+
+// Widest column strip one launch covers: 128 vectors per row.
+static int strip_floats(int vw) { return vw == 4 ? 512 : 128; }
+
+extern "C" size_t gnnagg_spmm_scratch_bytes(int64_t M, int64_t nnz, int32_t F) {
+    if (M < 0 || nnz < 0 || F <= 0) return 0;
+    const int64_t nc = num_chunks(M, nnz, chunk_items());
+    int ld = (F + 3) & ~3;
+    if (ld > 512) ld = 512;
+    return (((size_t)nc * ld * sizeof(float)) + 255) & ~(size_t)255;
+}
+
+extern "C" int gnnagg_spmm_csr_f32(const int64_t *rowptr, const int32_t *col, const float *val, int64_t M, int64_t K,
+                                   int64_t nnz, const float *X, int64_t ldx, float *Y, int64_t ldy, int32_t F,
+                                   int32_t accumulate, const void *plan, void *scratch, size_t scratch_bytes,
+                                   void *stream) {
+    if (M < 0 || K < 0 || nnz < 0 || F < 0) return fail(GNNAGG_ERR_ARG, "spmm: negative size");
+    if (M == 0 || F == 0) return GNNAGG_OK;
+    if (rowptr == nullptr || Y == nullptr || plan == nullptr) return fail(GNNAGG_ERR_ARG, "spmm: null pointer");
+    if (nnz > 0 && (col == nullptr || val == nullptr || X == nullptr))
+        return fail(GNNAGG_ERR_ARG, "spmm: null pointer");
+    if (ldx < F || ldy < F) return fail(GNNAGG_ERR_ARG, "spmm: leading dimension smaller than F");
+    if (M > INT32_MAX - 64 || K > INT32_MAX) return fail(GNNAGG_ERR_UNSUPPORTED, "spmm: M, K must fit int32");
+    if (scratch == nullptr || scratch_bytes < gnnagg_spmm_scratch_bytes(M, nnz, F) || !aligned16(scratch))
+        return fail(GNNAGG_ERR_SCRATCH, "spmm: scratch missing, too small or not 16-byte aligned");
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    const int items = chunk_items();
+    const int64_t nc = num_chunks(M, nnz, items);
+    const int64_t *cnz = plan_chunk_nz(plan);
+    const int32_t *crow = plan_chunk_row(plan, nc);
+    float *carry = static_cast<float *>(scratch);
+
+    const bool vec4 = (F % 4 == 0) && (ldx % 4 == 0) && (ldy % 4 == 0) && aligned16(X) && aligned16(Y);
+    const int vw = vec4 ? 4 : 1;
+    const int strip = strip_floats(vw);
+    for (int f0 = 0; f0 < F; f0 += strip) {
+        const int fs = (F - f0) < strip ? (F - f0) : strip;
+        const int carry_ld = (fs + 3) & ~3;
+        const float *Xs = X == nullptr ? nullptr : X + f0;
+        float *Ys = Y + f0;
+        if (vec4)
+            dispatch_width<4>(fs / 4, rowptr, col, val, M, Xs, ldx, Ys, ldy, accumulate, cnz, crow, nc, carry, carry_ld,
+                              st);
+        else
+            dispatch_width<1>(fs, rowptr, col, val, M, Xs, ldx, Ys, ldy, accumulate, cnz, crow, nc, carry, carry_ld, st);
+        int rc = check_launch("spmm_chunk_kernel");
+        if (rc != GNNAGG_OK) return rc;
+        spmm_fixup_kernel<<<(unsigned)div_up(nc, kWarpsPerBlock), kWarpsPerBlock * 32, 0, st>>>(
+            rowptr, M, Ys, ldy, fs, cnz, crow, nc, carry, carry_ld);
+        rc = check_launch("spmm_fixup_kernel");
+        if (rc != GNNAGG_OK) return rc;
+    }
+    return GNNAGG_OK;
+}
+
+extern "C" int gnnagg_csr_validate(const int64_t *rowptr, const int32_t *col, int64_t M, int64_t K, int64_t nnz,
+                                   int32_t *status, void *stream) {
+    if (rowptr == nullptr || status == nullptr || M < 0 || K < 0 || nnz < 0 || (nnz > 0 && col == nullptr))
+        return fail(GNNAGG_ERR_ARG, "csr_validate: null pointer or negative size");
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    cudaMemsetAsync(status, 0, sizeof(int32_t), st);
+    csr_validate_kernel<<<kNumSMs * 8, 256, 0, st>>>(rowptr, col, M, K, nnz, status);
+    return check_launch("csr_validate_kernel");
+}

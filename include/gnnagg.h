@@ -1,0 +1,152 @@
+/*
+ * libgnnagg -- C ABI of the B200 (sm_100a) graph-aggregation kernels.
+ *
+ * This is the boundary a maintainer of the reference binds in place of its pybind11
+ * module `computation_ops` (self_benchmark/a64fx/model/ops/src/ops.cpp:11-24).
+ *
+ * Conventions
+ *   - every pointer is a DEVICE pointer owned by the caller unless its comment says
+ *     "host"; nothing here allocates or frees device memory;
+ *   - `stream` is a cudaStream_t passed as void*; work is enqueued, never synchronised;
+ *   - dense matrices are row-major fp32 with an explicit leading dimension in elements;
+ *   - return value: 0 = ok, < 0 = argument / launch error found on the host
+ *     (see gnnagg_error_string), never a device trap;
+ *   - safe to call from one host thread per GPU; the library keeps no global state
+ *     apart from a thread-local message for the last error.
+ */
+#ifndef GNNAGG_H
+#define GNNAGG_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define GNNAGG_OK 0
+#define GNNAGG_ERR_ARG (-1)         /* null pointer, negative size, bad flag          */
+#define GNNAGG_ERR_UNSUPPORTED (-2) /* shape outside what the kernels are built for   */
+#define GNNAGG_ERR_CUDA (-3)        /* cudaGetLastError() after the launch was not ok */
+#define GNNAGG_ERR_SCRATCH (-4)     /* plan / scratch buffer too small or malformed   */
+
+/* Library version (major*10000 + minor*100 + patch). */
+int gnnagg_version(void);
+
+/* Static text for a status code; the thread's last detailed message when code < 0 and
+ * one was recorded.  Never NULL. */
+const char *gnnagg_error_string(int code);
+
+/* ------------------------------------------------------------------------------------
+ * K1  CSR SpMM   Y[M,F] (+)= A[M,K] * X[K,F]
+ *
+ * Replaces computation_ops.spmm == spmm_cpu_optimized_no_tile_v1
+ * (model/ops/src/spmm.cpp:327-507, inner loop kernel_1xN :24-143) and the greedy
+ * per-thread row split computed by distribute_work_for_row
+ * (model/ops/spmm_kernel.py:7-28), which becomes the `plan` below.
+ *
+ * The transposed product (SPMM_backward, model/ops/spmm_kernel.py:71-90) is the same
+ * call on the CSC arrays (colptr, row_T, value_T) with its own plan.
+ *
+ * A plan is an opaque, relocatable byte buffer describing how the (rows + nonzeros) of
+ * one sparsity pattern are cut into equal work chunks (merge-path).  It depends only
+ * on rowptr, is built once per matrix and is valid for every F.
+ *
+ * scratch: device buffer of gnnagg_spmm_scratch_bytes(); holds the partial sums of the
+ * rows that are cut across chunks (hub rows).  Contents need not be initialised and are
+ * garbage afterwards; two SpMM calls that may overlap on the GPU need separate scratch.
+ *
+ * accumulate != 0 : Y += A*X (the reference's semantics: it loads `out` first,
+ *                   spmm.cpp:79-95);  accumulate == 0 : Y = A*X, empty rows written 0.
+ * Summation order: nonzeros of a row are applied in CSR order with one fused
+ * multiply-add each, as in the reference, whenever the row is processed by one
+ * chunk and F > 64; rows cut across chunks, and narrower F (several nonzeros in
+ * flight per warp), differ from it only by fp32 re-association.  The result is
+ * deterministic (no float atomics).
+ * ---------------------------------------------------------------------------------- */
+size_t gnnagg_spmm_plan_bytes(int64_t M, int64_t nnz);
+int gnnagg_spmm_plan_build(const int64_t *rowptr, int64_t M, int64_t nnz, void *plan, size_t plan_bytes,
+                           void *stream);
+size_t gnnagg_spmm_scratch_bytes(int64_t M, int64_t nnz, int32_t F);
+int gnnagg_spmm_csr_f32(const int64_t *rowptr, const int32_t *col, const float *val, int64_t M, int64_t K,
+                        int64_t nnz, const float *X, int64_t ldx, float *Y, int64_t ldy, int32_t F,
+                        int32_t accumulate, const void *plan, void *scratch, size_t scratch_bytes,
+                        void *stream);
+
+/* Checks on the device that rowptr is monotone with rowptr[0]==0, rowptr[M]==nnz and
+ * that every col is in [0,K).  status (device int32[1]) receives 0 or a bit mask
+ * (1 = rowptr, 2 = col); the caller reads it back.  Has no counterpart in the
+ * reference, which trusts its inputs; used by the host layer before a first launch. */
+int gnnagg_csr_validate(const int64_t *rowptr, const int32_t *col, int64_t M, int64_t K, int64_t nnz,
+                        int32_t *status, void *stream);
+
+/* ------------------------------------------------------------------------------------
+ * K2a  row gather   OUT[i,:] = X[idx[i],:]
+ * Replaces torch.index_select(local_nodes_feat, 0, idx_nodes_send_to_others, out=send_buf)
+ * (model/layers/aggregator.py:51).
+ * ---------------------------------------------------------------------------------- */
+int gnnagg_gather_rows_f32(const float *X, int64_t ldx, const int32_t *idx, int64_t rows, int32_t F,
+                           float *OUT, int64_t ldo, void *stream);
+
+/* ------------------------------------------------------------------------------------
+ * K3a  per-row min/max quantise + row-pack, one call for all peer segments
+ *
+ * Replaces computation_ops.quantize_tensor_for_all_procs
+ * (model/ops/src/quantization_arm.cpp:364-435, kernel :80-217, segmenting :21-78) for
+ * bits == 2, and, with one segment, the row-packed layout of the x86
+ * computation_ops.quantize_tensor (model/ops/src/quantization_x86.cpp:17-102) for
+ * bits in {2,4,8}.
+ *
+ *   seg        device int32[P+1], prefix of per-peer row counts (seg[0] == 0)
+ *   idx        optional: row i is read from X[idx[i],:] (fuses K2a); NULL = X[i,:]
+ *   params     (rows,2) fp32 [zero_point, scale].  params_given == 0: computed here
+ *              (zero_point = row min, scale = (max-min)/(2^bits-1), 0 -> 1) and written;
+ *              params_given != 0: read (the x86 generic signature: caller-supplied).
+ *   params_bf16 optional (rows,2) bf16 copy of params, round-to-nearest-even: the wire
+ *              format of communicator.py:297 (fuses that cast); NULL to skip.
+ *   codes      (sum_p ceil(n_p / (8/bits)), F) uint8, row stride F; 8/bits consecutive
+ *              rows of one segment share a byte per column, first row in the high bits.
+ * ---------------------------------------------------------------------------------- */
+int gnnagg_quant_pack_rows(const float *X, int64_t ldx, const int32_t *idx, int32_t F, const int32_t *seg,
+                           int32_t P, int64_t rows, int32_t bits, int32_t params_given, float *params,
+                           void *params_bf16, uint8_t *codes, void *stream);
+
+/* ------------------------------------------------------------------------------------
+ * K3b  unpack + dequantise   OUT[i,k] = fma(code, scale_i, zero_point_i)
+ *
+ * Replaces computation_ops.dequantize_tensor_for_all_procs
+ * (model/ops/src/quantization_arm.cpp:437-479, kernel :219-299) and, with one segment,
+ * the x86 dequantize_tensor (model/ops/src/quantization_x86.cpp:104-168; its
+ * val*scale+min is one fma under the reference's own build flags).
+ *
+ *   params_bf16 != NULL: parameters are read from the bf16 wire buffer (fuses the
+ *   bf16 -> fp32 copy of communicator.py:303) and, if params != NULL, the widened fp32
+ *   values are also stored there; params_bf16 == NULL: parameters are read from params.
+ * ---------------------------------------------------------------------------------- */
+int gnnagg_unpack_dequant_rows(const uint8_t *codes, int32_t F, const int32_t *seg, int32_t P, int64_t rows,
+                               int32_t bits, float *params, const void *params_bf16, float *OUT, int64_t ldo,
+                               void *stream);
+
+/* ------------------------------------------------------------------------------------
+ * K3c  mixed-bit column-packed codec (per-row bits in {8,4,2})
+ *
+ * Replaces computation_ops.quantize_tensor_v1 / dequantize_tensor_v1
+ * (model/ops/src/quantization_x86.cpp:170-312, quantization_kernel_x86.h:11-75).
+ *   params (rows,3) fp32 [bits, zero_point, scale]; bits is read, the other two written
+ *   (quantise) or read (dequantise).  range int64[rows+1]: byte offsets of each row in
+ *   codes (quantizer.py:69-76).
+ * ---------------------------------------------------------------------------------- */
+int gnnagg_quant_v1_rows(const float *X, int64_t ldx, int64_t rows, int32_t F, const int64_t *range,
+                         float *params, uint8_t *codes, void *stream);
+int gnnagg_dequant_v1_rows(const uint8_t *codes, int64_t rows, int32_t F, const int64_t *range,
+                           const float *params, float *OUT, int64_t ldo, void *stream);
+
+/* fp32 <-> bf16 (round-to-nearest-even) buffer casts of the 16-bit halo mode
+ * (communicator.py:128,137: send_buf_fp16.copy_(send_buf), recv_buf.copy_(recv_buf_fp16)). */
+int gnnagg_cast_f32_to_bf16(const float *src, void *dst_bf16, int64_t n, void *stream);
+int gnnagg_cast_bf16_to_f32(const void *src_bf16, float *dst, int64_t n, void *stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* GNNAGG_H */

@@ -1,0 +1,112 @@
+"""In-process stand-in for torch.distributed so that P ranks of the aggregation path can run as P
+threads on ONE GPU (NCCL refuses two ranks on one device, and kernels of different ranks must not
+spin on one another on a shared GPU -- here they never wait on the device, only on host barriers).
+
+Only what the path uses is provided: get_rank / get_world_size / is_initialized / get_backend /
+barrier / all_to_all_single (row splits, sync or "async").  Each rank runs on its own CUDA stream.
+"""
+import threading
+from contextlib import contextmanager
+
+import torch
+import torch.distributed as dist
+
+
+class _Work:
+    def wait(self):
+        return True
+
+
+class FakeWorld:
+    def __init__(self, world_size: int):
+        self.P = world_size
+        self._barrier = threading.Barrier(world_size)
+        self._slots = [None] * world_size
+        self._local = threading.local()
+
+    # ---- torch.distributed surface ----
+    def get_rank(self, group=None):
+        return self._local.rank
+
+    def get_world_size(self, group=None):
+        return self.P
+
+    def is_initialized(self):
+        return True
+
+    def is_available(self):
+        return True
+
+    def get_backend(self, group=None):
+        return "nccl"  # plans are built on the tensors' own device
+
+    def barrier(self, *a, **k):
+        self._barrier.wait()
+
+    def all_to_all_single(self, output, input, output_split_sizes=None, input_split_sizes=None, group=None,
+                          async_op=False):
+        r, P = self._local.rank, self.P
+        if input_split_sizes is None:
+            input_split_sizes = [input.size(0) // P] * P
+        if output_split_sizes is None:
+            output_split_sizes = [output.size(0) // P] * P
+        if input.is_cuda:
+            torch.cuda.current_stream().synchronize()  # producers of `input` are done
+        self._slots[r] = (input, list(input_split_sizes))
+        self._barrier.wait()
+        off_out = 0
+        for q in range(P):
+            src, splits = self._slots[q]
+            off_in = sum(splits[:r])
+            n = splits[r]
+            assert n == output_split_sizes[q], f"rank {r}: peer {q} sends {n} rows, expected {output_split_sizes[q]}"
+            if n:
+                output[off_out:off_out + n].copy_(src[off_in:off_in + n])
+            off_out += n
+        if output.is_cuda:
+            torch.cuda.current_stream().synchronize()
+        self._barrier.wait()  # nobody overwrites a send buffer before every peer has copied from it
+        return _Work() if async_op else None
+
+    # ---- harness ----
+    @contextmanager
+    def patched(self):
+        names = ("get_rank", "get_world_size", "is_initialized", "is_available", "get_backend", "barrier",
+                 "all_to_all_single")
+        saved = {n: getattr(dist, n) for n in names}
+        try:
+            for n in names:
+                setattr(dist, n, getattr(self, n))
+            yield self
+        finally:
+            for n, f in saved.items():
+                setattr(dist, n, f)
+
+    def run(self, fn):
+        """fn(rank) on P threads, each on its own CUDA stream; returns the list of results."""
+        results, errors = [None] * self.P, []
+
+        def target(rank):
+            self._local.rank = rank
+            try:
+                if torch.cuda.is_available():
+                    stream = torch.cuda.Stream()
+                    with torch.cuda.stream(stream):
+                        results[rank] = fn(rank)
+                        stream.synchronize()
+                else:
+                    results[rank] = fn(rank)
+            except BaseException as e:  # noqa: BLE001
+                errors.append((rank, e))
+                self._barrier.abort()
+
+        with self.patched():
+            threads = [threading.Thread(target=target, args=(r,)) for r in range(self.P)]
+            for t in threads:
+                t.start()
+            for t in threads:
+                t.join()
+        if errors:
+            errors.sort(key=lambda x: isinstance(x[1], threading.BrokenBarrierError))
+            raise errors[0][1]
+        return results

@@ -1,0 +1,180 @@
+"""Aggregator parity on one GPU: P ranks run as threads over an in-process exchange
+(tests/fake_dist.py).  Checked against (a) the product of the GLOBAL adjacency (plans + kernels +
+exchange together) and (b) the reference's order of operations restated with the CPU oracle on the
+same per-rank matrices: zeros -> local SpMM -> [quantise -> bf16 params -> dequantise] -> remote
+SpMM, which the CUDA path reproduces bit for bit at F >= 128 (one nonzero per warp instruction)."""
+from types import SimpleNamespace
+
+import numpy as np
+import pytest
+import torch
+
+import oracle
+from fake_dist import FakeWorld
+
+pytestmark = pytest.mark.gpu
+
+
+def make_graph(seed, P, n_per, deg):
+    """Directed multigraph over P contiguous blocks, with hubs; returns begin, global (src, dst)."""
+    rng = np.random.default_rng(seed)
+    sizes = rng.integers(max(1, n_per // 2), n_per + 1, size=P)
+    begin = np.concatenate([[0], np.cumsum(sizes)]).astype(np.int64)
+    N = int(begin[-1])
+    E = N * deg
+    src = rng.integers(0, N, size=E)
+    dst = rng.integers(0, N, size=E)
+    hubs = rng.integers(0, N, size=max(2, N // 50))
+    src[: E // 5] = rng.choice(hubs, size=E // 5)
+    dst[E // 5: 2 * E // 5] = rng.choice(hubs, size=2 * E // 5 - E // 5)
+    src = np.concatenate([src, src[: E // 20]])  # duplicated edges stay duplicated
+    dst = np.concatenate([dst, dst[: E // 20]])
+    return begin, src.astype(np.int64), dst.astype(np.int64)
+
+
+def global_csr(src, dst, N, transpose=False):
+    r, c = (src, dst) if transpose else (dst, src)
+    order = np.lexsort((c, r))
+    r, c = r[order], c[order]
+    rowptr = np.concatenate([[0], np.cumsum(np.bincount(r, minlength=N))]).astype(np.int64)
+    return rowptr, c.astype(np.int64), np.ones(len(c), np.float32)
+
+
+def csr_np(sp):
+    rp, c, v = sp.csr()
+    return rp.cpu().numpy(), c.cpu().numpy().astype(np.int64), v.cpu().numpy()
+
+
+def csc_np(sp):
+    return (sp.storage.colptr().cpu().numpy(), sp.storage.row_T().cpu().numpy().astype(np.int64),
+            sp.storage.value_T().cpu().numpy())
+
+
+def close(got, want, scale, rtol=1e-5):
+    err = np.abs(got.astype(np.float64) - want.astype(np.float64))
+    assert (err <= rtol * scale + 1e-30).all(), f"worst ratio {np.max(err / (scale + 1e-30)):.3e}"
+
+
+@pytest.mark.parametrize("P,num_bits,is_pre,F", [
+    (1, 32, False, 128), (2, 32, False, 128), (4, 32, False, 64), (3, 32, True, 128), (4, 32, True, 32),
+    (2, 2, False, 128), (4, 2, False, 256), (3, 2, True, 128), (4, 16, False, 128), (3, 8, False, 100),
+    (2, 4, True, 64),
+])
+def test_aggregator_forward_backward(cuda_lib, P, num_bits, is_pre, F):
+    from gnn_benchmark_b200 import Communicator, Quantizer_for_all_procs, TimeRecorder, graphgen
+    from gnn_benchmark_b200.aggregator import Aggregator
+    from gnn_benchmark_b200.data_manager.DataLoader import build_graph
+
+    begin_np, src, dst = make_graph(100 * P + F + num_bits, P, 700, 6)
+    N = int(begin_np[-1])
+    begin = torch.from_numpy(begin_np)
+    rng = np.random.default_rng(1)
+    X = rng.standard_normal((N, F)).astype(np.float32)
+    G = rng.standard_normal((N, F)).astype(np.float32)
+    s_t, d_t = torch.from_numpy(src).cuda(), torch.from_numpy(dst).cuda()
+
+    Communicator(num_bits, is_async=True)
+    Quantizer_for_all_procs(P, num_bits)
+    TimeRecorder(1, 1, enabled=False)
+    world = FakeWorld(P)
+
+    def rank_fn(rank):
+        local, remote = graphgen.partition_edges(s_t, d_t, begin, rank)
+        graph = build_graph(local, remote, begin, rank, P, F, num_bits, is_pre, device="cuda")
+        b0, b1 = int(begin[rank]), int(begin[rank + 1])
+        x = torch.from_numpy(X[b0:b1]).cuda()
+        g = torch.from_numpy(G[b0:b1]).cuda()
+        ctx = SimpleNamespace()
+        out = Aggregator.forward(ctx, graph, x, 0, num_bits, is_pre, True)
+        snap = {}
+        if P > 1:
+            snap["recv_fwd"] = graph.comm_buf.recv_buf.clone()
+            if num_bits in (2, 4, 8):
+                q = graph.comm_buf_for_quantization
+                snap["codes_fwd"] = q.quantized_send_data_buf.clone()
+                snap["params_fwd"] = q.quantized_send_params_buf_fp32.clone()
+        grad = Aggregator.backward(ctx, g)[1]
+        torch.cuda.current_stream().synchronize()
+        return graph, out.cpu().numpy(), grad.cpu().numpy(), {k: v.cpu().numpy() for k, v in snap.items()}
+
+    res = world.run(rank_fn)
+
+    # (a) against the global adjacency
+    rp, c, v = global_csr(src, dst, N)
+    want_out = oracle.spmm(rp, c, v, X)
+    scale_out = oracle.spmm(rp, c, v, np.abs(X))
+    rpt, ct, vt = global_csr(src, dst, N, transpose=True)
+    want_grad = oracle.spmm(rpt, ct, vt, G)
+    scale_grad = oracle.spmm(rpt, ct, vt, np.abs(G))
+    exact_halo = num_bits == 32
+    for r in range(P):
+        b0, b1 = int(begin[r]), int(begin[r + 1])
+        _, out, grad, _ = res[r]
+        if exact_halo:
+            close(out, want_out[b0:b1], scale_out[b0:b1])
+            close(grad, want_grad[b0:b1], scale_grad[b0:b1])
+        else:
+            # lossy halo: bounded by the quantisation step of the rows that crossed (loose sanity bound)
+            tol = {16: 2e-2, 8: 5e-2, 4: 0.5, 2: 2.5}[num_bits]
+            assert np.abs(out - want_out[b0:b1]).max() <= tol * max(1.0, scale_out[b0:b1].max())
+            assert np.abs(grad - want_grad[b0:b1]).max() <= tol * max(1.0, scale_grad[b0:b1].max())
+
+    # (b) the reference's sequence of operations, restated with the oracle on the same plan
+    if P > 1 and not is_pre and num_bits in (32, 2):
+        for r in range(P):
+            graph, out, grad, snap = res[r]
+            b0, b1 = int(begin[r]), int(begin[r + 1])
+            # what every peer sends to r, in peer order
+            recv_rows = []
+            for qk in range(P):
+                gq = res[qk][0]
+                idx = gq.idx_nodes_send_to_others.cpu().numpy()
+                offs = np.concatenate([[0], np.cumsum(gq.comm_splits.send_splits)])
+                sel = idx[offs[r]:offs[r + 1]]
+                qb0 = int(begin[qk])
+                rows = X[qb0 + sel]
+                if num_bits == 2:
+                    # peer qk quantises ALL its send rows in one call; r receives its segment
+                    allrows = X[qb0 + idx]
+                    codes, params = oracle.quantize_int2_for_all_procs(allrows, offs.astype(np.int32))
+                    np.testing.assert_array_equal(res[qk][3]["codes_fwd"], codes)
+                    np.testing.assert_array_equal(res[qk][3]["params_fwd"], params)
+                    deq = oracle.dequantize_int2_for_all_procs(codes, offs.astype(np.int32), oracle.bf16_round(params))
+                    rows = deq[offs[r]:offs[r + 1]]
+                recv_rows.append(rows)
+            recv = np.concatenate(recv_rows) if recv_rows else np.zeros((0, F), np.float32)
+            np.testing.assert_array_equal(snap["recv_fwd"], recv)
+            want = oracle.spmm(*csr_np(graph.local_adj_t), X[b0:b1])
+            if recv.shape[0]:
+                want = oracle.spmm(*csr_np(graph.remote_adj_t), recv, want)
+            if F >= 128:
+                np.testing.assert_array_equal(out, want)  # same FMA chain, same order
+            else:
+                close(out, want, scale_out[b0:b1])
+
+
+def test_single_rank_autograd(cuda_lib):
+    """world_size 1 through torch.autograd: forward A x, backward A^T g, no exchange."""
+    from gnn_benchmark_b200 import Aggregator, Communicator, Quantizer_for_all_procs, TimeRecorder, graphgen
+    from gnn_benchmark_b200.data_manager.DataLoader import build_graph
+
+    begin_np, src, dst = make_graph(5, 1, 900, 5)
+    N, F = int(begin_np[-1]), 128
+    begin = torch.from_numpy(begin_np)
+    Communicator(32)
+    Quantizer_for_all_procs(1, 32)
+    TimeRecorder(2, 1, enabled=True)
+    local, remote = graphgen.partition_edges(torch.from_numpy(src).cuda(), torch.from_numpy(dst).cuda(), begin, 0)
+    assert remote.shape[1] == 0
+    graph = build_graph(local, remote, begin, 0, 1, F, 32, False, device="cuda")
+    rng = np.random.default_rng(0)
+    X = rng.standard_normal((N, F)).astype(np.float32)
+    G = rng.standard_normal((N, F)).astype(np.float32)
+    x = torch.from_numpy(X).cuda().requires_grad_()
+    out = Aggregator.apply(graph, x, 0, 32, False, True)
+    out.backward(torch.from_numpy(G).cuda())
+    rp, c, v = global_csr(src, dst, N)
+    np.testing.assert_array_equal(out.detach().cpu().numpy(), oracle.spmm(rp, c, v, X))
+    rpt, ct, vt = global_csr(src, dst, N, transpose=True)
+    np.testing.assert_array_equal(x.grad.cpu().numpy(), oracle.spmm(rpt, ct, vt, G))
+    assert TimeRecorder.ctx.get_total_local_aggregate_time() > 0
