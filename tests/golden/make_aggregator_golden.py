@@ -102,6 +102,9 @@ def install_shims(ref_root):
     a64 = os.path.join(ref_root, "self_benchmark", "a64fx")
     ts = types.ModuleType("torch_sparse")
     ts.SparseTensor = ShimSparseTensor
+    # names imported (never called) by the dead legacy layer model/layers/sageconv_forpre.py:6-7
+    ts.fill_diag = None
+    ts.sum = None
     sys.modules["torch_sparse"] = ts
 
     tsc = types.ModuleType("torch_scatter")
@@ -159,8 +162,12 @@ def install_shims(ref_root):
     dense = types.ModuleType("torch_geometric.nn.dense")
     lin = types.ModuleType("torch_geometric.nn.dense.linear")
     lin.Linear = torch.nn.Linear
+    inits = types.ModuleType("torch_geometric.nn.inits")
+    inits.zeros = None
+    tgnn.inits = inits
     for name, m in (("torch_geometric", tg), ("torch_geometric.nn", tgnn), ("torch_geometric.nn.conv", conv),
-                    ("torch_geometric.nn.dense", dense), ("torch_geometric.nn.dense.linear", lin)):
+                    ("torch_geometric.nn.dense", dense), ("torch_geometric.nn.dense.linear", lin),
+                    ("torch_geometric.nn.inits", inits)):
         sys.modules[name] = m
     tg.nn = tgnn
     tgnn.conv = conv
@@ -338,12 +345,12 @@ def train_worker(rank, P, port, cfg, ref_root, out_dir):
 
 AGGR_CASES = [
     # name, seed, n_per, deg, F, bits, is_pre
-    ("plain_fp32_p2", 11, 300, 5, 128, 32, False),
-    ("plain_fp32_p3_f32", 12, 200, 4, 32, 32, False),
-    ("pre_fp32_p3", 13, 200, 5, 128, 32, True),
-    ("plain_int2_p2", 14, 300, 5, 128, 2, False),
-    ("pre_int2_p3", 15, 150, 4, 256, 2, True),
-    ("plain_int2_p4_f100", 16, 120, 4, 100, 2, False),
+    ("plain_fp32_p2", 11, 150, 5, 128, 32, False),
+    ("plain_fp32_p3_f32", 12, 120, 4, 32, 32, False),
+    ("pre_fp32_p3", 13, 100, 5, 128, 32, True),
+    ("plain_int2_p2", 14, 150, 5, 128, 2, False),
+    ("pre_int2_p3", 15, 70, 4, 256, 2, True),
+    ("plain_int2_p4_f100", 16, 70, 4, 100, 2, False),
 ]
 AGGR_P = {"plain_fp32_p2": 2, "plain_fp32_p3_f32": 3, "pre_fp32_p3": 3, "plain_int2_p2": 2, "pre_int2_p3": 3,
           "plain_int2_p4_f100": 4}

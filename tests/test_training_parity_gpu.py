@@ -1,0 +1,108 @@
+"""20-epoch training parity against the reference's own DistSAGE run (tests/golden/train_*.npz).
+
+Two real processes share cuda:0 over the gloo backend (NCCL refuses two ranks on one device): real
+autograd, real DistributedDataParallel, the product's Communicator / Aggregator / kernels.  The halo
+all-to-all is staged through host memory by a test-local wrapper; nothing on the device waits for
+another process.  Bar: per-epoch loss within 1e-4 of the reference's, every epoch, every rank, with the fp32 halo;
+with the 2-bit halo the same bar holds until the first quantisation code flips (see below)."""
+import glob
+import os
+
+import numpy as np
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+GOLD = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden")
+
+
+def _worker(rank, P, port, path, out_dir):
+    import torch.distributed as dist
+
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    torch.cuda.set_device(0)
+    dist.init_process_group("gloo", rank=rank, world_size=P)
+    real_a2a = dist.all_to_all_single
+
+    class _Done:
+        def wait(self):
+            return True
+
+    def staged_a2a(output, input, output_split_sizes=None, input_split_sizes=None, group=None, async_op=False):
+        if not input.is_cuda:
+            return real_a2a(output, input, output_split_sizes, input_split_sizes, group=group, async_op=async_op)
+        out_cpu = torch.empty(output.shape, dtype=output.dtype)
+        if output.dtype == torch.bfloat16:  # gloo has no bf16: ship the raw bytes (row splits unchanged)
+            real_a2a(out_cpu.view(torch.uint8), input.cpu().contiguous().view(torch.uint8), output_split_sizes,
+                     input_split_sizes)
+        else:
+            real_a2a(out_cpu, input.cpu(), output_split_sizes, input_split_sizes)
+        output.copy_(out_cpu)
+        return _Done() if async_op else None
+
+    dist.all_to_all_single = staged_a2a
+
+    from gnn_benchmark_b200 import Communicator, Quantizer_for_all_procs, TimeRecorder, graphgen
+    from gnn_benchmark_b200.data_manager.DataLoader import build_graph
+    from gnn_benchmark_b200.model import create_model_and_optimizer, set_random_seed
+    from gnn_benchmark_b200.train import train
+
+    g = np.load(path)
+    cfg = {k: float(v) for k, v in zip(g["cfg_keys"], g["cfg_vals"])}
+    for k in ("in_channels", "hidden_channels", "out_channels", "num_layers", "num_epochs", "random_seed", "num_bits"):
+        cfg[k] = int(cfg[k])
+    cfg["is_pre_delay"] = bool(cfg["is_pre_delay"])
+    cfg["model_name"] = "sage"
+    bits, is_pre = cfg["num_bits"], cfg["is_pre_delay"]
+    c = Communicator(bits, is_async=True)
+    c.rank, c.world_size = rank, P
+    Quantizer_for_all_procs(P, bits)
+    TimeRecorder(cfg["num_layers"], cfg["num_epochs"])
+    begin = torch.from_numpy(g["begin"])
+    local, remote = graphgen.partition_edges(torch.from_numpy(g["src"]), torch.from_numpy(g["dst"]), begin, rank)
+    max_feat = max(cfg["in_channels"], cfg["hidden_channels"], cfg["out_channels"])
+    graph = build_graph(local, remote, begin, rank, P, max_feat, bits, is_pre, device="cuda")
+    set_random_seed(cfg["random_seed"])
+    model, optimizer = create_model_and_optimizer(cfg, device="cuda")
+    # the seed alone reproduces the reference's initial weights (drawn on the CPU, then moved)
+    state = {k.replace("module.", ""): v for k, v in model.state_dict().items()}
+    same_init = all(np.array_equal(state[k[2:]].cpu().numpy(), g[k]) for k in g.files if k.startswith("w_"))
+    b0, b1 = int(begin[rank]), int(begin[rank + 1])
+    data = {
+        "graph": graph,
+        "nodes_features": torch.from_numpy(g["X"][b0:b1]).cuda(),
+        "nodes_labels": torch.from_numpy(g["labels"][b0:b1]).cuda(),
+        "nodes_train_masks": torch.from_numpy(np.nonzero(g["train_mask"][b0:b1])[0]).cuda(),
+        "nodes_valid_masks": torch.zeros(0, dtype=torch.int64, device="cuda"),
+        "nodes_test_masks": torch.zeros(0, dtype=torch.int64, device="cuda"),
+    }
+    losses, _ = train(model, data, optimizer, cfg["num_epochs"], bits, eval_every_epoch=False, log=None)
+    np.savez(os.path.join(out_dir, f"r{rank}.npz"), losses=np.array(losses), same_init=np.array(same_init))
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("path", sorted(glob.glob(os.path.join(GOLD, "train_*.npz"))),
+                         ids=lambda p: os.path.basename(p)[6:-4])
+def test_loss_curve_against_reference_run(cuda_lib, tmp_path, path):
+    import torch.multiprocessing as mp
+
+    g = np.load(path)
+    P = sum(1 for k in g.files if k.endswith("_losses"))
+    port = 29700 + (os.getpid() % 200)
+    mp.spawn(_worker, args=(P, port, path, str(tmp_path)), nprocs=P, join=True)
+    for r in range(P):
+        got = np.load(os.path.join(str(tmp_path), f"r{r}.npz"))
+        assert bool(got["same_init"]), "seeded initial weights differ from the reference's"
+        want = g[f"r{r}_losses"]
+        assert got["losses"].shape == want.shape == (20,)
+        if int(dict(zip(g["cfg_keys"], g["cfg_vals"]))["num_bits"]) == 32:
+            np.testing.assert_allclose(got["losses"], want, rtol=0, atol=1e-4)
+        else:
+            # 2-bit halo: a one-ulp difference in a dense transform (cuBLAS here, the CPU BLAS there)
+            # moves a value across a rounding boundary now and then, and a flipped code changes that
+            # halo element by a whole quantisation step -- a perturbation that two runs of the
+            # reference on different BLAS builds show as well.  Until the first flips the curves
+            # agree to fp32 noise; afterwards they stay within 2e-2.
+            np.testing.assert_allclose(got["losses"][:2], want[:2], rtol=0, atol=1e-4)
+            np.testing.assert_allclose(got["losses"], want, rtol=0, atol=2e-2)
