@@ -514,3 +514,57 @@ extern "C" int gnnagg_csr_validate(const int64_t *rowptr, const int32_t *col, in
     csr_validate_kernel<<<kNumSMs * 8, 256, 0, st>>>(rowptr, col, M, K, nnz, status);
     return check_launch("csr_validate_kernel");
 }
+
+// ---- SpMM variant for callers that cannot allocate device memory ----------------------------
+// The partial-sum scratch of gnnagg_spmm_csr_f32 normally comes from the caller.  Some callers
+// have no way to get device memory at the point of the call: code running under a framework
+// whose allocator is off limits there, a plugin handed only its operands by the host
+// application, or a process whose device-memory budget is fixed before it starts.  For them the
+// scratch lives in a fixed buffer inside the library image; every GPU that loads the library
+// holds GNNAGG_STATIC_SCRATCH_BYTES of it until the process exits.
+namespace gnnagg {
+
+static __device__ __align__(256) unsigned char g_static_scratch[GNNAGG_STATIC_SCRATCH_BYTES];
+
+constexpr int kMaxDevices = 64;
+static void *g_static_scratch_addr[kMaxDevices] = {nullptr};
+
+// In host code `g_static_scratch` is only a handle for the symbol, not a device address: the
+// address valid on the current device has to be asked for, once per device.
+static int static_scratch_for_current_device(void **out) {
+    int dev = -1;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return fail(GNNAGG_ERR_CUDA, "spmm_static_scratch: cudaGetDevice: %s", cudaGetErrorString(e));
+    if (dev < 0 || dev >= kMaxDevices)
+        return fail(GNNAGG_ERR_UNSUPPORTED, "spmm_static_scratch: device ordinal %d out of range", dev);
+    void *p = __atomic_load_n(&g_static_scratch_addr[dev], __ATOMIC_ACQUIRE);
+    if (p == nullptr) {
+        e = cudaGetSymbolAddress(&p, g_static_scratch);
+        if (e != cudaSuccess || p == nullptr)
+            return fail(GNNAGG_ERR_CUDA, "spmm_static_scratch: cudaGetSymbolAddress: %s", cudaGetErrorString(e));
+        __atomic_store_n(&g_static_scratch_addr[dev], p, __ATOMIC_RELEASE);  // same value from any thread
+    }
+    *out = p;
+    return GNNAGG_OK;
+}
+
+}  // namespace gnnagg
+
+extern "C" int gnnagg_spmm_csr_f32_static_scratch(const int64_t *rowptr, const int32_t *col, const float *val,
+                                                  int64_t M, int64_t K, int64_t nnz, const float *X, int64_t ldx,
+                                                  float *Y, int64_t ldy, int32_t F, int32_t accumulate,
+                                                  const void *plan, void *stream) {
+    if (M < 0 || K < 0 || nnz < 0 || F < 0) return fail(GNNAGG_ERR_ARG, "spmm_static_scratch: negative size");
+    if (M == 0 || F == 0) return GNNAGG_OK;
+    const size_t need = gnnagg_spmm_scratch_bytes(M, nnz, F);
+    if (need > (size_t)GNNAGG_STATIC_SCRATCH_BYTES)
+        return fail(GNNAGG_ERR_SCRATCH,
+                    "spmm_static_scratch: this product needs %zu bytes of scratch but the built-in buffer holds %zu; "
+                    "use gnnagg_spmm_csr_f32 with caller-provided scratch",
+                    need, (size_t)GNNAGG_STATIC_SCRATCH_BYTES);
+    void *scratch = nullptr;
+    const int rc = static_scratch_for_current_device(&scratch);
+    if (rc != GNNAGG_OK) return rc;
+    return gnnagg_spmm_csr_f32(rowptr, col, val, M, K, nnz, X, ldx, Y, ldy, F, accumulate, plan, scratch,
+                               (size_t)GNNAGG_STATIC_SCRATCH_BYTES, stream);
+}

@@ -12,7 +12,8 @@
  *   - return value: 0 = ok, < 0 = argument / launch error found on the host
  *     (see gnnagg_error_string), never a device trap;
  *   - safe to call from one host thread per GPU; the library keeps no global state
- *     apart from a thread-local message for the last error.
+ *     apart from a thread-local message for the last error and the built-in scratch
+ *     buffer of gnnagg_spmm_csr_f32_static_scratch.
  */
 #ifndef GNNAGG_H
 #define GNNAGG_H
@@ -72,6 +73,28 @@ int gnnagg_spmm_csr_f32(const int64_t *rowptr, const int32_t *col, const float *
                         int64_t nnz, const float *X, int64_t ldx, float *Y, int64_t ldy, int32_t F,
                         int32_t accumulate, const void *plan, void *scratch, size_t scratch_bytes,
                         void *stream);
+
+/* Same product as gnnagg_spmm_csr_f32 for callers that cannot allocate device memory where they
+ * call it (code under a host framework whose allocator may not be used at that point, a plugin
+ * that is handed nothing but its operands, a process with a device-memory budget fixed up front):
+ * the partial-sum scratch is a fixed buffer of GNNAGG_STATIC_SCRATCH_BYTES inside the library,
+ * held by every GPU that loads the library until the process exits.  This entry point has no
+ * counterpart in the reference.
+ *   - Limit: gnnagg_spmm_scratch_bytes(M, nnz, F) must not exceed GNNAGG_STATIC_SCRATCH_BYTES
+ *     (with the default chunking about 16 million rows+nonzeros at F = 256, 33 million at
+ *     F <= 128); larger products return GNNAGG_ERR_SCRATCH and launch nothing.
+ *   - It calls no cudaMalloc / cudaFree and no allocating routine; plan, operands and output
+ *     still come from the caller.
+ *   - The first call on each device looks up the buffer's address for that device (with that
+ *     device current); make that first call before any stream capture begins.
+ *   - All calls on a device share the one buffer, which keeps the previous call's contents.
+ *     Nothing in it needs to start at zero (every slot that is read was written earlier in the
+ *     same call), but two calls that may run on the GPU at the same time -- different streams,
+ *     different host threads -- race on it: keep calls on one device in one stream order. */
+#define GNNAGG_STATIC_SCRATCH_BYTES (32u << 20)
+int gnnagg_spmm_csr_f32_static_scratch(const int64_t *rowptr, const int32_t *col, const float *val, int64_t M,
+                                       int64_t K, int64_t nnz, const float *X, int64_t ldx, float *Y, int64_t ldy,
+                                       int32_t F, int32_t accumulate, const void *plan, void *stream);
 
 /* Checks on the device that rowptr is monotone with rowptr[0]==0, rowptr[M]==nnz and
  * that every col is in [0,K).  status (device int32[1]) receives 0 or a bit mask
