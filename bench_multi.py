@@ -1,0 +1,205 @@
+"""Multi-GPU leg of bench.py: distributed aggregation on N GPUs of one node (one process per GPU).
+
+Workload "aggregate_rmat22_per_gpu" (weak scaling): R-MAT with 2^22 vertices per GPU (scale
+22 + log2 N), edge factor 16, symmetrised, deduplicated, self-loops, vertex ids randomly relabelled,
+N contiguous partitions -- the reference's 1-D partitioning across MPI ranks.  Every rank generates
+the edge stream from the same seed and keeps the in-edges of its own vertex range, so the global
+graph is never held by one process.  One step = Aggregator forward + backward at F = 32, 128, 256:
+send-side gather, halo all-to-all over NCCL overlapped with the local SpMM, remote SpMM; backward the
+transposed chain with the deterministic scatter-add.  Adjacency values are GCN-normalised
+(d_dst^-1/2 d_src^-1/2; remote degrees fetched once with the halo exchange itself).
+"""
+import json
+import math
+import os
+import time
+from types import SimpleNamespace
+
+import torch
+import torch.distributed as dist
+
+
+def _partition_rmat(scale, edge_factor, seed, rank, world, device, chunk=1 << 25):
+    """In-edges (src, dst) of this rank's vertex block of the relabelled, symmetrised, deduplicated
+    R-MAT graph with self-loops; plus the partition table."""
+    from gnn_benchmark_b200 import graphgen
+
+    n = 1 << scale
+    begin = graphgen.contiguous_partitions(n, world)
+    b0, b1 = int(begin[rank]), int(begin[rank + 1])
+    perm = torch.randperm(n, generator=graphgen._gen(seed + 1, device), device=device) if world > 1 else None
+    g = graphgen._gen(seed, device)
+    a, b, c = 0.57, 0.19, 0.19
+    keys = []
+    n_edges = edge_factor << scale
+    for start in range(0, n_edges, chunk):
+        m = min(chunk, n_edges - start)
+        src = torch.zeros(m, dtype=torch.int64, device=device)
+        dst = torch.zeros(m, dtype=torch.int64, device=device)
+        for _ in range(scale):
+            r = torch.rand(m, generator=g, device=device)
+            src = (src << 1) | (r >= (a + b)).to(torch.int64)
+            dst = (dst << 1) | (((r >= a) & (r < a + b)) | (r >= a + b + c)).to(torch.int64)
+        keep = src != dst
+        src, dst = src[keep], dst[keep]
+        if perm is not None:
+            src, dst = perm[src], perm[dst]
+        for s_, d_ in ((src, dst), (dst, src)):  # both directions; keep what lands in my rows
+            mine = (d_ >= b0) & (d_ < b1)
+            keys.append(torch.unique(d_[mine] * n + s_[mine]))
+        del src, dst, keep
+    diag = torch.arange(b0, b1, dtype=torch.int64, device=device)
+    keys.append(diag * n + diag)
+    key = torch.unique(torch.cat(keys))
+    del keys
+    return key % n, key // n, begin  # src, dst (global ids), partition table
+
+
+def _gcn_values(graph, comm, world):
+    """d_dst^-1/2 * d_src^-1/2 on the local and remote matrices; the remote sources' degrees come
+    through one fp32 halo exchange of a single column."""
+    import torch
+
+    from gnn_benchmark_b200.aggregator import gather_rows
+
+    n = graph.local_adj_t.sparse_size(0)
+    dev = graph.local_adj_t.device
+    rp_l, col_l, _ = graph.local_adj_t.csr()
+    deg = (rp_l[1:] - rp_l[:-1]).to(torch.float32)
+    if world > 1:
+        rp_r, col_r, _ = graph.remote_adj_t.csr()
+        deg = deg + (rp_r[1:] - rp_r[:-1]).to(torch.float32)
+    dinv = deg.clamp(min=1).rsqrt()
+    rows_l = torch.repeat_interleave(torch.arange(n, device=dev), rp_l[1:] - rp_l[:-1])
+    graph.local_adj_t.set_value_(dinv[rows_l] * dinv[col_l.to(torch.int64)])
+    if world > 1:
+        graph.comm_buf.resize_buffer(graph.comm_splits, 4, 32)
+        send = graph.comm_buf.send_buf
+        x = dinv.view(-1, 1).expand(n, 4).contiguous()
+        gather_rows(x, graph.idx_nodes_send_to_others_i32, send)
+        h = comm.comm_with_fp32(graph.comm_splits, graph.comm_buf, "forward")
+        if h is not None:
+            h.wait()
+        torch.cuda.synchronize()
+        dinv_halo = graph.comm_buf.recv_buf[:, 0].clone()
+        rows_r = torch.repeat_interleave(torch.arange(n, device=dev), rp_r[1:] - rp_r[:-1])
+        graph.remote_adj_t.set_value_(dinv[rows_r] * dinv_halo[col_r.to(torch.int64)])
+
+
+def run_multi_gpu(args):
+    import bench
+    from gnn_benchmark_b200 import Communicator, Quantizer_for_all_procs, TimeRecorder, graphgen
+    from gnn_benchmark_b200.aggregator import Aggregator
+    from gnn_benchmark_b200.data_manager.DataLoader import build_graph
+
+    num_bits = int(os.environ.get("GNNAGG_BENCH_BITS", "32"))
+    is_pre = os.environ.get("GNNAGG_BENCH_PRE", "0") == "1"
+    comm = Communicator(num_bits, is_async=True)
+    rank, world = comm.init_dist_group("nccl")
+    device = torch.device("cuda", torch.cuda.current_device())
+    Quantizer_for_all_procs(world, num_bits)
+    TimeRecorder(1, 1, enabled=False)
+    widths = bench.WIDTHS
+    scale = bench.SCALE + int(math.ceil(math.log2(world)))
+
+    t0 = time.time()
+    src, dst, begin = _partition_rmat(scale, bench.EDGE_FACTOR, bench.SEED, rank, world, device)
+    local, remote = graphgen.partition_edges(src, dst, begin, rank)
+    del src, dst
+    graph = build_graph(local, remote, begin, rank, world, max(widths), num_bits, is_pre, device=device)
+    del local, remote
+    torch.cuda.empty_cache()
+    if not is_pre:
+        _gcn_values(graph, comm, world)
+    n = graph.local_adj_t.sparse_size(0)
+    if is_pre:
+        nnz = graph.local_adj_t.nnz() + graph.adj_t_pre_post_aggr_from.nnz() + graph.adj_t_pre_post_aggr_to.nnz()
+    else:
+        nnz = graph.local_adj_t.nnz() + (graph.remote_adj_t.nnz() if world > 1 else 0)
+    # warm the cached CSC twins and launch plans outside the timed region
+    setup_s = time.time() - t0
+
+    g = torch.Generator(device=device).manual_seed(bench.SEED + rank)
+    X = {F: torch.randn(n, F, device=device, generator=g) for F in widths}
+    G = {F: torch.randn(n, F, device=device, generator=g) for F in widths}
+
+    def step():
+        for F in widths:
+            ctx = SimpleNamespace()
+            Aggregator.forward(ctx, graph, X[F], 0, num_bits, is_pre, True)
+            Aggregator.backward(ctx, G[F])
+
+    warmup = max(args.warmup, 3)
+    for _ in range(warmup):
+        step()
+    torch.cuda.synchronize()
+    dist.barrier()
+    torch.cuda.synchronize()
+    with bench.ClockSampler(torch.cuda.current_device()) as clk:
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(args.steps):
+            step()
+        e1.record()
+        torch.cuda.synchronize()
+        dist.barrier()
+        torch.cuda.synchronize()
+    t_local = e0.elapsed_time(e1) / 1e3 / args.steps
+    stats = torch.tensor([t_local, float(nnz), float(sum(graph.comm_splits.send_splits)),
+                          float(sum(graph.comm_splits.recv_splits))], dtype=torch.float64, device=device)
+    t_max = stats[0:1].clone()
+    dist.all_reduce(t_max, op=dist.ReduceOp.MAX)
+    tot = stats.clone()
+    dist.all_reduce(tot, op=dist.ReduceOp.SUM)
+    t_step = float(t_max.item())
+    edges_per_step = 2 * len(widths) * float(tot[1].item())
+
+    # the exchange alone (not overlapped), widest feature, forward direction: NVLink fraction
+    nv = None
+    if world > 1 and num_bits == 32:
+        F = max(widths)
+        graph.comm_buf.resize_buffer(graph.comm_splits, F, 32)
+        ts = []
+        for _ in range(5):
+            dist.barrier()
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            h = comm.comm_with_fp32(graph.comm_splits, graph.comm_buf, "forward")
+            if h is not None:
+                h.wait()
+            b.record()
+            torch.cuda.synchronize()
+            ts.append(a.elapsed_time(b) / 1e3)
+        t_x = torch.tensor([sorted(ts)[len(ts) // 2]], dtype=torch.float64, device=device)
+        dist.all_reduce(t_x, op=dist.ReduceOp.MAX)
+        sent = max(sum(graph.comm_splits.send_splits), sum(graph.comm_splits.recv_splits)) * F * 4
+        sent_t = torch.tensor([float(sent)], dtype=torch.float64, device=device)
+        dist.all_reduce(sent_t, op=dist.ReduceOp.MAX)
+        gbs = float(sent_t.item()) / float(t_x.item()) / 1e9
+        nv = {"exchange_ms": float(t_x.item()) * 1e3, "bytes_per_rank_per_direction": int(sent_t.item()),
+              "achieved_gbs": gbs, "frac_of_measured_770": gbs / 770.0, "frac_of_nominal_900": gbs / 900.0, "F": F}
+
+    clocks = clk.summary()
+    if rank == 0:
+        peak, peak_kind = bench.measured_peak_gbs()
+        cfg = bench.workload_config(world)
+        cfg.update({"rows_per_gpu": n, "nnz_total": int(tot[1].item()), "partitions": world,
+                    "halo_rows_sent_total": int(tot[2].item()), "halo": f"{num_bits}-bit" + (" pre/post" if is_pre else ""),
+                    "setup_s": round(setup_s, 1), "parallelism": f"1-D vertex partition x{world}"})
+        by = sum(bench.spmm_algorithmic_bytes(n, nnz, F) for F in widths) * 2
+        line = {
+            "metric": "aggregated_edges_per_s", "value": edges_per_step / t_step, "unit": "edges/s", "n_gpus": world,
+            "steps": args.steps, "warmup": warmup, "ms_per_step": t_step * 1e3, "higher_is_better": True,
+            "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic", "config": cfg,
+            "clocks": clocks,
+            "e2e": None,
+            "gpu_launches": args.steps * len(widths) * (2 * 2 * (1 if world == 1 else 2) + (1 if world > 1 else 0)),
+            "roofline": {"bound": "hbm", "kernel": "spmm_chunk_kernel (all SpMM calls of a step, rank 0)",
+                         "achieved": by / t_step / 1e9, "peak": peak, "unit": "GB/s", "frac": by / t_step / 1e9 / peak,
+                         "peak_kind": peak_kind + " copy bandwidth", "traffic": None,
+                         "note": "whole step including the exchange; SpMM algorithmic bytes only"},
+            "nvlink": nv, "cpu_baseline": None,
+        }
+        print(json.dumps(line), flush=True)
+    dist.barrier()
+    dist.destroy_process_group()

@@ -31,7 +31,21 @@
 
 namespace gnnagg {
 
-constexpr int kWarpsPerBlock = 4;
+// Launch shape, measured on B200 with the R-MAT scale-22 benchmark matrix: 64-thread CTAs; kernels
+// with one vector per lane (F <= 128) run best capped at 85 registers (24 warps per SM resident),
+// the wider ones (two to four vectors per lane, more gathers in flight per lane) uncapped.
+#ifndef GNNAGG_SPMM_WARPS
+#define GNNAGG_SPMM_WARPS 2
+#endif
+#ifndef GNNAGG_SPMM_MINBLOCKS_NARROW
+#define GNNAGG_SPMM_MINBLOCKS_NARROW 12
+#endif
+#ifndef GNNAGG_SPMM_MINBLOCKS_WIDE
+#define GNNAGG_SPMM_MINBLOCKS_WIDE 8
+#endif
+constexpr int kWarpsPerBlock = GNNAGG_SPMM_WARPS;
+// register cap per thread = 65536 / (threads per CTA * min CTAs per SM)
+constexpr int min_blocks_per_sm(int nv) { return nv == 1 ? GNNAGG_SPMM_MINBLOCKS_NARROW : GNNAGG_SPMM_MINBLOCKS_WIDE; }
 constexpr uint32_t kPlanMagic = 0x4d50534eu;  // "NSPM"
 constexpr int kDefaultItems = 512;
 
@@ -163,11 +177,13 @@ __device__ __forceinline__ void vstore_plain<1>(float *p, const Vec<1> &a) {
 }
 
 // G lanes per feature row, NV vectors of VW floats per lane, U gather instructions in flight.
-template <int G, int NV, int VW, int U>
-__global__ void __launch_bounds__(kWarpsPerBlock * 32)
+// ACC: accumulate onto the old output.  FULL: the row is exactly G*NV vectors wide, so no lane
+// holds a vector past the row's end and the per-vector predicates vanish.
+template <int G, int NV, int VW, int U, bool ACC, bool FULL>
+__global__ void __launch_bounds__(kWarpsPerBlock * 32, min_blocks_per_sm(NV))
     spmm_chunk_kernel(const int64_t *__restrict__ rowptr, const int32_t *__restrict__ col,
                       const float *__restrict__ val, int64_t M, const float *__restrict__ X, int64_t ldx,
-                      float *__restrict__ Y, int64_t ldy, int FV, int accumulate,
+                      float *__restrict__ Y, int64_t ldy, int FV,
                       const int64_t *__restrict__ chunk_nz, const int32_t *__restrict__ chunk_row, int64_t nchunks,
                       float *__restrict__ carry, int carry_ld) {
     constexpr int S = 32 / G;  // nonzeros fetched per warp-wide gather instruction
@@ -186,10 +202,10 @@ __global__ void __launch_bounds__(kWarpsPerBlock * 32)
 #pragma unroll
     for (int k = 0; k < NV; ++k) {
         voff[k] = (gl + k * G) * VW;
-        vok[k] = (gl + k * G) < FV;
+        vok[k] = FULL || (gl + k * G) < FV;
     }
 
-    const bool acc_mode = accumulate != 0;
+    constexpr bool acc_mode = ACC;
     Vec<VW> acc[NV];    // running sum of the current row (lane group 0 starts from the old Y when accumulating)
     Vec<VW> ynext[NV];  // accumulate mode: old Y of the row after the current one, fetched one row ahead
 
@@ -271,9 +287,34 @@ __global__ void __launch_bounds__(kWarpsPerBlock * 32)
         }
         const int in_batch = (n - eb) < 32 ? (n - eb) : 32;
         const int nsteps = (in_batch + S - 1) / S;
+        const int full_steps = in_batch / S;  // steps in which every lane group holds a nonzero
         for (int s0 = 0; s0 < nsteps; s0 += U) {
             Vec<VW> xr[U][NV];
             float av[U];
+            if (s0 + U <= full_steps && next_end >= eb + (s0 + U) * S) {
+                // Fast path: the next U*S nonzeros all belong to the current row -- issue the U
+                // gathers back to back, then the U FMA groups, with nothing else in between.
+#pragma unroll
+                for (int u = 0; u < U; ++u) {
+                    const int j = (s0 + u) * S + grp;
+                    const int cc = __shfl_sync(kFullMask, my_col, j);
+                    av[u] = __shfl_sync(kFullMask, my_val, j);
+                    const float *xp = X + (int64_t)cc * ldx;
+#pragma unroll
+                    for (int k = 0; k < NV; ++k)
+                        if (vok[k]) xr[u][k] = vload<VW>(xp + voff[k]);
+                }
+#pragma unroll
+                for (int u = 0; u < U; ++u)
+#pragma unroll
+                    for (int k = 0; k < NV; ++k)
+                        if (vok[k]) {
+#pragma unroll
+                            for (int i = 0; i < VW; ++i) acc[k].v[i] = fmaf(av[u], xr[u][k].v[i], acc[k].v[i]);
+                        }
+                continue;
+            }
+            // General path: a row ends inside these steps, or the batch runs out.
             bool ok[U];
 #pragma unroll
             for (int u = 0; u < U; ++u) {
@@ -283,14 +324,8 @@ __global__ void __launch_bounds__(kWarpsPerBlock * 32)
                 ok[u] = j < in_batch;
                 const float *xp = X + (int64_t)cc * ldx;
 #pragma unroll
-                for (int k = 0; k < NV; ++k) {
-                    if (ok[u] && vok[k]) {
-                        xr[u][k] = vload<VW>(xp + voff[k]);
-                    } else {
-#pragma unroll
-                        for (int i = 0; i < VW; ++i) xr[u][k].v[i] = 0.f;
-                    }
-                }
+                for (int k = 0; k < NV; ++k)
+                    if (ok[u] && vok[k]) xr[u][k] = vload<VW>(xp + voff[k]);
             }
 #pragma unroll
             for (int u = 0; u < U; ++u) {
@@ -302,9 +337,11 @@ __global__ void __launch_bounds__(kWarpsPerBlock * 32)
                         if (pending && eg < next_end) {
 #pragma unroll
                             for (int k = 0; k < NV; ++k)
+                                if (vok[k]) {
 #pragma unroll
-                                for (int i = 0; i < VW; ++i)
-                                    acc[k].v[i] = fmaf(av[u], xr[u][k].v[i], acc[k].v[i]);
+                                    for (int i = 0; i < VW; ++i)
+                                        acc[k].v[i] = fmaf(av[u], xr[u][k].v[i], acc[k].v[i]);
+                                }
                             pending = false;
                         }
                         flush_row();
@@ -313,8 +350,10 @@ __global__ void __launch_bounds__(kWarpsPerBlock * 32)
                     if (pending) {
 #pragma unroll
                         for (int k = 0; k < NV; ++k)
+                            if (vok[k]) {
 #pragma unroll
-                            for (int i = 0; i < VW; ++i) acc[k].v[i] = fmaf(av[u], xr[u][k].v[i], acc[k].v[i]);
+                                for (int i = 0; i < VW; ++i) acc[k].v[i] = fmaf(av[u], xr[u][k].v[i], acc[k].v[i]);
+                            }
                     }
                 }
             }
@@ -390,8 +429,16 @@ static void launch_chunks(const int64_t *rowptr, const int32_t *col, const float
                           int64_t ldx, float *Y, int64_t ldy, int FV, int accumulate, const int64_t *chunk_nz,
                           const int32_t *chunk_row, int64_t nchunks, float *carry, int carry_ld, cudaStream_t st) {
     const unsigned blocks = (unsigned)div_up(nchunks, kWarpsPerBlock);
-    spmm_chunk_kernel<G, NV, VW, U><<<blocks, kWarpsPerBlock * 32, 0, st>>>(
-        rowptr, col, val, M, X, ldx, Y, ldy, FV, accumulate, chunk_nz, chunk_row, nchunks, carry, carry_ld);
+    const bool full = (FV == G * NV) && VW == 4;
+#define GNNAGG_GO(ACC, FULL)                                                                                  \
+    spmm_chunk_kernel<G, NV, VW, U, ACC, FULL><<<blocks, kWarpsPerBlock * 32, 0, st>>>(                       \
+        rowptr, col, val, M, X, ldx, Y, ldy, FV, chunk_nz, chunk_row, nchunks, carry, carry_ld)
+    if (VW == 4 && full) {
+        if (accumulate) GNNAGG_GO(true, (VW == 4)); else GNNAGG_GO(false, (VW == 4));
+    } else {
+        if (accumulate) GNNAGG_GO(true, false); else GNNAGG_GO(false, false);
+    }
+#undef GNNAGG_GO
 }
 
 template <int VW>
