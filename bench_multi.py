@@ -86,6 +86,54 @@ def _gcn_values(graph, comm, world):
         graph.remote_adj_t.set_value_(dinv[rows_r] * dinv_halo[col_r.to(torch.int64)])
 
 
+def _run_e2e(args, graph, widths, num_bits, is_pre, n, nnz_total, device):
+    """The same step through Aggregator with this rank's features and output gradients in pinned
+    HOST memory: per call copy the operand host->device, run, copy the result device->host."""
+    from gnn_benchmark_b200.aggregator import Aggregator
+
+    Fmax = max(widths)
+    host_in = torch.empty(n, Fmax, pin_memory=True).normal_(generator=torch.Generator().manual_seed(1))
+    host_out = torch.empty(n, Fmax, pin_memory=True)
+    dev_in = torch.empty(n * Fmax, device=device)
+    moved = 0
+
+    def step():
+        nonlocal moved
+        moved = 0
+        for F in widths:
+            hin = host_in.view(-1)[: n * F].view(n, F)
+            hout = host_out.view(-1)[: n * F].view(n, F)
+            x = dev_in[: n * F].view(n, F)
+            ctx = SimpleNamespace()
+            x.copy_(hin, non_blocking=True)
+            out = Aggregator.forward(ctx, graph, x, 0, num_bits, is_pre, True)
+            hout.copy_(out, non_blocking=True)
+            x.copy_(hin, non_blocking=True)
+            grad = Aggregator.backward(ctx, x)[1]
+            hout.copy_(grad, non_blocking=True)
+            moved += 2 * n * F * 4
+
+    step()
+    torch.cuda.synchronize()
+    dist.barrier()
+    steps = max(1, min(args.steps, 3))
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(steps):
+        step()
+    e1.record()
+    torch.cuda.synchronize()
+    dist.barrier()
+    t = torch.tensor([e0.elapsed_time(e1) / 1e3 / steps], dtype=torch.float64, device=device)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    b = torch.tensor([float(moved)], dtype=torch.float64, device=device)
+    dist.all_reduce(b, op=dist.ReduceOp.SUM)
+    del host_in, host_out, dev_in
+    return {"value": 2 * len(widths) * nnz_total / float(t.item()), "unit": "edges/s",
+            "h2d_bytes_per_step": int(b.item()), "d2h_bytes_per_step": int(b.item()),
+            "ms_per_step": float(t.item()) * 1e3, "steps": steps}
+
+
 def run_multi_gpu(args):
     import bench
     from gnn_benchmark_b200 import Communicator, Quantizer_for_all_procs, TimeRecorder, graphgen
@@ -105,6 +153,7 @@ def run_multi_gpu(args):
     t0 = time.time()
     src, dst, begin = _partition_rmat(scale, bench.EDGE_FACTOR, bench.SEED, rank, world, device)
     local, remote = graphgen.partition_edges(src, dst, begin, rank)
+    nnz = int(local.shape[1] + remote.shape[1])  # edges aggregated by this rank per pass
     del src, dst
     graph = build_graph(local, remote, begin, rank, world, max(widths), num_bits, is_pre, device=device)
     del local, remote
@@ -112,11 +161,7 @@ def run_multi_gpu(args):
     if not is_pre:
         _gcn_values(graph, comm, world)
     n = graph.local_adj_t.sparse_size(0)
-    if is_pre:
-        nnz = graph.local_adj_t.nnz() + graph.adj_t_pre_post_aggr_from.nnz() + graph.adj_t_pre_post_aggr_to.nnz()
-    else:
-        nnz = graph.local_adj_t.nnz() + (graph.remote_adj_t.nnz() if world > 1 else 0)
-    # warm the cached CSC twins and launch plans outside the timed region
+    torch.cuda.synchronize()
     setup_s = time.time() - t0
 
     g = torch.Generator(device=device).manual_seed(bench.SEED + rank)
@@ -179,6 +224,7 @@ def run_multi_gpu(args):
         nv = {"exchange_ms": float(t_x.item()) * 1e3, "bytes_per_rank_per_direction": int(sent_t.item()),
               "achieved_gbs": gbs, "frac_of_measured_770": gbs / 770.0, "frac_of_nominal_900": gbs / 900.0, "F": F}
 
+    e2e = _run_e2e(args, graph, widths, num_bits, is_pre, n, float(tot[1].item()), device)
     clocks = clk.summary()
     if rank == 0:
         peak, peak_kind = bench.measured_peak_gbs()
@@ -192,7 +238,7 @@ def run_multi_gpu(args):
             "steps": args.steps, "warmup": warmup, "ms_per_step": t_step * 1e3, "higher_is_better": True,
             "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic", "config": cfg,
             "clocks": clocks,
-            "e2e": None,
+            "e2e": e2e,
             "gpu_launches": args.steps * len(widths) * (2 * 2 * (1 if world == 1 else 2) + (1 if world > 1 else 0)),
             "roofline": {"bound": "hbm", "kernel": "spmm_chunk_kernel (all SpMM calls of a step, rank 0)",
                          "achieved": by / t_step / 1e9, "peak": peak, "unit": "GB/s", "frac": by / t_step / 1e9 / peak,
