@@ -19,42 +19,6 @@ import torch
 import torch.distributed as dist
 
 
-def _partition_rmat(scale, edge_factor, seed, rank, world, device, chunk=1 << 25):
-    """In-edges (src, dst) of this rank's vertex block of the relabelled, symmetrised, deduplicated
-    R-MAT graph with self-loops; plus the partition table."""
-    from gnn_benchmark_b200 import graphgen
-
-    n = 1 << scale
-    begin = graphgen.contiguous_partitions(n, world)
-    b0, b1 = int(begin[rank]), int(begin[rank + 1])
-    perm = torch.randperm(n, generator=graphgen._gen(seed + 1, device), device=device) if world > 1 else None
-    g = graphgen._gen(seed, device)
-    a, b, c = 0.57, 0.19, 0.19
-    keys = []
-    n_edges = edge_factor << scale
-    for start in range(0, n_edges, chunk):
-        m = min(chunk, n_edges - start)
-        src = torch.zeros(m, dtype=torch.int64, device=device)
-        dst = torch.zeros(m, dtype=torch.int64, device=device)
-        for _ in range(scale):
-            r = torch.rand(m, generator=g, device=device)
-            src = (src << 1) | (r >= (a + b)).to(torch.int64)
-            dst = (dst << 1) | (((r >= a) & (r < a + b)) | (r >= a + b + c)).to(torch.int64)
-        keep = src != dst
-        src, dst = src[keep], dst[keep]
-        if perm is not None:
-            src, dst = perm[src], perm[dst]
-        for s_, d_ in ((src, dst), (dst, src)):  # both directions; keep what lands in my rows
-            mine = (d_ >= b0) & (d_ < b1)
-            keys.append(torch.unique(d_[mine] * n + s_[mine]))
-        del src, dst, keep
-    diag = torch.arange(b0, b1, dtype=torch.int64, device=device)
-    keys.append(diag * n + diag)
-    key = torch.unique(torch.cat(keys))
-    del keys
-    return key % n, key // n, begin  # src, dst (global ids), partition table
-
-
 def _gcn_values(graph, comm, world):
     """d_dst^-1/2 * d_src^-1/2 on the local and remote matrices; the remote sources' degrees come
     through one fp32 halo exchange of a single column."""
@@ -151,7 +115,8 @@ def run_multi_gpu(args):
     scale = bench.SCALE + int(math.ceil(math.log2(world)))
 
     t0 = time.time()
-    src, dst, begin = _partition_rmat(scale, bench.EDGE_FACTOR, bench.SEED, rank, world, device)
+    src, dst, begin = graphgen.partitioned_in_edges("rmat", 1 << scale, bench.EDGE_FACTOR << scale, bench.SEED, rank, world,
+                                                    device, relabel=world > 1, scale=scale)
     local, remote = graphgen.partition_edges(src, dst, begin, rank)
     nnz = int(local.shape[1] + remote.shape[1])  # edges aggregated by this rank per pass
     del src, dst

@@ -55,7 +55,10 @@ class Communicator(object):
             if backend == "nccl":
                 local_rank = int(os.environ.get("LOCAL_RANK", 0))
                 torch.cuda.set_device(local_rank)
-                dist.init_process_group(backend="nccl", device_id=torch.device("cuda", local_rank))
+                # the exchange runs on a high-priority stream: its few large CTAs must get onto the SMs
+                # while the local SpMM's many small CTAs keep arriving, or the overlap is lost
+                opts = dist.ProcessGroupNCCL.Options(is_high_priority_stream=True)
+                dist.init_process_group(backend="nccl", device_id=torch.device("cuda", local_rank), pg_options=opts)
             else:
                 dist.init_process_group(backend=backend)
         self.world_size = dist.get_world_size()

@@ -21,7 +21,10 @@ constexpr int kCodecWarps = 4;
 constexpr int kMaxSeg = 1024;  // peer segments per call
 
 // Packed-row prefix of the segments into shared memory: pbase[p] = sum_{q<p} ceil(n_q/epb).
-__device__ __forceinline__ void build_packed_prefix(const int32_t *__restrict__ seg, int P, int epb, int *pbase) {
+__device__ __forceinline__ void build_packed_prefix(const int32_t *__restrict__ seg, int P, int epb, int *pbase,
+                                                    int *sseg = nullptr) {
+    if (sseg != nullptr)
+        for (int p = threadIdx.x; p <= P; p += blockDim.x) sseg[p] = seg[p];
     if (threadIdx.x < 32) {
         const int lane = threadIdx.x;
         int running = 0;
@@ -58,21 +61,22 @@ __device__ __forceinline__ int find_segment(const int *pbase, int P, int R) {
     return lo;
 }
 
+// Warp min / max of non-NaN floats with one redux.sync each: floats are mapped to integers of the
+// same order (negative values have their magnitude bits flipped) and mapped back.  The lane-local
+// inputs are never NaN here (they start from +-inf and fminf / fmaxf skip NaNs); the sign of a zero
+// result is settled separately by fix_extreme.
+__device__ __forceinline__ int float_to_ordered(float v) {
+    const int i = __float_as_int(v);
+    return i ^ ((i >> 31) & 0x7fffffff);
+}
+__device__ __forceinline__ float ordered_to_float(int i) { return __int_as_float(i ^ ((i >> 31) & 0x7fffffff)); }
 __device__ __forceinline__ float warp_min(float v) {
-#pragma unroll
-    for (int off = 16; off > 0; off >>= 1) v = fminf(v, __shfl_xor_sync(kFullMask, v, off));
-    return v;
+    return ordered_to_float(__reduce_min_sync(kFullMask, float_to_ordered(v)));
 }
 __device__ __forceinline__ float warp_max(float v) {
-#pragma unroll
-    for (int off = 16; off > 0; off >>= 1) v = fmaxf(v, __shfl_xor_sync(kFullMask, v, off));
-    return v;
+    return ordered_to_float(__reduce_max_sync(kFullMask, float_to_ordered(v)));
 }
-__device__ __forceinline__ int warp_min_int(int v) {
-#pragma unroll
-    for (int off = 16; off > 0; off >>= 1) v = min(v, __shfl_xor_sync(kFullMask, v, off));
-    return v;
-}
+__device__ __forceinline__ int warp_min_int(int v) { return __reduce_min_sync(kFullMask, v); }
 
 // The reference scans a row from column 0 and replaces min/max only on a strict compare
 // (quantization_arm.cpp:93-104): a NaN never replaces, a NaN in column 0 sticks, and of
@@ -88,6 +92,33 @@ __device__ __forceinline__ float fix_extreme(float m, float x0, int first_zero_k
     return m;
 }
 
+// Per-row constants of the encoder.  The code is round-half-even(fl((x - zp) / scale)) with a true
+// IEEE division.  Dividing costs an order of magnitude more than the rest of the kernel, so the
+// quotient is first estimated as (x - zp) * fl(1/scale) (within 2 ulp of the true quotient when
+// scale is a normal number well inside the exponent range); only when that estimate lies within 8
+// ulp of a rounding boundary k + 0.5 -- where the two could round to different integers -- is the
+// exact division done.  Both paths therefore give the integer the exact division gives.
+struct RowCodec {
+    float zp, scale, rinv;
+    bool fast;  // scale in [2^-100, 2^100]: its reciprocal is a normal number with full precision
+};
+__device__ __forceinline__ RowCodec make_row_codec(float zp, float scale) {
+    RowCodec r;
+    r.zp = zp, r.scale = scale;
+    const float a = fabsf(scale);
+    r.fast = (a >= 7.888609e-31f) && (a <= 1.2676506e30f);
+    r.rinv = r.fast ? __frcp_rn(scale) : 0.f;
+    return r;
+}
+__device__ __forceinline__ uint32_t encode(float x, const RowCodec &rc, bool signed_cvt) {
+    const float d = __fsub_rn(x, rc.zp);
+    float q = __fmul_rn(d, rc.rinv);
+    const float k = rintf(q);
+    const float to_boundary = 0.5f - fabsf(__fsub_rn(q, k));
+    const float eps = fmaxf(fabsf(q), 1.0f) * 9.5367431640625e-07f;  // 2^-20 relative: 8 ulp
+    if (!rc.fast || !(to_boundary >= eps)) q = __fdiv_rn(d, rc.scale);  // also catches NaN / inf
+    return signed_cvt ? (uint32_t)__float2int_rn(q) : __float2uint_rn(q);
+}
 __device__ __forceinline__ uint32_t encode(float x, float zp, float scale, bool signed_cvt) {
     const float q = __fdiv_rn(__fsub_rn(x, zp), scale);
     // own parameters: unsigned saturating convert (SVE FCVTZU after FRINTN);
@@ -100,94 +131,138 @@ __device__ __forceinline__ uint32_t bf16_bits(float v) {
     return (uint32_t)__bfloat16_as_ushort(__float2bfloat16_rn(v));
 }
 
-// ---- fast path: F % 4 == 0, F <= 128*NV, 16-byte aligned rows ------------------------
-template <int BITS, int NV>
-__global__ void __launch_bounds__(kCodecWarps * 32)
+// ---- fast path: F % 4 == 0, F <= 512, 16-byte aligned rows ------------------------------
+// GQ lanes own one packed row (GQ = 8, 16 or 32 by width), so a warp works on 32/GQ packed rows at a
+// time and narrow rows do not leave lanes idle; NV float4 per lane and input row (NV > 1 only with
+// GQ = 32).  Reductions and broadcasts are scoped to the group's lane mask.
+template <int BITS, int NV, int GQ>
+__global__ void __launch_bounds__(kCodecWarps * 32, (NV == 1 ? 8 : (NV == 2 ? 5 : 3)))
     quant_pack_vec_kernel(const float *__restrict__ X, int64_t ldx, const int32_t *__restrict__ idx, int F,
                           const int32_t *__restrict__ seg, int P, int params_given, float *__restrict__ params,
                           uint32_t *__restrict__ params_bf16, uint8_t *__restrict__ codes) {
     constexpr int EPB = 8 / BITS;
+    constexpr int NG = 32 / GQ;
     constexpr float LEVELS = (float)((1 << BITS) - 1);
     __shared__ int pbase[kMaxSeg + 1];
-    build_packed_prefix(seg, P, EPB, pbase);
+    __shared__ int sseg[kMaxSeg + 1];
+    build_packed_prefix(seg, P, EPB, pbase, sseg);
     const int lane = threadIdx.x & 31;
-    const int64_t R = (int64_t)blockIdx.x * kCodecWarps + (threadIdx.x >> 5);
-    if (R >= pbase[P]) return;
-    const int p = find_segment(pbase, P, (int)R);
-    const int i0 = seg[p] + ((int)R - pbase[p]) * EPB;
-    const int cnt = min(EPB, seg[p + 1] - i0);
+    const int gl = lane % GQ, grp = lane / GQ;
+    const unsigned gmask = GQ == 32 ? kFullMask : (((1u << GQ) - 1u) << (grp * GQ));
+    const int lead = grp * GQ;  // the group's lane that holds column 0
     const int FV = F >> 2;
+    const int64_t total = pbase[P];
+    const int64_t stride = (int64_t)gridDim.x * kCodecWarps * NG;
+    for (int64_t R = ((int64_t)blockIdx.x * kCodecWarps + (threadIdx.x >> 5)) * NG + grp; R < total; R += stride) {
+        const int p = find_segment(pbase, P, (int)R);
+        const int i0 = sseg[p] + ((int)R - pbase[p]) * EPB;
+        const int cnt = min(EPB, sseg[p + 1] - i0);
 
-    float4 xv[EPB][NV];
-    float zp[EPB], sc[EPB];
+        float4 xv[EPB][NV];
+        const float *xp[EPB];
 #pragma unroll
-    for (int t = 0; t < EPB; ++t) {
-        zp[t] = 0.f;
-        sc[t] = 1.f;
-        if (t < cnt) {
-            const int64_t src = idx ? (int64_t)idx[i0 + t] : (int64_t)(i0 + t);
-            const float *xp = X + src * ldx;
-            float mn = __int_as_float(0x7f800000), mx = __int_as_float(0xff800000);  // +inf, -inf
-            int zkey = INT_MAX;
+        for (int t = 0; t < EPB; ++t) {  // all loads of the group first: EPB*NV independent 16-byte loads per lane
+            xp[t] = X;
+            if (t < cnt) xp[t] = X + (idx ? (int64_t)idx[i0 + t] : (int64_t)(i0 + t)) * ldx;
+        }
+#pragma unroll
+        for (int t = 0; t < EPB; ++t)
 #pragma unroll
             for (int k = 0; k < NV; ++k) {
-                const int vi = lane + 32 * k;
-                if (vi < FV) {
-                    const float4 v = __ldcs(reinterpret_cast<const float4 *>(xp) + vi);
-                    xv[t][k] = v;
-                    const float e[4] = {v.x, v.y, v.z, v.w};
+                const int vi = gl + GQ * k;
+                xv[t][k] = make_float4(0.f, 0.f, 0.f, 0.f);
+                if (t < cnt && vi < FV) xv[t][k] = __ldcs(reinterpret_cast<const float4 *>(xp[t]) + vi);
+            }
+
+        float zp[EPB], rinv[EPB], sc[EPB];
+        bool fast[EPB];
 #pragma unroll
-                    for (int i = 0; i < 4; ++i) {
-                        mn = fminf(mn, e[i]), mx = fmaxf(mx, e[i]);
-                        if (e[i] == 0.0f && zkey == INT_MAX)
-                            zkey = ((vi * 4 + i) << 1) | (int)(__float_as_uint(e[i]) >> 31);
+        for (int t = 0; t < EPB; ++t) {
+            zp[t] = 0.f, sc[t] = 1.f;
+            if (t < cnt) {
+                if (!params_given) {
+                    float mn = __int_as_float(0x7f800000), mx = __int_as_float(0xff800000);  // +inf, -inf
+#pragma unroll
+                    for (int k = 0; k < NV; ++k)
+                        if (gl + GQ * k < FV) {
+                            mn = fminf(fminf(mn, xv[t][k].x), fminf(xv[t][k].y, fminf(xv[t][k].z, xv[t][k].w)));
+                            mx = fmaxf(fmaxf(mx, xv[t][k].x), fmaxf(xv[t][k].y, fmaxf(xv[t][k].z, xv[t][k].w)));
+                        }
+                    // lanes past the row's end hold +inf / -inf and drop out of the reduction
+                    mn = ordered_to_float(__reduce_min_sync(gmask, float_to_ordered(mn)));
+                    mx = ordered_to_float(__reduce_max_sync(gmask, float_to_ordered(mx)));
+                    const float x0 = __shfl_sync(gmask, xv[t][0].x, lead);
+                    if (x0 != x0) {  // a NaN in column 0 is never replaced by the reference's scan
+                        mn = mx = x0;
+                    } else if (mn == 0.0f || mx == 0.0f) {
+                        // of several zeros of either sign the reference keeps the first one met:
+                        // find the first zero column of the row and take its sign
+                        int zkey = INT_MAX;
+#pragma unroll
+                        for (int k = NV - 1; k >= 0; --k) {
+                            const int vi = gl + GQ * k;
+                            if (vi < FV) {
+                                const float e[4] = {xv[t][k].x, xv[t][k].y, xv[t][k].z, xv[t][k].w};
+#pragma unroll
+                                for (int i = 3; i >= 0; --i)
+                                    if (e[i] == 0.0f) zkey = ((vi * 4 + i) << 1) | (int)(__float_as_uint(e[i]) >> 31);
+                            }
+                        }
+                        zkey = __reduce_min_sync(gmask, zkey);
+                        const float z = (zkey & 1) ? -0.0f : 0.0f;
+                        if (mn == 0.0f) mn = z;
+                        if (mx == 0.0f) mx = z;
+                    }
+                    float s = __fdiv_rn(__fsub_rn(mx, mn), LEVELS);
+                    if (s == 0.0f) s = 1.0f;
+                    zp[t] = mn, sc[t] = s;
+                    if (gl == 0) {
+                        *reinterpret_cast<float2 *>(params + (int64_t)(i0 + t) * 2) = make_float2(mn, s);
+                        if (params_bf16) params_bf16[i0 + t] = bf16_bits(mn) | (bf16_bits(s) << 16);
                     }
                 } else {
-                    xv[t][k] = make_float4(0.f, 0.f, 0.f, 0.f);
+                    zp[t] = params[(int64_t)(i0 + t) * 2];
+                    sc[t] = params[(int64_t)(i0 + t) * 2 + 1];
+                    if (gl == 0 && params_bf16) params_bf16[i0 + t] = bf16_bits(zp[t]) | (bf16_bits(sc[t]) << 16);
                 }
             }
-            if (!params_given) {
-                // lanes past the row's end hold +inf/-inf and drop out of the reduction;
-                // a row that starts with a NaN is handled by fix_extreme
-                mn = warp_min(mn);
-                mx = warp_max(mx);
-                const float x0 = __shfl_sync(kFullMask, xv[t][0].x, 0);
-                mn = fix_extreme(mn, x0, zkey);
-                mx = fix_extreme(mx, x0, zkey);
-                float s = __fdiv_rn(__fsub_rn(mx, mn), LEVELS);
-                if (s == 0.0f) s = 1.0f;
-                zp[t] = mn;
-                sc[t] = s;
-                if (lane == 0) {
-                    params[(int64_t)(i0 + t) * 2] = mn;
-                    params[(int64_t)(i0 + t) * 2 + 1] = s;
-                    if (params_bf16) params_bf16[i0 + t] = bf16_bits(mn) | (bf16_bits(s) << 16);
-                }
-            } else {
-                zp[t] = params[(int64_t)(i0 + t) * 2];
-                sc[t] = params[(int64_t)(i0 + t) * 2 + 1];
-                if (lane == 0 && params_bf16) params_bf16[i0 + t] = bf16_bits(zp[t]) | (bf16_bits(sc[t]) << 16);
-            }
+            const float a = fabsf(sc[t]);
+            fast[t] = (a >= 7.888609e-31f) && (a <= 1.2676506e30f);  // 1/scale is a full-precision normal
+            rinv[t] = fast[t] ? __frcp_rn(sc[t]) : 0.f;
         }
-    }
 
-    uint32_t *out = reinterpret_cast<uint32_t *>(codes + R * (int64_t)F);
+        // code = round-half-even(fl((x - zp) / scale)), IEEE division.  The quotient is estimated as
+        // (x - zp) * fl(1/scale) -- within 2 ulp of the true quotient -- and the exact division is done
+        // only when the estimate is within 8 ulp of a rounding boundary k + 0.5 (or out of the code
+        // range, or not finite): elsewhere both round to the same integer.
+        constexpr float kBound = LEVELS + 1.0f;
+        constexpr float kThr = 0.5f - kBound * 9.5367431640625e-07f;  // 0.5 - 2^-20 * bound
+        auto enc = [&](float x, int t) -> uint32_t {
+            const float d = __fsub_rn(x, zp[t]);
+            float q = __fmul_rn(d, rinv[t]);
+            const float k = rintf(q);
+            const bool sure = fast[t] && (fabsf(__fsub_rn(q, k)) < kThr) && (fabsf(q) <= kBound);
+            if (!sure) q = __fdiv_rn(d, sc[t]);
+            return params_given ? (uint32_t)__float2int_rn(q) : __float2uint_rn(q);
+        };
+        uint32_t *out = reinterpret_cast<uint32_t *>(codes + R * (int64_t)F);
 #pragma unroll
-    for (int k = 0; k < NV; ++k) {
-        const int vi = lane + 32 * k;
-        if (vi < FV) {
-            uint32_t b0 = 0, b1 = 0, b2 = 0, b3 = 0;
+        for (int k = 0; k < NV; ++k) {
+            const int vi = gl + GQ * k;
+            if (vi < FV) {
+                uint32_t b0 = 0, b1 = 0, b2 = 0, b3 = 0;
 #pragma unroll
-            for (int t = 0; t < EPB; ++t) {
-                if (t < cnt) {
-                    const int sh = (EPB - 1 - t) * BITS;
-                    b0 |= encode(xv[t][k].x, zp[t], sc[t], params_given) << sh;
-                    b1 |= encode(xv[t][k].y, zp[t], sc[t], params_given) << sh;
-                    b2 |= encode(xv[t][k].z, zp[t], sc[t], params_given) << sh;
-                    b3 |= encode(xv[t][k].w, zp[t], sc[t], params_given) << sh;
+                for (int t = 0; t < EPB; ++t) {
+                    if (t < cnt) {
+                        const int sh = (EPB - 1 - t) * BITS;
+                        b0 |= enc(xv[t][k].x, t) << sh;
+                        b1 |= enc(xv[t][k].y, t) << sh;
+                        b2 |= enc(xv[t][k].z, t) << sh;
+                        b3 |= enc(xv[t][k].w, t) << sh;
+                    }
                 }
+                __stcs(out + vi, (b0 & 255u) | ((b1 & 255u) << 8) | ((b2 & 255u) << 16) | ((b3 & 255u) << 24));
             }
-            __stcs(out + vi, (b0 & 255u) | ((b1 & 255u) << 8) | ((b2 & 255u) << 16) | ((b3 & 255u) << 24));
         }
     }
 }
@@ -203,8 +278,9 @@ __global__ void __launch_bounds__(kCodecWarps * 32)
     __shared__ int pbase[kMaxSeg + 1];
     build_packed_prefix(seg, P, epb, pbase);
     const int lane = threadIdx.x & 31;
-    const int64_t R = (int64_t)blockIdx.x * kCodecWarps + (threadIdx.x >> 5);
-    if (R >= pbase[P]) return;
+    // grid-stride over packed rows: a warp keeps working, so its loads overlap the previous row's stores
+    for (int64_t R = (int64_t)blockIdx.x * kCodecWarps + (threadIdx.x >> 5); R < pbase[P];
+         R += (int64_t)gridDim.x * kCodecWarps) {
     const int p = find_segment(pbase, P, (int)R);
     const int i0 = seg[p] + ((int)R - pbase[p]) * epb;
     const int cnt = min(epb, seg[p + 1] - i0);
@@ -254,6 +330,7 @@ __global__ void __launch_bounds__(kCodecWarps * 32)
             if (t < cnt) b |= encode(xp[t][k], zp[t], sc[t], params_given) << ((epb - 1 - t) * bits);
         out[k] = (uint8_t)b;
     }
+    }  // packed rows
 }
 
 // ---- unpack + dequantise -----------------------------------------------------------------
@@ -267,8 +344,9 @@ __global__ void __launch_bounds__(kCodecWarps * 32)
     __shared__ int pbase[kMaxSeg + 1];
     build_packed_prefix(seg, P, EPB, pbase);
     const int lane = threadIdx.x & 31;
-    const int64_t R = (int64_t)blockIdx.x * kCodecWarps + (threadIdx.x >> 5);
-    if (R >= pbase[P]) return;
+    // grid-stride over packed rows: a warp keeps working, so its loads overlap the previous row's stores
+    for (int64_t R = (int64_t)blockIdx.x * kCodecWarps + (threadIdx.x >> 5); R < pbase[P];
+         R += (int64_t)gridDim.x * kCodecWarps) {
     const int p = find_segment(pbase, P, (int)R);
     const int i0 = seg[p] + ((int)R - pbase[p]) * EPB;
     const int cnt = min(EPB, seg[p + 1] - i0);
@@ -318,6 +396,7 @@ __global__ void __launch_bounds__(kCodecWarps * 32)
                     OUT[(int64_t)(i0 + t) * ldo + k] = fmaf((float)((w >> ((EPB - 1 - t) * BITS)) & MASK), sc[t], zp[t]);
         }
     }
+    }  // packed rows
 }
 
 // ---- mixed-bit column-packed codec: one warp per row ------------------------------------
@@ -397,6 +476,13 @@ static int check_seg_args(const char *who, const int32_t *seg, int32_t P, int64_
 // launch only needs a grid that covers it.
 static int64_t packed_rows_bound(int64_t rows, int32_t P, int epb) { return div_up(rows, epb) + P; }
 
+// CTAs for the grid-stride codec kernels: enough to cover the rows, at most 16 per SM.
+static unsigned codec_blocks(int64_t rows, int32_t P, int epb) {
+    int64_t b = div_up(packed_rows_bound(rows, P, epb), kCodecWarps);
+    const int64_t cap = (int64_t)kNumSMs * 32;
+    return (unsigned)(b < cap ? b : cap);
+}
+
 extern "C" int gnnagg_quant_pack_rows(const float *X, int64_t ldx, const int32_t *idx, int32_t F, const int32_t *seg,
                                       int32_t P, int64_t rows, int32_t bits, int32_t params_given, float *params,
                                       void *params_bf16, uint8_t *codes, void *stream) {
@@ -407,23 +493,27 @@ extern "C" int gnnagg_quant_pack_rows(const float *X, int64_t ldx, const int32_t
         return fail(GNNAGG_ERR_ARG, "quant_pack_rows: null pointer or ldx < F");
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     const int epb = 8 / bits;
-    const unsigned blocks = (unsigned)div_up(packed_rows_bound(rows, P, epb), kCodecWarps);
+    const unsigned blocks = codec_blocks(rows, P, epb);
     const bool vec = (F % 4 == 0) && (ldx % 4 == 0) && aligned16(X) && F <= 512 &&
-                     (reinterpret_cast<uintptr_t>(codes) % 4 == 0) &&
+                     (reinterpret_cast<uintptr_t>(codes) % 4 == 0) && (reinterpret_cast<uintptr_t>(params) % 8 == 0) &&
                      (params_bf16 == nullptr || reinterpret_cast<uintptr_t>(params_bf16) % 4 == 0);
     if (vec) {
         uint32_t *pb = static_cast<uint32_t *>(params_bf16);
-#define GNNAGG_QP(B, NV)                                                                                      \
-    quant_pack_vec_kernel<B, NV><<<blocks, kCodecWarps * 32, 0, st>>>(X, ldx, idx, F, seg, P, params_given, params, \
-                                                                       pb, codes)
-        const int nv = (F + 127) / 128;
-        if (bits == 2) {
-            if (nv == 1) GNNAGG_QP(2, 1); else if (nv == 2) GNNAGG_QP(2, 2); else GNNAGG_QP(2, 4);
-        } else if (bits == 4) {
-            if (nv == 1) GNNAGG_QP(4, 1); else if (nv == 2) GNNAGG_QP(4, 2); else GNNAGG_QP(4, 4);
-        } else {
-            if (nv == 1) GNNAGG_QP(8, 1); else if (nv == 2) GNNAGG_QP(8, 2); else GNNAGG_QP(8, 4);
-        }
+#define GNNAGG_QP(B, NV, GQ)                                                                                      \
+    quant_pack_vec_kernel<B, NV, GQ><<<blocks, kCodecWarps * 32, 0, st>>>(X, ldx, idx, F, seg, P, params_given, params, \
+                                                                           pb, codes)
+#define GNNAGG_QP_WIDTH(B)                                         \
+    do {                                                           \
+        if (F <= 32) GNNAGG_QP(B, 1, 8);                           \
+        else if (F <= 64) GNNAGG_QP(B, 1, 16);                     \
+        else if (F <= 128) GNNAGG_QP(B, 1, 32);                    \
+        else if (F <= 256) GNNAGG_QP(B, 2, 32);                    \
+        else GNNAGG_QP(B, 4, 32);                                  \
+    } while (0)
+        if (bits == 2) GNNAGG_QP_WIDTH(2);
+        else if (bits == 4) GNNAGG_QP_WIDTH(4);
+        else GNNAGG_QP_WIDTH(8);
+#undef GNNAGG_QP_WIDTH
 #undef GNNAGG_QP
         return check_launch("quant_pack_vec_kernel");
     }
@@ -442,7 +532,7 @@ extern "C" int gnnagg_unpack_dequant_rows(const uint8_t *codes, int32_t F, const
         return fail(GNNAGG_ERR_ARG, "unpack_dequant_rows: null pointer or ldo < F");
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     const int epb = 8 / bits;
-    const unsigned blocks = (unsigned)div_up(packed_rows_bound(rows, P, epb), kCodecWarps);
+    const unsigned blocks = codec_blocks(rows, P, epb);
     const __nv_bfloat16 *pb = static_cast<const __nv_bfloat16 *>(params_bf16);
     const bool vec = (F % 4 == 0) && (ldo % 4 == 0) && aligned16(OUT) && (reinterpret_cast<uintptr_t>(codes) % 4 == 0);
 #define GNNAGG_UD(B, V) \

@@ -155,3 +155,57 @@ def write_partition_files(out_dir: str, graph_name: str, rank: int, begin: torch
     if rank == 0:
         with open(os.path.join(out_dir, "begin_node_on_each_partition.txt"), "w") as fh:
             fh.write(" ".join(str(int(x)) for x in begin.tolist()) + "\n")
+
+
+def partitioned_in_edges(kind: str, n: int, n_edges: int, seed: int, rank: int, world: int, device, relabel: bool = True,
+                         chunk: int = 1 << 25, scale: int = 0, gamma: float = 2.1, self_loops: bool = True):
+    """In-edges (src, dst; global ids) of rank `rank`'s contiguous vertex block of a symmetrised,
+    deduplicated synthetic graph, generated chunk by chunk from one seed so that every rank sees the
+    same global edge stream without any rank holding the whole graph.
+
+    kind "rmat": 2^scale vertices, (a,b,c,d) = (.57,.19,.19,.05); kind "chung_lu": expected degrees
+    ~ (i+1)^(-1/(gamma-1)).  relabel applies one seeded random permutation of the vertex ids (keeps
+    the partitions balanced: both generators put their hubs at low ids).  Returns (src, dst, begin)."""
+    begin = contiguous_partitions(n, world)
+    b0, b1 = int(begin[rank]), int(begin[rank + 1])
+    perm = torch.randperm(n, generator=_gen(seed + 1, device), device=device) if relabel else None
+    g = _gen(seed, device)
+    cdf = None
+    if kind == "chung_lu":
+        i = torch.arange(n, dtype=torch.float64, device=device)
+        w = (i + 1.0).pow(-1.0 / (gamma - 1.0))
+        w = w * (2.0 * n_edges / w.sum())
+        w = torch.clamp(w, max=math.sqrt(2.0 * n_edges))
+        cdf = torch.cumsum(w, 0)
+        cdf = (cdf / cdf[-1]).to(torch.float64)
+        del i, w
+    keys = []
+    for start in range(0, n_edges, chunk):
+        m = min(chunk, n_edges - start)
+        if kind == "rmat":
+            a, b, c = 0.57, 0.19, 0.19
+            src = torch.zeros(m, dtype=torch.int64, device=device)
+            dst = torch.zeros(m, dtype=torch.int64, device=device)
+            for _ in range(scale):
+                r = torch.rand(m, generator=g, device=device)
+                src = (src << 1) | (r >= (a + b)).to(torch.int64)
+                dst = (dst << 1) | (((r >= a) & (r < a + b)) | (r >= a + b + c)).to(torch.int64)
+        elif kind == "chung_lu":
+            src = torch.searchsorted(cdf, torch.rand(m, generator=g, device=device, dtype=torch.float64)).clamp_(max=n - 1)
+            dst = torch.searchsorted(cdf, torch.rand(m, generator=g, device=device, dtype=torch.float64)).clamp_(max=n - 1)
+        else:
+            raise ValueError(kind)
+        keep = src != dst
+        src, dst = src[keep], dst[keep]
+        if perm is not None:
+            src, dst = perm[src], perm[dst]
+        for s_, d_ in ((src, dst), (dst, src)):  # both directions; keep what lands in this rank's rows
+            mine = (d_ >= b0) & (d_ < b1)
+            keys.append(torch.unique(d_[mine] * n + s_[mine]))
+        del src, dst, keep
+    if self_loops:
+        diag = torch.arange(b0, b1, dtype=torch.int64, device=device)
+        keys.append(diag * n + diag)
+    key = torch.unique(torch.cat(keys)) if keys else torch.zeros(0, dtype=torch.int64, device=device)
+    del keys, cdf
+    return key % n, key // n, begin
