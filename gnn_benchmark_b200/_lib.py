@@ -28,6 +28,8 @@ SIGNATURES = {
     "gnnagg_spmm_scratch_bytes": (_sz, [_i64, _i64, _i32]),
     "gnnagg_spmm_csr_f32": (ctypes.c_int, [_vp, _vp, _vp, _i64, _i64, _i64, _vp, _i64, _vp, _i64, _i32, _i32, _vp,
                                            _vp, _sz, _vp]),
+    "gnnagg_spmm_csr_q": (ctypes.c_int, [_vp, _vp, _vp, _i64, _i64, _i64, _vp, _vp, _vp, _i32, _i32, _vp, _i64, _i32, _i32,
+                                         _vp, _vp, _sz, _vp]),
     "gnnagg_spmm_csr_f32_static_scratch": (ctypes.c_int, [_vp, _vp, _vp, _i64, _i64, _i64, _vp, _i64, _vp, _i64, _i32,
                                                           _i32, _vp, _vp]),
     "gnnagg_csr_validate": (ctypes.c_int, [_vp, _vp, _i64, _i64, _i64, _vp, _vp]),

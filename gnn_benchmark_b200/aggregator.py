@@ -22,8 +22,14 @@ import torch.distributed as dist
 from . import _lib
 from .communicator import Communicator
 from .quantizer import Quantizer_for_all_procs
-from .spmm_kernel import SPMM_backward, SPMM_forward
+from .spmm_kernel import SPMM_backward, SPMM_backward_packed, SPMM_forward, SPMM_forward_packed
 from .time_recorder import TimeRecorder
+
+
+# Packed halo modes: decode the received codes inside the receive-side SpMM instead of unpacking them
+# into the fp32 halo buffer first (same result bit for bit; the fp32 buffer is then left untouched).
+# Set to False to get the reference's two-step sequence, e.g. to inspect comm_buf.recv_buf.
+FUSE_UNPACK = True
 
 
 def _world_size() -> int:
@@ -107,7 +113,8 @@ class Aggregator(torch.autograd.Function):
             comm_handle.wait()
 
         num_recv_nodes = sum(graph.comm_splits.recv_splits) if world_size > 1 else 0
-        if packed and num_recv_nodes != 0:
+        fused = packed and FUSE_UNPACK and feat_len % 4 == 0
+        if packed and num_recv_nodes != 0 and not fused:
             t = rec.start() if rec else None
             q = graph.comm_buf_for_quantization
             Quantizer_for_all_procs.ctx.dequantize_intX_to_fp32(
@@ -118,11 +125,14 @@ class Aggregator(torch.autograd.Function):
 
         if world_size > 1 and num_recv_nodes != 0:
             t = rec.start() if rec else None
-            remote_nodes_feat = graph.comm_buf.recv_buf
-            if is_pre_delay:  # post-aggregation
-                SPMM_forward(graph.adj_t_pre_post_aggr_from, remote_nodes_feat, out)
+            adj = graph.adj_t_pre_post_aggr_from if is_pre_delay else graph.remote_adj_t  # post-aggregation / remote
+            if fused:
+                q = graph.comm_buf_for_quantization
+                SPMM_forward_packed(adj, q.quantized_recv_data_buf, q.quantized_recv_params_buf_bf16,
+                                    q.dequantized_work_range_per_proc, world_size, Quantizer_for_all_procs.ctx._bits(),
+                                    out)
             else:
-                SPMM_forward(graph.remote_adj_t, remote_nodes_feat, out)
+                SPMM_forward(adj, graph.comm_buf.recv_buf, out)
             if rec:
                 rec.record_remote_aggregate_time(t)
 
@@ -172,7 +182,8 @@ class Aggregator(torch.autograd.Function):
             comm_handle.wait()
 
         num_recv_nodes = sum(graph.comm_splits.send_splits) if world_size > 1 else 0
-        if packed and num_recv_nodes != 0:
+        fused = packed and FUSE_UNPACK and feat_len % 4 == 0
+        if packed and num_recv_nodes != 0 and not fused:
             t = rec.start() if rec else None
             q = graph.comm_buf_for_quantization
             Quantizer_for_all_procs.ctx.dequantize_intX_to_fp32(
@@ -184,7 +195,15 @@ class Aggregator(torch.autograd.Function):
         if world_size > 1 and num_recv_nodes != 0:
             t = rec.start() if rec else None
             local_nodes_grad_buf = graph.comm_buf.send_buf
-            if is_pre_delay:
+            if fused:
+                q = graph.comm_buf_for_quantization
+                args = (q.quantized_send_data_buf, q.quantized_send_params_buf_bf16, q.quantized_work_range_per_proc,
+                        world_size, Quantizer_for_all_procs.ctx._bits(), local_nodes_grad)
+                if is_pre_delay:
+                    SPMM_backward_packed(graph.adj_t_pre_post_aggr_to, *args)
+                else:
+                    SPMM_forward_packed(_scatter_adj(graph), *args)
+            elif is_pre_delay:
                 SPMM_backward(graph.adj_t_pre_post_aggr_to, local_nodes_grad_buf, local_nodes_grad)
             else:
                 # grad.index_add_(0, idx_nodes_send_to_others, buf) as an accumulating SpMM with the

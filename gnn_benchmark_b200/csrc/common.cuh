@@ -37,4 +37,48 @@ __device__ __forceinline__ float ld_stream(const float *p) { return __ldcs(p); }
 __device__ __forceinline__ void st_stream_v4(float *p, float4 v) { __stcs(reinterpret_cast<float4 *>(p), v); }
 __device__ __forceinline__ void st_stream(float *p, float v) { __stcs(p, v); }
 
+constexpr int kMaxSeg = 1024;  // peer segments per call
+
+// Packed-row prefix of the segments into shared memory: pbase[p] = sum_{q<p} ceil(n_q/epb).
+__device__ __forceinline__ void build_packed_prefix(const int32_t *__restrict__ seg, int P, int epb, int *pbase,
+                                                    int *sseg = nullptr) {
+    if (sseg != nullptr)
+        for (int p = threadIdx.x; p <= P; p += blockDim.x) sseg[p] = seg[p];
+    if (threadIdx.x < 32) {
+        const int lane = threadIdx.x;
+        int running = 0;
+        for (int p0 = 0; p0 < P; p0 += 32) {
+            const int p = p0 + lane;
+            int cnt = 0;
+            if (p < P) cnt = (seg[p + 1] - seg[p] + epb - 1) / epb;
+            int incl = cnt;
+#pragma unroll
+            for (int off = 1; off < 32; off <<= 1) {
+                const int t = __shfl_up_sync(kFullMask, incl, off);
+                if (lane >= off) incl += t;
+            }
+            if (p < P) pbase[p] = running + incl - cnt;
+            running += __shfl_sync(kFullMask, incl, 31);
+        }
+        if (lane == 0) pbase[P] = running;
+    }
+    __syncthreads();
+}
+
+// Packed row R -> segment p with pbase[p] <= R < pbase[p+1] (empty segments skipped).
+__device__ __forceinline__ int find_segment(const int *pbase, int P, int R) {
+    int lo = 0, hi = P - 1;
+    while (lo < hi) {
+        const int mid = (lo + hi + 1) >> 1;
+        if (pbase[mid] <= R)
+            lo = mid;
+        else
+            hi = mid - 1;
+    }
+    // several empty segments may share pbase[lo]; the owner is the last one with pbase <= R,
+    // which the search above returns because it moves right on equality.
+    return lo;
+}
+
+
 }  // namespace gnnagg

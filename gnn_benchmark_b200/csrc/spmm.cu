@@ -179,14 +179,31 @@ __device__ __forceinline__ void vstore_plain<1>(float *p, const Vec<1> &a) {
 // G lanes per feature row, NV vectors of VW floats per lane, U gather instructions in flight.
 // ACC: accumulate onto the old output.  FULL: the row is exactly G*NV vectors wide, so no lane
 // holds a vector past the row's end and the per-vector predicates vanish.
-template <int G, int NV, int VW, int U, bool ACC, bool FULL>
+// QB: 0 = the dense operand is the fp32 matrix X; 2 / 4 / 8 = the dense operand is a row-packed
+// quantised halo buffer (codes + bf16 parameters per wire slot, per-peer segments `seg`): column
+// index c is a wire slot, its row is decoded on the fly as fma(code, scale, zero_point) -- the
+// value the unpack kernel would have written -- and used in the same FMA chain.
+struct PackedOperand {
+    const uint8_t *codes;     // (sum_p ceil(n_p / (8/QB)), F) bytes, row stride F
+    const uint32_t *params;   // per slot: bf16 zero_point (low half), bf16 scale (high half)
+    const int32_t *seg;       // P+1 prefix of per-peer slot counts
+    int P;
+    int F;
+};
+
+template <int G, int NV, int VW, int U, bool ACC, bool FULL, int QB>
 __global__ void __launch_bounds__(kWarpsPerBlock * 32, min_blocks_per_sm(NV))
     spmm_chunk_kernel(const int64_t *__restrict__ rowptr, const int32_t *__restrict__ col,
                       const float *__restrict__ val, int64_t M, const float *__restrict__ X, int64_t ldx,
                       float *__restrict__ Y, int64_t ldy, int FV,
                       const int64_t *__restrict__ chunk_nz, const int32_t *__restrict__ chunk_row, int64_t nchunks,
-                      float *__restrict__ carry, int carry_ld) {
+                      float *__restrict__ carry, int carry_ld, PackedOperand q) {
     constexpr int S = 32 / G;  // nonzeros fetched per warp-wide gather instruction
+    constexpr int EPB = QB ? 8 / QB : 1;
+    constexpr int SEGCAP = QB ? kMaxSeg + 1 : 1;
+    __shared__ int sseg[SEGCAP];
+    __shared__ int pbase[SEGCAP];
+    if (QB) build_packed_prefix(q.seg, q.P, EPB, pbase, sseg);  // before any warp leaves: it synchronises the CTA
     const int lane = threadIdx.x & 31;
     const int64_t c = (int64_t)blockIdx.x * kWarpsPerBlock + (threadIdx.x >> 5);
     if (c >= nchunks) return;
@@ -278,40 +295,77 @@ __global__ void __launch_bounds__(kWarpsPerBlock * 32, min_blocks_per_sm(NV))
         }
     };
 
+    // What one gather instruction brings in, per step u: the fp32 vectors, or the packed words plus
+    // the slot's decode parameters.
+    Vec<VW> xr[QB ? 1 : U][QB ? 1 : NV];
+    uint32_t wq[QB ? U : 1][QB ? NV : 1];
+    float av[U], zq[QB ? U : 1], sq[QB ? U : 1];
+    int shq[QB ? U : 1];
+
     for (int eb = 0; eb < n; eb += 32) {
         int my_col = 0;
-        float my_val = 0.f;
+        float my_val = 0.f, my_zp = 0.f, my_sc = 0.f;
         if (eb + lane < n) {
             my_col = ld_stream(col + e0 + eb + lane);
             my_val = ld_stream(val + e0 + eb + lane);
+            if (QB) {
+                // wire slot -> (packed row, bit position) and its bf16 parameters, once per nonzero
+                const int pseg = find_segment(sseg, q.P, my_col);
+                const int j = my_col - sseg[pseg];
+                const uint32_t prm = __ldg(q.params + my_col);
+                my_zp = __uint_as_float(prm << 16);
+                my_sc = __uint_as_float(prm & 0xffff0000u);
+                my_col = ((pbase[pseg] + j / EPB) << 3) | ((EPB - 1 - j % EPB) * QB);
+            }
         }
         const int in_batch = (n - eb) < 32 ? (n - eb) : 32;
         const int nsteps = (in_batch + S - 1) / S;
         const int full_steps = in_batch / S;  // steps in which every lane group holds a nonzero
+
+        auto fetch = [&](int u, int src_lane, bool ok) {
+            const int cc = __shfl_sync(kFullMask, my_col, src_lane);
+            av[u] = __shfl_sync(kFullMask, my_val, src_lane);
+            if (QB) {
+                zq[u] = __shfl_sync(kFullMask, my_zp, src_lane);
+                sq[u] = __shfl_sync(kFullMask, my_sc, src_lane);
+                shq[u] = cc & 7;
+                const uint32_t *wp = reinterpret_cast<const uint32_t *>(q.codes + (int64_t)(cc >> 3) * q.F);
+#pragma unroll
+                for (int k = 0; k < NV; ++k)
+                    if (ok && vok[k]) wq[u][k] = __ldg(wp + gl + k * G);
+            } else {
+                const float *xp = X + (int64_t)cc * ldx;
+#pragma unroll
+                for (int k = 0; k < NV; ++k)
+                    if (ok && vok[k]) xr[u][k] = vload<VW>(xp + voff[k]);
+            }
+        };
+        auto apply = [&](int u) {
+#pragma unroll
+            for (int k = 0; k < NV; ++k)
+                if (vok[k]) {
+#pragma unroll
+                    for (int i = 0; i < VW; ++i) {
+                        float x;
+                        if (QB) {
+                            const uint32_t code = (wq[u][k] >> (8 * i + shq[u])) & ((1u << QB) - 1u);
+                            x = fmaf((float)code, sq[u], zq[u]);
+                        } else {
+                            x = xr[u][k].v[i];
+                        }
+                        acc[k].v[i] = fmaf(av[u], x, acc[k].v[i]);
+                    }
+                }
+        };
+
         for (int s0 = 0; s0 < nsteps; s0 += U) {
-            Vec<VW> xr[U][NV];
-            float av[U];
             if (s0 + U <= full_steps && next_end >= eb + (s0 + U) * S) {
                 // Fast path: the next U*S nonzeros all belong to the current row -- issue the U
                 // gathers back to back, then the U FMA groups, with nothing else in between.
 #pragma unroll
-                for (int u = 0; u < U; ++u) {
-                    const int j = (s0 + u) * S + grp;
-                    const int cc = __shfl_sync(kFullMask, my_col, j);
-                    av[u] = __shfl_sync(kFullMask, my_val, j);
-                    const float *xp = X + (int64_t)cc * ldx;
+                for (int u = 0; u < U; ++u) fetch(u, (s0 + u) * S + grp, true);
 #pragma unroll
-                    for (int k = 0; k < NV; ++k)
-                        if (vok[k]) xr[u][k] = vload<VW>(xp + voff[k]);
-                }
-#pragma unroll
-                for (int u = 0; u < U; ++u)
-#pragma unroll
-                    for (int k = 0; k < NV; ++k)
-                        if (vok[k]) {
-#pragma unroll
-                            for (int i = 0; i < VW; ++i) acc[k].v[i] = fmaf(av[u], xr[u][k].v[i], acc[k].v[i]);
-                        }
+                for (int u = 0; u < U; ++u) apply(u);
                 continue;
             }
             // General path: a row ends inside these steps, or the batch runs out.
@@ -319,13 +373,8 @@ __global__ void __launch_bounds__(kWarpsPerBlock * 32, min_blocks_per_sm(NV))
 #pragma unroll
             for (int u = 0; u < U; ++u) {
                 const int j = (s0 + u) * S + grp;  // position inside the 32-nonzero batch
-                const int cc = __shfl_sync(kFullMask, my_col, j & 31);
-                av[u] = __shfl_sync(kFullMask, my_val, j & 31);
                 ok[u] = j < in_batch;
-                const float *xp = X + (int64_t)cc * ldx;
-#pragma unroll
-                for (int k = 0; k < NV; ++k)
-                    if (ok[u] && vok[k]) xr[u][k] = vload<VW>(xp + voff[k]);
+                fetch(u, j & 31, ok[u]);
             }
 #pragma unroll
             for (int u = 0; u < U; ++u) {
@@ -335,26 +384,13 @@ __global__ void __launch_bounds__(kWarpsPerBlock * 32, min_blocks_per_sm(NV))
                     bool pending = ok[u];
                     while (next_end < step_end) {  // a row ends before this step's last nonzero
                         if (pending && eg < next_end) {
-#pragma unroll
-                            for (int k = 0; k < NV; ++k)
-                                if (vok[k]) {
-#pragma unroll
-                                    for (int i = 0; i < VW; ++i)
-                                        acc[k].v[i] = fmaf(av[u], xr[u][k].v[i], acc[k].v[i]);
-                                }
+                            apply(u);
                             pending = false;
                         }
                         flush_row();
                         advance_row();
                     }
-                    if (pending) {
-#pragma unroll
-                        for (int k = 0; k < NV; ++k)
-                            if (vok[k]) {
-#pragma unroll
-                                for (int i = 0; i < VW; ++i) acc[k].v[i] = fmaf(av[u], xr[u][k].v[i], acc[k].v[i]);
-                            }
-                    }
+                    if (pending) apply(u);
                 }
             }
         }
@@ -427,16 +463,25 @@ __global__ void csr_validate_kernel(const int64_t *__restrict__ rowptr, const in
 template <int G, int NV, int VW, int U>
 static void launch_chunks(const int64_t *rowptr, const int32_t *col, const float *val, int64_t M, const float *X,
                           int64_t ldx, float *Y, int64_t ldy, int FV, int accumulate, const int64_t *chunk_nz,
-                          const int32_t *chunk_row, int64_t nchunks, float *carry, int carry_ld, cudaStream_t st) {
+                          const int32_t *chunk_row, int64_t nchunks, float *carry, int carry_ld, int qbits,
+                          const PackedOperand &q, cudaStream_t st) {
     const unsigned blocks = (unsigned)div_up(nchunks, kWarpsPerBlock);
     const bool full = (FV == G * NV) && VW == 4;
-#define GNNAGG_GO(ACC, FULL)                                                                                  \
-    spmm_chunk_kernel<G, NV, VW, U, ACC, FULL><<<blocks, kWarpsPerBlock * 32, 0, st>>>(                       \
-        rowptr, col, val, M, X, ldx, Y, ldy, FV, chunk_nz, chunk_row, nchunks, carry, carry_ld)
-    if (VW == 4 && full) {
-        if (accumulate) GNNAGG_GO(true, (VW == 4)); else GNNAGG_GO(false, (VW == 4));
+#define GNNAGG_GO(ACC, FULL, QB)                                                                              \
+    spmm_chunk_kernel<G, NV, VW, U, ACC, FULL, QB><<<blocks, kWarpsPerBlock * 32, 0, st>>>(                   \
+        rowptr, col, val, M, X, ldx, Y, ldy, FV, chunk_nz, chunk_row, nchunks, carry, carry_ld, q)
+    if (VW == 4 && qbits != 0) {  // packed operand: 128-bit path only, per-vector predicates kept
+        if (qbits == 2) {
+            if (accumulate) GNNAGG_GO(true, false, (VW == 4 ? 2 : 0)); else GNNAGG_GO(false, false, (VW == 4 ? 2 : 0));
+        } else if (qbits == 4) {
+            if (accumulate) GNNAGG_GO(true, false, (VW == 4 ? 4 : 0)); else GNNAGG_GO(false, false, (VW == 4 ? 4 : 0));
+        } else {
+            if (accumulate) GNNAGG_GO(true, false, (VW == 4 ? 8 : 0)); else GNNAGG_GO(false, false, (VW == 4 ? 8 : 0));
+        }
+    } else if (VW == 4 && full) {
+        if (accumulate) GNNAGG_GO(true, (VW == 4), 0); else GNNAGG_GO(false, (VW == 4), 0);
     } else {
-        if (accumulate) GNNAGG_GO(true, false); else GNNAGG_GO(false, false);
+        if (accumulate) GNNAGG_GO(true, false, 0); else GNNAGG_GO(false, false, 0);
     }
 #undef GNNAGG_GO
 }
@@ -445,10 +490,10 @@ template <int VW>
 static void dispatch_width(int FV, const int64_t *rowptr, const int32_t *col, const float *val, int64_t M,
                            const float *X, int64_t ldx, float *Y, int64_t ldy, int accumulate,
                            const int64_t *chunk_nz, const int32_t *chunk_row, int64_t nchunks, float *carry,
-                           int carry_ld, cudaStream_t st) {
+                           int carry_ld, int qbits, const PackedOperand &q, cudaStream_t st) {
 #define GNNAGG_LAUNCH(G, NV, U)                                                                                 \
     launch_chunks<G, NV, VW, U>(rowptr, col, val, M, X, ldx, Y, ldy, FV, accumulate, chunk_nz, chunk_row, nchunks, \
-                                carry, carry_ld, st)
+                                carry, carry_ld, qbits, q, st)
     if (FV <= 2)
         GNNAGG_LAUNCH(2, 1, 2);
     else if (FV <= 4)
@@ -509,19 +554,20 @@ extern "C" size_t gnnagg_spmm_scratch_bytes(int64_t M, int64_t nnz, int32_t F) {
     return (((size_t)nc * ld * sizeof(float)) + 255) & ~(size_t)255;
 }
 
-extern "C" int gnnagg_spmm_csr_f32(const int64_t *rowptr, const int32_t *col, const float *val, int64_t M, int64_t K,
-                                   int64_t nnz, const float *X, int64_t ldx, float *Y, int64_t ldy, int32_t F,
-                                   int32_t accumulate, const void *plan, void *scratch, size_t scratch_bytes,
-                                   void *stream) {
-    if (M < 0 || K < 0 || nnz < 0 || F < 0) return fail(GNNAGG_ERR_ARG, "spmm: negative size");
+// Shared body of the fp32-operand and packed-operand entry points.
+static int spmm_launch(const char *who, const int64_t *rowptr, const int32_t *col, const float *val, int64_t M,
+                       int64_t K, int64_t nnz, const float *X, int64_t ldx, float *Y, int64_t ldy, int32_t F,
+                       int32_t accumulate, const void *plan, void *scratch, size_t scratch_bytes, int qbits,
+                       PackedOperand q, void *stream) {
+    if (M < 0 || K < 0 || nnz < 0 || F < 0) return fail(GNNAGG_ERR_ARG, "%s: negative size", who);
     if (M == 0 || F == 0) return GNNAGG_OK;
-    if (rowptr == nullptr || Y == nullptr || plan == nullptr) return fail(GNNAGG_ERR_ARG, "spmm: null pointer");
-    if (nnz > 0 && (col == nullptr || val == nullptr || X == nullptr))
-        return fail(GNNAGG_ERR_ARG, "spmm: null pointer");
-    if (ldx < F || ldy < F) return fail(GNNAGG_ERR_ARG, "spmm: leading dimension smaller than F");
-    if (M > INT32_MAX - 64 || K > INT32_MAX) return fail(GNNAGG_ERR_UNSUPPORTED, "spmm: M, K must fit int32");
+    if (rowptr == nullptr || Y == nullptr || plan == nullptr) return fail(GNNAGG_ERR_ARG, "%s: null pointer", who);
+    if (nnz > 0 && (col == nullptr || val == nullptr || (qbits == 0 && X == nullptr)))
+        return fail(GNNAGG_ERR_ARG, "%s: null pointer", who);
+    if ((qbits == 0 && ldx < F) || ldy < F) return fail(GNNAGG_ERR_ARG, "%s: leading dimension smaller than F", who);
+    if (M > INT32_MAX - 64 || K > INT32_MAX) return fail(GNNAGG_ERR_UNSUPPORTED, "%s: M, K must fit int32", who);
     if (scratch == nullptr || scratch_bytes < gnnagg_spmm_scratch_bytes(M, nnz, F) || !aligned16(scratch))
-        return fail(GNNAGG_ERR_SCRATCH, "spmm: scratch missing, too small or not 16-byte aligned");
+        return fail(GNNAGG_ERR_SCRATCH, "%s: scratch missing, too small or not 16-byte aligned", who);
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     const int items = chunk_items();
     const int64_t nc = num_chunks(M, nnz, items);
@@ -529,7 +575,9 @@ extern "C" int gnnagg_spmm_csr_f32(const int64_t *rowptr, const int32_t *col, co
     const int32_t *crow = plan_chunk_row(plan, nc);
     float *carry = static_cast<float *>(scratch);
 
-    const bool vec4 = (F % 4 == 0) && (ldx % 4 == 0) && (ldy % 4 == 0) && aligned16(X) && aligned16(Y);
+    const bool vec4 = (F % 4 == 0) && (qbits != 0 || (ldx % 4 == 0 && aligned16(X))) && (ldy % 4 == 0) && aligned16(Y);
+    if (qbits != 0 && !vec4)
+        return fail(GNNAGG_ERR_UNSUPPORTED, "%s: packed operand needs F %% 4 == 0 and a 16-byte aligned output", who);
     const int vw = vec4 ? 4 : 1;
     const int strip = strip_floats(vw);
     for (int f0 = 0; f0 < F; f0 += strip) {
@@ -537,11 +585,14 @@ extern "C" int gnnagg_spmm_csr_f32(const int64_t *rowptr, const int32_t *col, co
         const int carry_ld = (fs + 3) & ~3;
         const float *Xs = X == nullptr ? nullptr : X + f0;
         float *Ys = Y + f0;
+        PackedOperand qs = q;
+        if (qbits != 0) qs.codes = q.codes + f0;  // one byte per column: the strip starts f0 bytes into each packed row
         if (vec4)
             dispatch_width<4>(fs / 4, rowptr, col, val, M, Xs, ldx, Ys, ldy, accumulate, cnz, crow, nc, carry, carry_ld,
-                              st);
+                              qbits, qs, st);
         else
-            dispatch_width<1>(fs, rowptr, col, val, M, Xs, ldx, Ys, ldy, accumulate, cnz, crow, nc, carry, carry_ld, st);
+            dispatch_width<1>(fs, rowptr, col, val, M, Xs, ldx, Ys, ldy, accumulate, cnz, crow, nc, carry, carry_ld, 0, qs,
+                              st);
         int rc = check_launch("spmm_chunk_kernel");
         if (rc != GNNAGG_OK) return rc;
         spmm_fixup_kernel<<<(unsigned)div_up(nc, kWarpsPerBlock), kWarpsPerBlock * 32, 0, st>>>(
@@ -550,6 +601,31 @@ extern "C" int gnnagg_spmm_csr_f32(const int64_t *rowptr, const int32_t *col, co
         if (rc != GNNAGG_OK) return rc;
     }
     return GNNAGG_OK;
+}
+
+extern "C" int gnnagg_spmm_csr_f32(const int64_t *rowptr, const int32_t *col, const float *val, int64_t M, int64_t K,
+                                   int64_t nnz, const float *X, int64_t ldx, float *Y, int64_t ldy, int32_t F,
+                                   int32_t accumulate, const void *plan, void *scratch, size_t scratch_bytes,
+                                   void *stream) {
+    PackedOperand none = {nullptr, nullptr, nullptr, 0, 0};
+    return spmm_launch("spmm", rowptr, col, val, M, K, nnz, X, ldx, Y, ldy, F, accumulate, plan, scratch, scratch_bytes,
+                       0, none, stream);
+}
+
+extern "C" int gnnagg_spmm_csr_q(const int64_t *rowptr, const int32_t *col, const float *val, int64_t M, int64_t K,
+                                 int64_t nnz, const uint8_t *codes, const void *params_bf16, const int32_t *seg,
+                                 int32_t P, int32_t bits, float *Y, int64_t ldy, int32_t F, int32_t accumulate,
+                                 const void *plan, void *scratch, size_t scratch_bytes, void *stream) {
+    if (bits != 2 && bits != 4 && bits != 8) return fail(GNNAGG_ERR_ARG, "spmm_q: bits must be 2, 4 or 8");
+    if (seg == nullptr || P < 1) return fail(GNNAGG_ERR_ARG, "spmm_q: bad seg / P");
+    if (P > kMaxSeg) return fail(GNNAGG_ERR_UNSUPPORTED, "spmm_q: more than %d segments", kMaxSeg);
+    if (nnz > 0 && (codes == nullptr || params_bf16 == nullptr)) return fail(GNNAGG_ERR_ARG, "spmm_q: null pointer");
+    if ((reinterpret_cast<uintptr_t>(codes) & 3u) || (reinterpret_cast<uintptr_t>(params_bf16) & 3u))
+        return fail(GNNAGG_ERR_ARG, "spmm_q: codes and params must be 4-byte aligned");
+    if (K > (INT32_MAX >> 3)) return fail(GNNAGG_ERR_UNSUPPORTED, "spmm_q: too many wire slots");
+    PackedOperand q = {codes, static_cast<const uint32_t *>(params_bf16), seg, P, F};
+    return spmm_launch("spmm_q", rowptr, col, val, M, K, nnz, nullptr, 0, Y, ldy, F, accumulate, plan, scratch,
+                       scratch_bytes, bits, q, stream);
 }
 
 extern "C" int gnnagg_csr_validate(const int64_t *rowptr, const int32_t *col, int64_t M, int64_t K, int64_t nnz,

@@ -61,6 +61,55 @@ def spmm(rowptr, col, value, K: int, other: torch.Tensor, out: torch.Tensor, pla
     _lib.check(rc, "spmm_csr_f32")
 
 
+def spmm_packed(rowptr, col, value, K: int, codes: torch.Tensor, params_bf16: torch.Tensor, seg: torch.Tensor,
+                num_segments: int, bits: int, out: torch.Tensor, plan: torch.Tensor, accumulate: bool = True) -> None:
+    """out (+)= CSR[M,K] @ unpack(codes, params_bf16): the dense operand is the packed halo buffer
+    (K wire slots, `seg` = per-peer slot prefix), decoded inside the SpMM."""
+    _lib.require_cuda(rowptr, col, value, codes, params_bf16, seg, out, plan)
+    if out.dtype != torch.float32 or codes.dtype != torch.uint8 or params_bf16.dtype != torch.bfloat16:
+        raise RuntimeError("spmm_packed: expected uint8 codes, bfloat16 params and float32 output")
+    M, F = rowptr.numel() - 1, out.size(1)
+    if out.size(0) != M or codes.size(-1) != F or out.stride(1) != 1 or not codes.is_contiguous():
+        raise RuntimeError("spmm_packed: shape mismatch")
+    if M == 0 or F == 0:
+        return
+    nnz = col.numel()
+    lib = _lib.lib()
+    sbytes = lib.gnnagg_spmm_scratch_bytes(M, nnz, F)
+    scratch = _get_scratch(out.device, sbytes)
+    rc = lib.gnnagg_spmm_csr_q(rowptr.data_ptr(), _lib.ptr(col), _lib.ptr(value), M, K, nnz, _lib.ptr(codes),
+                               _lib.ptr(params_bf16), seg.data_ptr(), num_segments, bits, out.data_ptr(), out.stride(0),
+                               F, 1 if accumulate else 0, plan.data_ptr(), scratch.data_ptr(), scratch.numel(),
+                               _lib.stream_ptr(out.device))
+    _lib.check(rc, "spmm_csr_q")
+
+
+def SPMM_forward_packed(src: SparseTensor, codes, params_bf16, seg, num_segments: int, bits: int, out: torch.Tensor,
+                        accumulate: bool = True):
+    """SPMM_forward whose dense operand is still in its packed wire form (no counterpart call in the
+    reference, which always unpacks first)."""
+    rowptr, col, value = src.csr()
+    plan = src.get_work_range()
+    if plan.size(0) == 0:
+        plan = build_plan(rowptr, src.nnz())
+        src.set_work_range(plan)
+    spmm_packed(rowptr, col, value, src.sparse_size(1), codes, params_bf16, seg, num_segments, bits, out, plan, accumulate)
+    return None
+
+
+def SPMM_backward_packed(src: SparseTensor, codes, params_bf16, seg, num_segments: int, bits: int, out: torch.Tensor,
+                         accumulate: bool = True):
+    """SPMM_backward (src^T @ operand) with a packed dense operand."""
+    colptr, row_T, value_T = src.storage.colptr(), src.storage.row_T(), src.storage.value_T()
+    plan = src.get_work_range_for_transpose()
+    if plan.size(0) == 0:
+        plan = build_plan(colptr, src.nnz())
+        src.set_work_range_for_transpose(plan)
+    spmm_packed(colptr, row_T, value_T, src.sparse_size(0), codes, params_bf16, seg, num_segments, bits, out, plan,
+                accumulate)
+    return None
+
+
 def SPMM_forward(src: SparseTensor, other: torch.Tensor, out: torch.Tensor, accumulate: bool = True):
     """out += src @ other.  Returns None, like the reference (spmm_kernel.py:45-67).
 

@@ -74,6 +74,21 @@ int gnnagg_spmm_csr_f32(const int64_t *rowptr, const int32_t *col, const float *
                         int32_t accumulate, const void *plan, void *scratch, size_t scratch_bytes,
                         void *stream);
 
+/* K3b + K4 fused: the same SpMM with the dense operand given as a row-packed quantised halo buffer
+ * instead of fp32 rows.  Column index c of the sparse matrix is a wire slot; its feature row is
+ * decoded on the fly as fma(code, scale_c, zero_point_c) with the bf16 wire parameters -- exactly
+ * the value gnnagg_unpack_dequant_rows would have stored -- and enters the same FMA chain, so the
+ * result equals unpack + gnnagg_spmm_csr_f32 bit for bit while the fp32 halo buffer is never
+ * written or read (4F -> F*bits/8 + 4 gathered bytes per nonzero).
+ * Replaces the pair dequantize_tensor_for_all_procs (quantization_arm.cpp:437-479) + spmm on the
+ * receive side of the exchange (model/layers/aggregator.py:83-104, :180-199).
+ *   codes / params_bf16 / seg / P / bits: as produced by gnnagg_quant_pack_rows on the sender and
+ *   laid out by the receiver's own segment prefix; K = seg[P] wire slots.  F % 4 == 0 required. */
+int gnnagg_spmm_csr_q(const int64_t *rowptr, const int32_t *col, const float *val, int64_t M, int64_t K,
+                      int64_t nnz, const uint8_t *codes, const void *params_bf16, const int32_t *seg, int32_t P,
+                      int32_t bits, float *Y, int64_t ldy, int32_t F, int32_t accumulate, const void *plan,
+                      void *scratch, size_t scratch_bytes, void *stream);
+
 /* Same product as gnnagg_spmm_csr_f32 for callers that cannot allocate device memory where they
  * call it (code under a host framework whose allocator may not be used at that point, a plugin
  * that is handed nothing but its operands, a process with a device-memory budget fixed up front):

@@ -30,7 +30,8 @@ def _scale(src, dst, N, V, transpose):
 
 @pytest.mark.parametrize("path", sorted(glob.glob(os.path.join(GOLD, "aggr_*.npz"))),
                          ids=lambda p: os.path.basename(p)[5:-4])
-def test_aggregator_against_reference_run(cuda_lib, path):
+@pytest.mark.parametrize("fuse", [False, True], ids=["unpack_then_spmm", "fused_unpack"])
+def test_aggregator_against_reference_run(cuda_lib, monkeypatch, fuse, path):
     from gnn_benchmark_b200 import Communicator, Quantizer_for_all_procs, TimeRecorder, graphgen
     from gnn_benchmark_b200.aggregator import Aggregator
     from gnn_benchmark_b200.data_manager.DataLoader import build_graph
@@ -41,6 +42,8 @@ def test_aggregator_against_reference_run(cuda_lib, path):
     N = int(begin[-1])
     X, G = g["X"], g["G"]
     s_t, d_t = torch.from_numpy(g["src"]).cuda(), torch.from_numpy(g["dst"]).cuda()
+    import gnn_benchmark_b200.aggregator as agg_mod
+    monkeypatch.setattr(agg_mod, "FUSE_UNPACK", fuse)
     Communicator(bits, is_async=True)
     Quantizer_for_all_procs(P, bits)
     TimeRecorder(1, 1)
@@ -76,7 +79,8 @@ def test_aggregator_against_reference_run(cuda_lib, path):
             np.testing.assert_array_equal(snap["fwd_codes"], g[f"r{r}_fwd_codes"])
             np.testing.assert_array_equal(snap["fwd_params"], g[f"r{r}_fwd_params"])
         # halo rows as received (after dequantisation in int2 mode): bit-exact
-        np.testing.assert_array_equal(snap["fwd_recv"], g[f"r{r}_fwd_recv"])
+        if not (fuse and bits == 2):  # the fused path never materialises the fp32 halo rows
+            np.testing.assert_array_equal(snap["fwd_recv"], g[f"r{r}_fwd_recv"])
         want_out, want_grad = g[f"r{r}_out"], g[f"r{r}_grad"]
         if bits == 32:
             tol_out, tol_grad = 1e-5 * sc_out[b0:b1] + 1e-30, 1e-5 * sc_grad[b0:b1] + 1e-30

@@ -217,3 +217,36 @@ def test_full_size_properties(cuda_lib):
     acc = Ax.clone()
     SPMM_forward(A, y, acc, accumulate=True)
     assert torch.allclose(acc, Ax + Ay, rtol=1e-5, atol=1e-5)
+
+
+@pytest.mark.parametrize("bits", [2, 4, 8])
+@pytest.mark.parametrize("F", [4, 32, 100, 128, 256, 516])
+def test_packed_operand_equals_unpack_then_spmm(cuda_lib, bits, F):
+    """gnnagg_spmm_csr_q (codes decoded inside the SpMM) against gnnagg_unpack_dequant_rows followed by
+    gnnagg_spmm_csr_f32: bit-identical, accumulate on and off, with empty and ragged peer segments."""
+    from gnn_benchmark_b200 import Quantizer_for_all_procs, spmm_kernel
+
+    rng = np.random.default_rng(bits * 1000 + F)
+    seg = [0, 37, 37, 401, 402, 1500]
+    K, M = seg[-1], 1200
+    rowptr, col, val = random_csr(rng, M, K, 7, hubs=2, hub_len=1300)
+    halo = rng.standard_normal((K, F)).astype(np.float32)
+    q = Quantizer_for_all_procs(len(seg) - 1, bits)
+    segd = to_dev(np.asarray(seg, dtype=np.int32))
+    epb = 8 // bits
+    prow = sum((b - a + epb - 1) // epb for a, b in zip(seg[:-1], seg[1:]))
+    codes = torch.zeros(prow, F, dtype=torch.uint8, device="cuda")
+    params = torch.zeros(K, 2, device="cuda")
+    pb = torch.zeros(K, 2, dtype=torch.bfloat16, device="cuda")
+    q.quantize_fp32_to_intX(to_dev(halo), codes, params, segd, params_bf16=pb)
+    unpacked = torch.empty(K, F, device="cuda")
+    q.dequantize_intX_to_fp32(codes, unpacked, params, segd, params_bf16=pb)
+    rp, c, v = to_dev(rowptr, torch.int64), to_dev(col, torch.int32), to_dev(val)
+    plan = spmm_kernel.build_plan(rp, len(col))
+    base = to_dev(rng.standard_normal((M, F)).astype(np.float32))
+    for accumulate in (False, True):
+        want, got = base.clone(), base.clone()
+        spmm_kernel.spmm(rp, c, v, K, unpacked, want, plan, accumulate=accumulate)
+        spmm_kernel.spmm_packed(rp, c, v, K, codes, pb, segd, len(seg) - 1, bits, got, plan, accumulate=accumulate)
+        torch.cuda.synchronize()
+        np.testing.assert_array_equal(got.cpu().numpy().view(np.uint32), want.cpu().numpy().view(np.uint32))
