@@ -51,6 +51,7 @@ def main():
     ap.add_argument("--pre", type=int, default=0)
     ap.add_argument("--epochs", type=int, default=6)
     ap.add_argument("--train-frac", type=float, default=0.01)
+    ap.add_argument("--dropout", type=float, default=0.5)
     ap.add_argument("--seed", type=int, default=20261130)
     args = ap.parse_args()
 
@@ -83,7 +84,7 @@ def main():
         "nodes_test_masks": torch.zeros(0, dtype=torch.int64, device=device),
     }
     cfg = dict(model_name=args.model, in_channels=args.in_channels, hidden_channels=args.hidden,
-               out_channels=args.out_channels, num_layers=args.layers, dropout=0.5, lr=0.01, weight_decay=0.0,
+               out_channels=args.out_channels, num_layers=args.layers, dropout=args.dropout, lr=0.01, weight_decay=0.0,
                num_bits=args.bits, is_pre_delay=bool(args.pre))
     set_random_seed(args.seed)
     model, optimizer = create_model_and_optimizer(cfg, device)
@@ -107,7 +108,7 @@ def main():
             "config": {"model": args.model, "dims": dims, "nodes": args.nodes, "directed_edges_after_symmetrising":
                        int(tsum[1]), "halo": f"{args.bits}-bit" + (" pre/post" if args.pre else ""),
                        "halo_rows_sent_per_exchange": int(tsum[2]), "graph": "Chung-Lu gamma=2.1, relabelled",
-                       "epochs_timed": len(times) - 1, "dropout": 0.5, "optimizer": "Adam lr 0.01"},
+                       "epochs_timed": len(times) - 1, "dropout": args.dropout, "optimizer": "Adam lr 0.01"},
             "losses": [round(x, 5) for x in losses], "epoch_times_s": [round(x, 4) for x in times],
             "peak_mem_gib_max_rank": float(tmax[3]), "setup_s": round(setup_s, 1), "data": "synthetic",
         }), flush=True)

@@ -344,16 +344,21 @@ __global__ void __launch_bounds__(kWarpsPerBlock * 32, min_blocks_per_sm(NV))
 #pragma unroll
             for (int k = 0; k < NV; ++k)
                 if (vok[k]) {
+                    if (QB) {
+                        // four codes of one packed word: shift the row's bit field down, mask every
+                        // byte, then splice each byte under the exponent of 2^23 -- the float
+                        // 8388608 + code -- and subtract 2^23 (exact): no integer-to-float conversion
+                        constexpr uint32_t kMask = ((1u << QB) - 1u) * 0x01010101u;
+                        const uint32_t ws = (wq[u][k] >> shq[u]) & kMask;
 #pragma unroll
-                    for (int i = 0; i < VW; ++i) {
-                        float x;
-                        if (QB) {
-                            const uint32_t code = (wq[u][k] >> (8 * i + shq[u])) & ((1u << QB) - 1u);
-                            x = fmaf((float)code, sq[u], zq[u]);
-                        } else {
-                            x = xr[u][k].v[i];
+                        for (int i = 0; i < VW; ++i) {
+                            const float m = __uint_as_float(__byte_perm(ws, 0x4B000000u, 0x7440 + i));
+                            const float x = fmaf(m - 8388608.0f, sq[u], zq[u]);
+                            acc[k].v[i] = fmaf(av[u], x, acc[k].v[i]);
                         }
-                        acc[k].v[i] = fmaf(av[u], x, acc[k].v[i]);
+                    } else {
+#pragma unroll
+                        for (int i = 0; i < VW; ++i) acc[k].v[i] = fmaf(av[u], xr[u][k].v[i], acc[k].v[i]);
                     }
                 }
         };
