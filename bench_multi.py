@@ -52,50 +52,49 @@ def _gcn_values(graph, comm, world):
 
 def _run_e2e(args, graph, widths, num_bits, is_pre, n, nnz_total, device):
     """The same step through Aggregator with this rank's features and output gradients in pinned
-    HOST memory: per call copy the operand host->device, run, copy the result device->host."""
+    HOST memory: per call copy the operand host->device, run, copy the result device->host, pipelined
+    over three streams (bench.HostPipeline)."""
+    import bench
     from gnn_benchmark_b200.aggregator import Aggregator
 
     Fmax = max(widths)
     host_in = torch.empty(n, Fmax, pin_memory=True).normal_(generator=torch.Generator().manual_seed(1))
     host_out = torch.empty(n, Fmax, pin_memory=True)
-    dev_in = torch.empty(n * Fmax, device=device)
-    moved = 0
+    pipe = bench.HostPipeline(device, n * Fmax)
 
     def step():
-        nonlocal moved
-        moved = 0
+        pipe.h2d = pipe.d2h = 0
         for F in widths:
             hin = host_in.view(-1)[: n * F].view(n, F)
             hout = host_out.view(-1)[: n * F].view(n, F)
-            x = dev_in[: n * F].view(n, F)
             ctx = SimpleNamespace()
-            x.copy_(hin, non_blocking=True)
-            out = Aggregator.forward(ctx, graph, x, 0, num_bits, is_pre, True)
-            hout.copy_(out, non_blocking=True)
-            x.copy_(hin, non_blocking=True)
-            grad = Aggregator.backward(ctx, x)[1]
-            hout.copy_(grad, non_blocking=True)
-            moved += 2 * n * F * 4
+            pipe.call(hin, hout, (n, F), lambda x, y: Aggregator.forward(ctx, graph, x, 0, num_bits, is_pre, True))
+            pipe.call(hin, hout, (n, F), lambda x, y: Aggregator.backward(ctx, x)[1])
 
     step()
+    pipe.drain()
     torch.cuda.synchronize()
     dist.barrier()
     steps = max(1, min(args.steps, 3))
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e0.record()
+    with torch.cuda.stream(pipe.s_in):
+        e0.record()
     for _ in range(steps):
         step()
-    e1.record()
+    pipe.drain()
+    with torch.cuda.stream(pipe.s_out):
+        e1.record()
     torch.cuda.synchronize()
     dist.barrier()
     t = torch.tensor([e0.elapsed_time(e1) / 1e3 / steps], dtype=torch.float64, device=device)
     dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    b = torch.tensor([float(moved)], dtype=torch.float64, device=device)
+    b = torch.tensor([float(pipe.h2d)], dtype=torch.float64, device=device)
     dist.all_reduce(b, op=dist.ReduceOp.SUM)
-    del host_in, host_out, dev_in
+    del host_in, host_out, pipe
     return {"value": 2 * len(widths) * nnz_total / float(t.item()), "unit": "edges/s",
             "h2d_bytes_per_step": int(b.item()), "d2h_bytes_per_step": int(b.item()),
-            "ms_per_step": float(t.item()) * 1e3, "steps": steps}
+            "ms_per_step": float(t.item()) * 1e3, "steps": steps,
+            "pipeline": "h2d / kernels / d2h on three streams, two buffer pairs"}
 
 
 def run_multi_gpu(args):
@@ -104,12 +103,14 @@ def run_multi_gpu(args):
     from gnn_benchmark_b200.aggregator import Aggregator
     from gnn_benchmark_b200.data_manager.DataLoader import build_graph
 
-    num_bits = int(os.environ.get("GNNAGG_BENCH_BITS", "32"))
+    num_bits = int(os.environ.get("GNNAGG_BENCH_BITS", "32"))  # halo format of the headline number
     is_pre = os.environ.get("GNNAGG_BENCH_PRE", "0") == "1"
     comm = Communicator(num_bits, is_async=True)
     rank, world = comm.init_dist_group("nccl")
     device = torch.device("cuda", torch.cuda.current_device())
-    Quantizer_for_all_procs(world, num_bits)
+    # the graph always carries the packed-halo buffers, so the 2-bit variant can be timed on it too
+    plan_bits = num_bits if num_bits in (2, 4, 8) else 2
+    Quantizer_for_all_procs(world, plan_bits)
     TimeRecorder(1, 1, enabled=False)
     widths = bench.WIDTHS
     scale = bench.SCALE + int(math.ceil(math.log2(world)))
@@ -120,7 +121,7 @@ def run_multi_gpu(args):
     local, remote = graphgen.partition_edges(src, dst, begin, rank)
     nnz = int(local.shape[1] + remote.shape[1])  # edges aggregated by this rank per pass
     del src, dst
-    graph = build_graph(local, remote, begin, rank, world, max(widths), num_bits, is_pre, device=device)
+    graph = build_graph(local, remote, begin, rank, world, max(widths), plan_bits, is_pre, device=device)
     del local, remote
     torch.cuda.empty_cache()
     if not is_pre:
@@ -133,11 +134,30 @@ def run_multi_gpu(args):
     X = {F: torch.randn(n, F, device=device, generator=g) for F in widths}
     G = {F: torch.randn(n, F, device=device, generator=g) for F in widths}
 
-    def step():
+    def step(bits=num_bits):
         for F in widths:
             ctx = SimpleNamespace()
-            Aggregator.forward(ctx, graph, X[F], 0, num_bits, is_pre, True)
+            Aggregator.forward(ctx, graph, X[F], 0, bits, is_pre, True)
             Aggregator.backward(ctx, G[F])
+
+    def time_variant(bits, steps=3):
+        """ms per step (max over ranks) with another halo format on the same graph."""
+        comm.num_bits = bits
+        for _ in range(2):
+            step(bits)
+        torch.cuda.synchronize()
+        dist.barrier()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        for _ in range(steps):
+            step(bits)
+        b.record()
+        torch.cuda.synchronize()
+        dist.barrier()
+        t = torch.tensor([a.elapsed_time(b) / steps], dtype=torch.float64, device=device)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        comm.num_bits = num_bits
+        return float(t.item())
 
     warmup = max(args.warmup, 3)
     for _ in range(warmup):
@@ -189,6 +209,12 @@ def run_multi_gpu(args):
         nv = {"exchange_ms": float(t_x.item()) * 1e3, "bytes_per_rank_per_direction": int(sent_t.item()),
               "achieved_gbs": gbs, "frac_of_measured_770": gbs / 770.0, "frac_of_nominal_900": gbs / 900.0, "F": F}
 
+    variants = None
+    if world > 1 and num_bits == 32:
+        ms2 = time_variant(2)
+        variants = {"int2_halo": {"ms_per_step": ms2, "value": edges_per_step / (ms2 / 1e3), "unit": "edges/s",
+                                  "note": "per-row min/max 2-bit codes + bf16 parameters on the wire (the "
+                                          "reference's quantised mode), unpack fused into the receive-side SpMM"}}
     e2e = _run_e2e(args, graph, widths, num_bits, is_pre, n, float(tot[1].item()), device)
     clocks = clk.summary()
     if rank == 0:
@@ -209,7 +235,7 @@ def run_multi_gpu(args):
                          "achieved": by / t_step / 1e9, "peak": peak, "unit": "GB/s", "frac": by / t_step / 1e9 / peak,
                          "peak_kind": peak_kind + " copy bandwidth", "traffic": None,
                          "note": "whole step including the exchange; SpMM algorithmic bytes only"},
-            "nvlink": nv, "cpu_baseline": None,
+            "nvlink": nv, "variants": variants, "cpu_baseline": None,
         }
         print(json.dumps(line), flush=True)
     dist.barrier()
