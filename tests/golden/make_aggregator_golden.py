@@ -1,6 +1,7 @@
 """Golden vectors of the reference's OWN Aggregator / Communicator / DistSAGE, run here on CPU.
 
     python tests/golden/make_aggregator_golden.py [reference_root]
+    python tests/golden/make_aggregator_golden.py gcn [reference_root]   # train_gcn_config1.npz (minutes)
 
 What runs: the unmodified Python of the reference (model/layers/aggregator.py, communicator.py,
 quantizer.py, data_manager/*, model/ops/spmm_kernel.py, model/DistSAGE.py, model/layers/sageconv.py)
@@ -343,6 +344,103 @@ def train_worker(rank, P, port, cfg, ref_root, out_dir):
     dist.destroy_process_group()
 
 
+def gcn_config1_worker(rank, P, port, cfg, ref_root, out_dir):
+    """BASELINE configuration 1 at full size: 2-layer GCN, Erdos-Renyi 131 072 nodes, average degree 16,
+    self-loops, symmetric normalisation, 2 contiguous blocks, F 128 -> 128 -> 16, Adam lr 0.01, fp32
+    halo, 20 epochs.  The reference has no GCN layer; the layer below wraps the REFERENCE's Aggregator
+    exactly as gnn_benchmark_b200.model.DistGCNConv wraps the CUDA one (row scaling by d^-1/2 before and
+    after the aggregation; transform first when in > out)."""
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=P)
+    torch.set_num_threads(4)
+    install_shims(ref_root)
+    import torch.nn.functional as Fn
+    from communicator import Communicator
+    from quantizer import Quantizer_for_all_procs
+    from time_recorder import TimeRecorder
+    from model.layers.aggregator import Aggregator
+    from gnn_benchmark_b200 import graphgen
+
+    class RefGCNConv(torch.nn.Module):
+        def __init__(self, cin, cout):
+            super().__init__()
+            self.cin, self.cout = cin, cout
+            self.lin = torch.nn.Linear(cin, cout, bias=False)
+            self.bias = torch.nn.Parameter(torch.zeros(cout))
+
+        def reset_parameters(self):
+            torch.nn.init.xavier_uniform_(self.lin.weight)
+            torch.nn.init.zeros_(self.bias)
+
+        def forward(self, graph, x, layer):
+            dinv = graph.in_degrees.rsqrt()
+            first = self.cin > self.cout
+            h = self.lin(x) if first else x
+            h = Aggregator.apply(graph, h * dinv, layer, 32, False, self.training)
+            h = h * dinv
+            if not first:
+                h = self.lin(h)
+            return h + self.bias
+
+    class RefGCN(torch.nn.Module):
+        def __init__(self, dims):
+            super().__init__()
+            self.convs = torch.nn.ModuleList(RefGCNConv(dims[i], dims[i + 1]) for i in range(len(dims) - 1))
+
+        def forward(self, graph, x):
+            for i, conv in enumerate(self.convs[:-1]):
+                x = Fn.relu(conv(graph, x, i))
+            return Fn.log_softmax(self.convs[-1](graph, x, len(self.convs) - 1), dim=1)
+
+    c = Communicator(32, is_async=True)
+    c.rank, c.world_size = rank, P
+    Quantizer_for_all_procs(P, 32)
+    n = cfg["nodes"]
+    src, dst = graphgen.erdos_renyi_edges(n, n * cfg["avg_degree"] // 2, seed=cfg["graph_seed"], device="cpu")
+    src, dst = graphgen.symmetrize(src, dst, n, self_loops=True)
+    begin = graphgen.contiguous_partitions(n, P)
+    local, remote = graphgen.partition_edges(src, dst, begin, rank)
+    g = torch.Generator().manual_seed(cfg["graph_seed"] + 1)
+    X = torch.randn(n, cfg["dims"][0], generator=g)
+    labels = torch.randint(0, cfg["dims"][-1], (n,), generator=g)
+    train_mask = torch.rand(n, generator=g) < 0.5
+    b0, b1 = int(begin[rank]), int(begin[rank + 1])
+    losses = []
+    with contextlib.redirect_stdout(io.StringIO()):
+        torch.manual_seed(cfg["random_seed"])
+        model = RefGCN(cfg["dims"])
+        for conv in model.convs:
+            conv.reset_parameters()
+        ddp = torch.nn.parallel.DistributedDataParallel(model)
+        opt = torch.optim.Adam(ddp.parameters(), lr=0.01)
+        graph = build_reference_graph(local.numpy(), remote.numpy(), begin.numpy(), rank, P, max(cfg["dims"]), 32, False)
+        TimeRecorder(len(cfg["dims"]) - 1, cfg["num_epochs"])
+        x, y = X[b0:b1].clone(), labels[b0:b1].clone()
+        tm = torch.nonzero(train_mask[b0:b1]).view(-1)
+        for epoch in range(cfg["num_epochs"]):
+            ddp.train()
+            opt.zero_grad()
+            out = ddp(graph, x)
+            loss = Fn.nll_loss(out[tm], y[tm])
+            loss.backward()
+            opt.step()
+            losses.append(float(loss.detach()))
+            TimeRecorder.ctx.next_epoch()
+    np.save(os.path.join(out_dir, f"_tmp_gcn_r{rank}.npy"), np.array(losses, dtype=np.float64))
+    dist.barrier()
+    if rank == 0:
+        merged = {k: np.array(v) for k, v in cfg.items() if k != "name"}
+        for r in range(P):
+            pth = os.path.join(out_dir, f"_tmp_gcn_r{r}.npy")
+            merged[f"r{r}_losses"] = np.load(pth)
+            os.unlink(pth)
+        np.savez_compressed(os.path.join(out_dir, "train_gcn_config1.npz"), **merged)
+    dist.destroy_process_group()
+
+
+GCN_CONFIG1 = dict(name="gcn_config1", nodes=131072, avg_degree=16, dims=[128, 128, 16], num_epochs=20, random_seed=4321,
+                   graph_seed=20261126)
+
 AGGR_CASES = [
     # name, seed, n_per, deg, F, bits, is_pre
     ("plain_fp32_p2", 11, 150, 5, 128, 32, False),
@@ -379,5 +477,14 @@ def main():
         print("wrote train_%s.npz" % cfg["name"])
 
 
+def main_gcn():
+    ref_root = sys.argv[2] if len(sys.argv) > 2 else "/root/reference"
+    mp.spawn(gcn_config1_worker, args=(2, 29690, GCN_CONFIG1, ref_root, HERE), nprocs=2, join=True)
+    print("wrote train_gcn_config1.npz")
+
+
 if __name__ == "__main__":
-    main()
+    if len(sys.argv) > 1 and sys.argv[1] == "gcn":
+        main_gcn()
+    else:
+        main()

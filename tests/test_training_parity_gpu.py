@@ -82,7 +82,87 @@ def _worker(rank, P, port, path, out_dir):
     dist.destroy_process_group()
 
 
-@pytest.mark.parametrize("path", sorted(glob.glob(os.path.join(GOLD, "train_*.npz"))),
+def _gcn_worker(rank, P, port, path, out_dir):
+    import torch.distributed as dist
+
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    torch.cuda.set_device(0)
+    dist.init_process_group("gloo", rank=rank, world_size=P)
+    real_a2a = dist.all_to_all_single
+
+    class _Done:
+        def wait(self):
+            return True
+
+    def staged_a2a(output, input, output_split_sizes=None, input_split_sizes=None, group=None, async_op=False):
+        if not input.is_cuda:
+            return real_a2a(output, input, output_split_sizes, input_split_sizes, group=group, async_op=async_op)
+        out_cpu = torch.empty(output.shape, dtype=output.dtype)
+        real_a2a(out_cpu, input.cpu(), output_split_sizes, input_split_sizes)
+        output.copy_(out_cpu)
+        return _Done() if async_op else None
+
+    dist.all_to_all_single = staged_a2a
+    from gnn_benchmark_b200 import Communicator, Quantizer_for_all_procs, TimeRecorder, graphgen
+    from gnn_benchmark_b200.data_manager.DataLoader import build_graph
+    from gnn_benchmark_b200.model import create_model_and_optimizer, set_random_seed
+    from gnn_benchmark_b200.train import train
+
+    g = np.load(path)
+    n, dims, epochs = int(g["nodes"]), g["dims"].tolist(), int(g["num_epochs"])
+    c = Communicator(32, is_async=True)
+    c.rank, c.world_size = rank, P
+    Quantizer_for_all_procs(P, 32)
+    TimeRecorder(len(dims) - 1, epochs)
+    # the same seeded generators the golden script used, on the CPU
+    src, dst = graphgen.erdos_renyi_edges(n, n * int(g["avg_degree"]) // 2, seed=int(g["graph_seed"]), device="cpu")
+    src, dst = graphgen.symmetrize(src, dst, n, self_loops=True)
+    begin = graphgen.contiguous_partitions(n, P)
+    local, remote = graphgen.partition_edges(src, dst, begin, rank)
+    gen = torch.Generator().manual_seed(int(g["graph_seed"]) + 1)
+    X = torch.randn(n, dims[0], generator=gen)
+    labels = torch.randint(0, dims[-1], (n,), generator=gen)
+    train_mask = torch.rand(n, generator=gen) < 0.5
+    graph = build_graph(local, remote, begin, rank, P, max(dims), 32, False, device="cuda")
+    cfg = dict(model_name="gcn", in_channels=dims[0], hidden_channels=dims[1], out_channels=dims[-1],
+               num_layers=len(dims) - 1, dropout=0.0, lr=0.01, weight_decay=0.0, num_bits=32, is_pre_delay=False)
+    set_random_seed(int(g["random_seed"]))
+    model, optimizer = create_model_and_optimizer(cfg, device="cuda")
+    b0, b1 = int(begin[rank]), int(begin[rank + 1])
+    data = {
+        "graph": graph,
+        "nodes_features": X[b0:b1].cuda(),
+        "nodes_labels": labels[b0:b1].cuda(),
+        "nodes_train_masks": torch.nonzero(train_mask[b0:b1]).view(-1).cuda(),
+        "nodes_valid_masks": torch.zeros(0, dtype=torch.int64, device="cuda"),
+        "nodes_test_masks": torch.zeros(0, dtype=torch.int64, device="cuda"),
+    }
+    losses, _ = train(model, data, optimizer, epochs, 32, eval_every_epoch=False, log=None)
+    np.save(os.path.join(out_dir, f"gcn_r{rank}.npy"), np.array(losses))
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def test_gcn_configuration_1_against_reference_aggregator_run(cuda_lib, tmp_path):
+    """BASELINE configuration 1 at full size (131 072-node Erdos-Renyi graph, 2 ranks, 2-layer GCN
+    128 -> 128 -> 16, Adam lr 0.01, fp32 halo, 20 epochs): the golden losses come from the reference's own
+    Aggregator / Communicator / plan builders on CPU under the same GCN wrapper."""
+    import torch.multiprocessing as mp
+
+    path = os.path.join(GOLD, "train_gcn_config1.npz")
+    if not os.path.isfile(path):
+        pytest.skip("tests/golden/train_gcn_config1.npz not generated")
+    g = np.load(path)
+    port = 29750 + (os.getpid() % 200)
+    mp.spawn(_gcn_worker, args=(2, port, path, str(tmp_path)), nprocs=2, join=True)
+    for r in range(2):
+        got = np.load(os.path.join(str(tmp_path), f"gcn_r{r}.npy"))
+        want = g[f"r{r}_losses"]
+        assert got.shape == want.shape == (20,)
+        np.testing.assert_allclose(got, want, rtol=0, atol=1e-4)
+
+
+@pytest.mark.parametrize("path", sorted(glob.glob(os.path.join(GOLD, "train_sage_*.npz"))),
                          ids=lambda p: os.path.basename(p)[6:-4])
 def test_loss_curve_against_reference_run(cuda_lib, tmp_path, path):
     import torch.multiprocessing as mp
