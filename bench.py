@@ -41,6 +41,9 @@ SEED = 20261127
 SCALE = int(os.environ.get("GNNAGG_BENCH_SCALE", "22"))  # 22 is the benchmark; smaller only for dry runs
 EDGE_FACTOR = 16
 FALLBACK_HBM_GBS = 6650.0
+# dram__bytes_read.sum + dram__bytes_write.sum of ONE spmm_chunk_kernel launch on the default workload
+# (scale 22), from a one-pass ncu capture at full size (profiles/spmm_dram_traffic_rmat22.md); keyed by F
+NCU_DRAM_BYTES_PER_LAUNCH = {256: 76.16e9, 128: 31.27e9, 32: 4.73e9}
 
 
 def measured_peak_gbs():
@@ -300,7 +303,9 @@ def run_single_gpu(args):
         "bound": "hbm", "kernel": f"spmm_chunk_kernel (F={top}, forward and transposed launches averaged)",
         "achieved": per_width[top]["gbs"], "peak": peak, "unit": "GB/s", "frac": per_width[top]["gbs"] / peak,
         "peak_kind": peak_kind + " copy bandwidth, burst",
-        "traffic": None,
+        "traffic": NCU_DRAM_BYTES_PER_LAUNCH.get(top) if SCALE == 22 else None,
+        "traffic_gbs": (NCU_DRAM_BYTES_PER_LAUNCH[top] / (per_width[top]["ms"] / 1e3) / 1e9
+                        if SCALE == 22 and top in NCU_DRAM_BYTES_PER_LAUNCH else None),
         "by_width": {str(F): {"ms": round(per_width[F]["ms"], 4), "gbs": round(per_width[F]["gbs"], 1),
                               "frac": round(per_width[F]["gbs"] / peak, 4)} for F in WIDTHS},
     }

@@ -105,7 +105,10 @@ def run_multi_gpu(args):
 
     num_bits = int(os.environ.get("GNNAGG_BENCH_BITS", "32"))  # halo format of the headline number
     is_pre = os.environ.get("GNNAGG_BENCH_PRE", "0") == "1"
-    comm = Communicator(num_bits, is_async=True)
+    # GNNAGG_BENCH_PIPELINE=1: fp32 halo exchanged peer by peer, each peer's rows aggregated on arrival
+    # (measured equal to the one-shot all-to-all at 2 and 4 GPUs, so the one-shot exchange is the default)
+    pipeline = os.environ.get("GNNAGG_BENCH_PIPELINE", "0") == "1"
+    comm = Communicator(num_bits, is_async=True, pipeline_peers=pipeline)
     rank, world = comm.init_dist_group("nccl")
     device = torch.device("cuda", torch.cuda.current_device())
     # the graph always carries the packed-halo buffers, so the 2-bit variant can be timed on it too
@@ -222,6 +225,8 @@ def run_multi_gpu(args):
         cfg = bench.workload_config(world)
         cfg.update({"rows_per_gpu": n, "nnz_total": int(tot[1].item()), "partitions": world,
                     "halo_rows_sent_total": int(tot[2].item()), "halo": f"{num_bits}-bit" + (" pre/post" if is_pre else ""),
+                    "exchange": "peer-by-peer, aggregated on arrival" if (pipeline and num_bits == 32 and not is_pre)
+                    else "one all-to-all per aggregation",
                     "setup_s": round(setup_s, 1), "parallelism": f"1-D vertex partition x{world}"})
         by = sum(bench.spmm_algorithmic_bytes(n, nnz, F) for F in widths) * 2
         line = {

@@ -63,6 +63,43 @@ def _rec():
     return TimeRecorder.ctx
 
 
+def _prefix(splits):
+    out = [0]
+    for x in splits:
+        out.append(out[-1] + x)
+    return out
+
+
+def _remote_parts(graph, world_size):
+    """remote_adj_t cut into one matrix per source peer (columns = that peer's halo slots, renumbered
+    from 0), built on first use and cached on the graph.  Rows keep CSR order, so applying the parts
+    one after the other in ascending peer order is the same FMA chain as the whole matrix."""
+    parts = getattr(graph, "_remote_parts", None)
+    if parts is None:
+        from .sparse import SparseTensor
+        rowptr, col, val = graph.remote_adj_t.csr()
+        n = graph.remote_adj_t.sparse_size(0)
+        rows = torch.repeat_interleave(torch.arange(n, device=col.device), rowptr[1:] - rowptr[:-1])
+        offs = _prefix(graph.comm_splits.recv_splits)
+        parts = []
+        for p in range(world_size):
+            lo, hi = offs[p], offs[p + 1]
+            if hi == lo:
+                parts.append(None)
+                continue
+            m = (col >= lo) & (col < hi)
+            parts.append(SparseTensor(row=rows[m], col=col[m].to(torch.int64) - lo, value=val[m],
+                                      sparse_sizes=(n, hi - lo), is_sorted=True))
+        graph._remote_parts = parts
+    return parts
+
+
+def _pipelined(num_bits, is_pre_delay, is_training, world_size) -> bool:
+    comm = Communicator.ctx
+    fp32 = comm is not None and (comm.num_bits == 32 or not is_training)
+    return world_size > 1 and fp32 and not is_pre_delay and comm.pipeline_peers
+
+
 class Aggregator(torch.autograd.Function):
     @staticmethod
     def forward(ctx, graph, local_nodes_feat, layer, num_bits: int, is_pre_delay: bool, is_training: bool):
@@ -79,7 +116,17 @@ class Aggregator(torch.autograd.Function):
         packed = world_size > 1 and is_training and _packed(num_bits, graph)
 
         comm_handle = None
-        if world_size > 1:
+        rounds = None
+        if _pipelined(num_bits, is_pre_delay, is_training, world_size):
+            # peer-by-peer exchange: every peer's rows are aggregated as soon as they are in
+            t = rec.start() if rec else None
+            _resize(graph, feat_len, num_bits)
+            gather_rows(x, _send_idx(graph), graph.comm_buf.send_buf)
+            if rec:
+                rec.record_prepare_comm_time(t)
+            rounds = Communicator.ctx.exchange_by_peer(graph.comm_buf.send_buf, graph.comm_buf.recv_buf,
+                                                       graph.comm_splits.send_splits, graph.comm_splits.recv_splits)
+        elif world_size > 1:
             t = rec.start() if rec else None
             _resize(graph, feat_len, num_bits)
             send_buf = graph.comm_buf.send_buf
@@ -111,6 +158,21 @@ class Aggregator(torch.autograd.Function):
 
         if comm_handle is not None:
             comm_handle.wait()
+
+        if rounds is not None:
+            t = rec.start() if rec else None
+            parts = _remote_parts(graph, world_size)
+            offs = _prefix(graph.comm_splits.recv_splits)
+            for src, works in rounds:
+                for w in works:
+                    w.wait()
+                if parts[src] is not None:
+                    SPMM_forward(parts[src], graph.comm_buf.recv_buf[offs[src]:offs[src + 1]], out)
+            if rec:
+                rec.record_remote_aggregate_time(t)
+                rec.record_total_convolution_time(t_total)
+                rec.next_layer()
+            return out
 
         num_recv_nodes = sum(graph.comm_splits.recv_splits) if world_size > 1 else 0
         fused = packed and FUSE_UNPACK and feat_len % 4 == 0
@@ -156,7 +218,24 @@ class Aggregator(torch.autograd.Function):
         packed = world_size > 1 and _packed(num_bits, graph)
 
         comm_handle = None
-        if world_size > 1:
+        rounds = None
+        if _pipelined(num_bits, is_pre_delay, True, world_size):
+            # the block of halo gradients that goes back to a peer is computed right before its round
+            _resize(graph, feat_len, num_bits)
+            parts = _remote_parts(graph, world_size)
+            offs = _prefix(graph.comm_splits.recv_splits)
+            t = rec.start() if rec else None
+
+            def make_block(dst):
+                if parts[dst] is not None:
+                    SPMM_backward(parts[dst], g, graph.comm_buf.recv_buf[offs[dst]:offs[dst + 1]], accumulate=False)
+
+            rounds = Communicator.ctx.exchange_by_peer(graph.comm_buf.recv_buf, graph.comm_buf.send_buf,
+                                                       graph.comm_splits.recv_splits, graph.comm_splits.send_splits,
+                                                       before_send=make_block)
+            if rec:
+                rec.record_pre_aggregate_time(t)
+        elif world_size > 1:
             _resize(graph, feat_len, num_bits)
             # the two buffers swap roles: recv_buf is sent, send_buf receives
             remote_nodes_grad_buf = graph.comm_buf.recv_buf
@@ -180,6 +259,10 @@ class Aggregator(torch.autograd.Function):
 
         if comm_handle is not None:
             comm_handle.wait()
+        if rounds is not None:
+            for _, works in rounds:
+                for w in works:
+                    w.wait()
 
         num_recv_nodes = sum(graph.comm_splits.send_splits) if world_size > 1 else 0
         fused = packed and FUSE_UNPACK and feat_len % 4 == 0

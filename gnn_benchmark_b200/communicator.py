@@ -37,10 +37,14 @@ class _Handles(object):
 class Communicator(object):
     ctx = None
 
-    def __init__(self, num_bits=32, is_async=True, use_barrier=False) -> None:
+    def __init__(self, num_bits=32, is_async=True, use_barrier=False, pipeline_peers=False) -> None:
         self.num_bits = num_bits
         self.is_async = is_async
         self.use_barrier = use_barrier
+        # fp32 halo only: exchange peer by peer and aggregate each peer's rows as they arrive (see
+        # exchange_by_peer).  Off by default because the peers' contributions are then added in arrival
+        # order, not in the reference's ascending-peer order (same terms, fp32 re-association).
+        self.pipeline_peers = pipeline_peers
         self.world_size = -1
         self.rank = -1
         Communicator.ctx = self
@@ -101,6 +105,37 @@ class Communicator(object):
         if TimeRecorder.ctx:
             TimeRecorder.ctx.record_communication_time(t)
         return handle
+
+    def exchange_by_peer(self, send_buf, recv_buf, send_splits, recv_splits, before_send=None):
+        """The fp32 all-to-all as P-1 rounds of one send + one receive (round s: send to rank+s, receive
+        from rank-s), each a grouped NCCL send/recv queued on the communication stream.  Returns
+        [(source_peer, [work, ...]), ...] in arrival order; waiting on a round's works orders the
+        caller's stream after that round only, so the rows of one peer can be aggregated while the
+        next peer's rows are still in flight.  `before_send(dst)` (optional) is called right before
+        round s is queued, to produce the block that goes to `dst` (backward direction)."""
+        P, r = dist.get_world_size(), dist.get_rank()
+        so = [0]
+        for x in send_splits:
+            so.append(so[-1] + x)
+        ro = [0]
+        for x in recv_splits:
+            ro.append(ro[-1] + x)
+        rounds = []
+        rec = TimeRecorder.ctx
+        t = rec.start() if rec else None
+        for s in range(1, P):
+            dst, src = (r + s) % P, (r - s) % P
+            if before_send is not None:
+                before_send(dst)
+            ops = []
+            if send_splits[dst]:
+                ops.append(dist.P2POp(dist.isend, send_buf[so[dst]:so[dst + 1]], dst))
+            if recv_splits[src]:
+                ops.append(dist.P2POp(dist.irecv, recv_buf[ro[src]:ro[src + 1]], src))
+            rounds.append((src, dist.batch_isend_irecv(ops) if ops else []))
+        if rec:
+            rec.record_communication_time(t)
+        return rounds
 
     def comm_with_fp16(self, comm_splits: CommSplits, comm_buf: CommBuffer, direction: str):
         """bf16 on the wire (communicator.py:111-143).  The reference widens the received buffer

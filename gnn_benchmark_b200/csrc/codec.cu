@@ -89,6 +89,32 @@ __device__ __forceinline__ uint32_t bf16_bits(float v) {
     return (uint32_t)__bfloat16_as_ushort(__float2bfloat16_rn(v));
 }
 
+// Exact (true division) encoding of one packed row held in registers: the rarely taken twin of the
+// estimate-based loop in quant_pack_vec_kernel; it runs under a warp-uniform branch of its own.
+template <int BITS, int NV, int GQ>
+__device__ __forceinline__ void quant_exact_rows(const float4 (&xv)[8 / BITS][NV], const float (&zp)[8 / BITS],
+                                              const float (&sc)[8 / BITS], int cnt, int gl, int FV, bool signed_cvt,
+                                              uint32_t (&words)[NV]) {
+    constexpr int EPB = 8 / BITS;
+#pragma unroll
+    for (int k = 0; k < NV; ++k) {
+        uint32_t b0 = 0, b1 = 0, b2 = 0, b3 = 0;
+        if (gl + GQ * k < FV) {
+#pragma unroll
+            for (int t = 0; t < EPB; ++t) {
+                if (t < cnt) {
+                    const int sh = (EPB - 1 - t) * BITS;
+                    b0 |= encode(xv[t][k].x, zp[t], sc[t], signed_cvt) << sh;
+                    b1 |= encode(xv[t][k].y, zp[t], sc[t], signed_cvt) << sh;
+                    b2 |= encode(xv[t][k].z, zp[t], sc[t], signed_cvt) << sh;
+                    b3 |= encode(xv[t][k].w, zp[t], sc[t], signed_cvt) << sh;
+                }
+            }
+        }
+        words[k] = (b0 & 255u) | ((b1 & 255u) << 8) | ((b2 & 255u) << 16) | ((b3 & 255u) << 24);
+    }
+}
+
 // ---- fast path: F % 4 == 0, F <= 512, 16-byte aligned rows ------------------------------
 // GQ lanes own one packed row (GQ = 8, 16 or 32 by width), so a warp works on 32/GQ packed rows at a
 // time and narrow rows do not leave lanes idle; NV float4 per lane and input row (NV > 1 only with
@@ -190,38 +216,47 @@ __global__ void __launch_bounds__(kCodecWarps * 32, (NV == 1 ? 8 : (NV == 2 ? 5 
         }
 
         // code = round-half-even(fl((x - zp) / scale)), IEEE division.  The quotient is estimated as
-        // (x - zp) * fl(1/scale) -- within 2 ulp of the true quotient -- and the exact division is done
-        // only when the estimate is within 8 ulp of a rounding boundary k + 0.5 (or out of the code
-        // range, or not finite): elsewhere both round to the same integer.
+        // (x - zp) * fl(1/scale) -- within 2 ulp of the true quotient -- which rounds to the same integer
+        // as the exact quotient unless it lies within 8 ulp of a rounding boundary k + 0.5 (or out of the
+        // code range, or is not finite).  The whole packed row is encoded from the estimate first; only if
+        // some element of the group was that close to a boundary (about one packed row in a hundred for
+        // 2-bit codes) is the row encoded again with true divisions, so the hot loop holds no division.
         constexpr float kBound = LEVELS + 1.0f;
         constexpr float kThr = 0.5f - kBound * 9.5367431640625e-07f;  // 0.5 - 2^-20 * bound
-        auto enc = [&](float x, int t) -> uint32_t {
-            const float d = __fsub_rn(x, zp[t]);
-            float q = __fmul_rn(d, rinv[t]);
+        bool unsure = false;
+        auto enc_fast = [&](float x, int t) -> uint32_t {
+            const float q = __fmul_rn(__fsub_rn(x, zp[t]), rinv[t]);
             const float k = rintf(q);
-            const bool sure = fast[t] && (fabsf(__fsub_rn(q, k)) < kThr) && (fabsf(q) <= kBound);
-            if (!sure) q = __fdiv_rn(d, sc[t]);
-            return params_given ? (uint32_t)__float2int_rn(q) : __float2uint_rn(q);
+            unsure = unsure || !((fabsf(__fsub_rn(q, k)) < kThr) && (fabsf(q) <= kBound));
+            return params_given ? (uint32_t)__float2int_rn(k) : __float2uint_rn(k);
         };
-        uint32_t *out = reinterpret_cast<uint32_t *>(codes + R * (int64_t)F);
+        uint32_t words[NV];
+#pragma unroll
+        for (int t = 0; t < EPB; ++t) unsure = unsure || (t < cnt && !fast[t]);
 #pragma unroll
         for (int k = 0; k < NV; ++k) {
-            const int vi = gl + GQ * k;
-            if (vi < FV) {
-                uint32_t b0 = 0, b1 = 0, b2 = 0, b3 = 0;
+            uint32_t b0 = 0, b1 = 0, b2 = 0, b3 = 0;
+            if (gl + GQ * k < FV) {
 #pragma unroll
                 for (int t = 0; t < EPB; ++t) {
                     if (t < cnt) {
                         const int sh = (EPB - 1 - t) * BITS;
-                        b0 |= enc(xv[t][k].x, t) << sh;
-                        b1 |= enc(xv[t][k].y, t) << sh;
-                        b2 |= enc(xv[t][k].z, t) << sh;
-                        b3 |= enc(xv[t][k].w, t) << sh;
+                        b0 |= enc_fast(xv[t][k].x, t) << sh;
+                        b1 |= enc_fast(xv[t][k].y, t) << sh;
+                        b2 |= enc_fast(xv[t][k].z, t) << sh;
+                        b3 |= enc_fast(xv[t][k].w, t) << sh;
                     }
                 }
-                __stcs(out + vi, (b0 & 255u) | ((b1 & 255u) << 8) | ((b2 & 255u) << 16) | ((b3 & 255u) << 24));
             }
+            words[k] = (b0 & 255u) | ((b1 & 255u) << 8) | ((b2 & 255u) << 16) | ((b3 & 255u) << 24);
         }
+        if (__any_sync(gmask, unsure)) {
+            quant_exact_rows<BITS, NV, GQ>(xv, zp, sc, cnt, gl, FV, params_given != 0, words);
+        }
+        uint32_t *out = reinterpret_cast<uint32_t *>(codes + R * (int64_t)F);
+#pragma unroll
+        for (int k = 0; k < NV; ++k)
+            if (gl + GQ * k < FV) __stcs(out + gl + GQ * k, words[k]);
     }
 }
 

@@ -259,8 +259,16 @@ __global__ void __launch_bounds__(kWarpsPerBlock * 32, min_blocks_per_sm(NV))
     // start the chain from the old row.  Only the chunk that FINISHES a row (r < r1) reads and
     // writes its Y, so a hub row cut across chunks has one reader/writer and no race; the chunks
     // before it start from zero and park their sums.
-    load_y(r < r1 ? r : (int)M, acc);
-    load_y(r + 1 < r1 ? r + 1 : (int)M, ynext);
+    // Rows without nonzeros are neither read nor written when accumulating (a remote or scatter
+    // matrix leaves most rows empty): row r+1 is known to be empty when its end equals row r's end.
+    auto next_row_needs_y = [&]() -> bool {
+        if (!ACC || r + 1 >= r1) return false;
+        const int w = r + 1 - rbase;
+        if (w >= 32) return true;  // its end is outside the prefetched window: fetch to be safe
+        return __shfl_sync(kFullMask, row_ends, w) > next_end;
+    };
+    load_y((r < r1 && !(row_start >= 0 && next_end == row_start)) ? r : (int)M, acc);
+    load_y(next_row_needs_y() ? r + 1 : (int)M, ynext);
 
     auto advance_row = [&]() {
         row_start = next_end;
@@ -272,7 +280,7 @@ __global__ void __launch_bounds__(kWarpsPerBlock * 32, min_blocks_per_sm(NV))
         next_end = __shfl_sync(kFullMask, row_ends, r - rbase);
 #pragma unroll
         for (int k = 0; k < NV; ++k) acc[k] = ynext[k];
-        load_y(r + 1 < r1 ? r + 1 : (int)M, ynext);
+        load_y(next_row_needs_y() ? r + 1 : (int)M, ynext);
     };
 
     // Fold the S lane groups and write row r (its last nonzero is in this chunk).
@@ -299,12 +307,14 @@ __global__ void __launch_bounds__(kWarpsPerBlock * 32, min_blocks_per_sm(NV))
     // the slot's decode parameters.
     Vec<VW> xr[QB ? 1 : U][QB ? 1 : NV];
     uint32_t wq[QB ? U : 1][QB ? NV : 1];
-    float av[U], zq[QB ? U : 1], sq[QB ? U : 1];
+    float av[U];
+    uint32_t pq[QB ? U : 1];  // the slot's bf16 (zero_point, scale) pair, widened when applied
     int shq[QB ? U : 1];
 
     for (int eb = 0; eb < n; eb += 32) {
         int my_col = 0;
-        float my_val = 0.f, my_zp = 0.f, my_sc = 0.f;
+        float my_val = 0.f;
+        uint32_t my_prm = 0u;
         if (eb + lane < n) {
             my_col = ld_stream(col + e0 + eb + lane);
             my_val = ld_stream(val + e0 + eb + lane);
@@ -312,9 +322,7 @@ __global__ void __launch_bounds__(kWarpsPerBlock * 32, min_blocks_per_sm(NV))
                 // wire slot -> (packed row, bit position) and its bf16 parameters, once per nonzero
                 const int pseg = find_segment(sseg, q.P, my_col);
                 const int j = my_col - sseg[pseg];
-                const uint32_t prm = __ldg(q.params + my_col);
-                my_zp = __uint_as_float(prm << 16);
-                my_sc = __uint_as_float(prm & 0xffff0000u);
+                my_prm = __ldg(q.params + my_col);
                 my_col = ((pbase[pseg] + j / EPB) << 3) | ((EPB - 1 - j % EPB) * QB);
             }
         }
@@ -326,8 +334,7 @@ __global__ void __launch_bounds__(kWarpsPerBlock * 32, min_blocks_per_sm(NV))
             const int cc = __shfl_sync(kFullMask, my_col, src_lane);
             av[u] = __shfl_sync(kFullMask, my_val, src_lane);
             if (QB) {
-                zq[u] = __shfl_sync(kFullMask, my_zp, src_lane);
-                sq[u] = __shfl_sync(kFullMask, my_sc, src_lane);
+                pq[u] = __shfl_sync(kFullMask, my_prm, src_lane);
                 shq[u] = cc & 7;
                 const uint32_t *wp = reinterpret_cast<const uint32_t *>(q.codes + (int64_t)(cc >> 3) * q.F);
 #pragma unroll
@@ -350,10 +357,11 @@ __global__ void __launch_bounds__(kWarpsPerBlock * 32, min_blocks_per_sm(NV))
                         // 8388608 + code -- and subtract 2^23 (exact): no integer-to-float conversion
                         constexpr uint32_t kMask = ((1u << QB) - 1u) * 0x01010101u;
                         const uint32_t ws = (wq[u][k] >> shq[u]) & kMask;
+                        const float zq_u = __uint_as_float(pq[u] << 16), sq_u = __uint_as_float(pq[u] & 0xffff0000u);
 #pragma unroll
                         for (int i = 0; i < VW; ++i) {
                             const float m = __uint_as_float(__byte_perm(ws, 0x4B000000u, 0x7440 + i));
-                            const float x = fmaf(m - 8388608.0f, sq[u], zq[u]);
+                            const float x = fmaf(m - 8388608.0f, sq_u, zq_u);
                             acc[k].v[i] = fmaf(av[u], x, acc[k].v[i]);
                         }
                     } else {
@@ -472,8 +480,10 @@ static void launch_chunks(const int64_t *rowptr, const int32_t *col, const float
                           const PackedOperand &q, cudaStream_t st) {
     const unsigned blocks = (unsigned)div_up(nchunks, kWarpsPerBlock);
     const bool full = (FV == G * NV) && VW == 4;
+    // a packed gather is 4 bytes per lane instead of 16: where registers allow, keep more in flight
+    constexpr int UQ = NV == 2 ? 8 : U;  // F in (128, 256]: eight packed gathers in flight instead of four
 #define GNNAGG_GO(ACC, FULL, QB)                                                                              \
-    spmm_chunk_kernel<G, NV, VW, U, ACC, FULL, QB><<<blocks, kWarpsPerBlock * 32, 0, st>>>(                   \
+    spmm_chunk_kernel<G, NV, VW, (QB ? UQ : U), ACC, FULL, QB><<<blocks, kWarpsPerBlock * 32, 0, st>>>(       \
         rowptr, col, val, M, X, ldx, Y, ldy, FV, chunk_nz, chunk_row, nchunks, carry, carry_ld, q)
     if (VW == 4 && qbits != 0) {  // packed operand: 128-bit path only, per-vector predicates kept
         if (qbits == 2) {

@@ -17,12 +17,23 @@ class _Work:
         return True
 
 
+class _P2POp:
+    """Stand-in for dist.P2POp (the real one insists on an initialised process group)."""
+
+    def __init__(self, op, tensor, peer=None, group=None, tag=0, group_peer=None):
+        self.op, self.tensor, self.peer = op, tensor, peer
+
+_REAL_ISEND, _REAL_IRECV = dist.isend, dist.irecv
+
+
 class FakeWorld:
     def __init__(self, world_size: int):
         self.P = world_size
         self._barrier = threading.Barrier(world_size)
         self._slots = [None] * world_size
         self._local = threading.local()
+        self._mail = {}
+        self._cond = threading.Condition()
 
     # ---- torch.distributed surface ----
     def get_rank(self, group=None):
@@ -68,15 +79,41 @@ class FakeWorld:
         self._barrier.wait()  # nobody overwrites a send buffer before every peer has copied from it
         return _Work() if async_op else None
 
+    def batch_isend_irecv(self, ops):
+        """Grouped point-to-point operations: sends post a copy into the receiver's mailbox, receives
+        block (on the host) until the matching send has been posted."""
+        r = self._local.rank
+        if any(o.tensor.is_cuda for o in ops):
+            torch.cuda.current_stream().synchronize()
+        for o in ops:
+            if o.op is _REAL_ISEND:
+                with self._cond:
+                    self._mail.setdefault((r, o.peer), []).append(o.tensor.clone())
+                    self._cond.notify_all()
+        for o in ops:
+            if o.op is _REAL_IRECV:
+                with self._cond:
+                    ok = self._cond.wait_for(lambda: self._mail.get((o.peer, r)), timeout=60)
+                    if not ok:
+                        raise RuntimeError(f"rank {r}: no message from rank {o.peer}")
+                    src = self._mail[(o.peer, r)].pop(0)
+                assert src.shape == o.tensor.shape, f"rank {r}: size mismatch with rank {o.peer}"
+                o.tensor.copy_(src)
+        if any(o.tensor.is_cuda for o in ops):
+            torch.cuda.current_stream().synchronize()
+        return [_Work()]
+
     # ---- harness ----
     @contextmanager
     def patched(self):
         names = ("get_rank", "get_world_size", "is_initialized", "is_available", "get_backend", "barrier",
-                 "all_to_all_single")
+                 "all_to_all_single", "batch_isend_irecv")
         saved = {n: getattr(dist, n) for n in names}
+        saved["P2POp"] = dist.P2POp
         try:
             for n in names:
                 setattr(dist, n, getattr(self, n))
+            dist.P2POp = _P2POp
             yield self
         finally:
             for n, f in saved.items():
