@@ -94,6 +94,40 @@ def _remote_parts(graph, world_size):
     return parts
 
 
+# Packed halo, backward: transposed remote SpMM and packing done peer by peer (always on when the
+# graph's CommBuffer is lean).
+PACK_PER_PEER = False
+
+
+def _pack_halo_gradients_per_peer(graph, g, world_size) -> None:
+    from .quantizer import _quant_pack
+
+    q = graph.comm_buf_for_quantization
+    bits = Quantizer_for_all_procs.ctx._bits()
+    epb = 8 // bits
+    parts = _remote_parts(graph, world_size)
+    offs = _prefix(graph.comm_splits.recv_splits)
+    poffs = _prefix(graph.comm_splits.recv_splits_int2)
+    feat_len = g.size(-1)
+    biggest = max(graph.comm_splits.recv_splits) if graph.comm_splits.recv_splits else 0
+    if biggest == 0:
+        return
+    scratch = torch.empty((biggest, feat_len), dtype=torch.float32, device=g.device)
+    segs = getattr(graph, "_one_peer_segs", None)
+    if segs is None:
+        segs = [torch.tensor([0, n], dtype=torch.int32, device=g.device) for n in graph.comm_splits.recv_splits]
+        graph._one_peer_segs = segs
+    for p in range(world_size):
+        n_p = offs[p + 1] - offs[p]
+        if n_p == 0:
+            continue
+        block = scratch[:n_p]
+        SPMM_backward(parts[p], g, block, accumulate=False)
+        _quant_pack(block, q.quantized_recv_data_buf[poffs[p]:poffs[p + 1]],
+                    q.quantized_recv_params_buf_fp32[offs[p]:offs[p + 1]], segs[p], 1, bits,
+                    params_bf16=q.quantized_recv_params_buf_bf16[offs[p]:offs[p + 1]])
+
+
 def _pipelined(num_bits, is_pre_delay, is_training, world_size) -> bool:
     comm = Communicator.ctx
     fp32 = comm is not None and (comm.num_bits == 32 or not is_training)
@@ -113,7 +147,8 @@ class Aggregator(torch.autograd.Function):
         t_total = rec.start() if rec else None
         x = local_nodes_feat.contiguous()
         feat_len = x.size(-1)
-        packed = world_size > 1 and is_training and _packed(num_bits, graph)
+        lean = bool(getattr(graph.comm_buf, "lean", False))  # no fp32 staging buffers: the halo stays packed
+        packed = world_size > 1 and (is_training or lean) and _packed(num_bits, graph)
 
         comm_handle = None
         rounds = None
@@ -143,6 +178,8 @@ class Aggregator(torch.autograd.Function):
                 gather_rows(x, _send_idx(graph), send_buf)
             if rec:
                 rec.record_prepare_comm_time(t)
+            if lean and not fused_pack:
+                raise RuntimeError("lean halo buffers need the plain (not pre/post) path with a packed halo")
             if fused_pack:
                 comm_handle = Communicator.ctx.comm_with_int2_quantization_for_all_procs(
                     graph.comm_splits, graph.comm_buf, q, "forward", already_quantized=True)
@@ -235,6 +272,18 @@ class Aggregator(torch.autograd.Function):
                                                        before_send=make_block)
             if rec:
                 rec.record_pre_aggregate_time(t)
+        elif world_size > 1 and packed and FUSE_UNPACK and not is_pre_delay and feat_len % 4 == 0 \
+                and (getattr(graph.comm_buf, "lean", False) or PACK_PER_PEER):
+            # halo gradients are produced and packed one peer at a time through a peer-sized scratch, so
+            # the full fp32 halo buffer is never needed (same codes: packing groups restart per peer)
+            _resize(graph, feat_len, num_bits)
+            t = rec.start() if rec else None
+            _pack_halo_gradients_per_peer(graph, g, world_size)
+            if rec:
+                rec.record_pre_aggregate_time(t)
+            comm_handle = Communicator.ctx.comm_with_int2_quantization_for_all_procs(
+                graph.comm_splits, graph.comm_buf, graph.comm_buf_for_quantization, "backward",
+                already_quantized=True)
         elif world_size > 1:
             _resize(graph, feat_len, num_bits)
             # the two buffers swap roles: recv_buf is sent, send_buf receives

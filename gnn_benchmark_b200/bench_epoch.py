@@ -52,6 +52,8 @@ def main():
     ap.add_argument("--epochs", type=int, default=6)
     ap.add_argument("--train-frac", type=float, default=0.01)
     ap.add_argument("--dropout", type=float, default=0.5)
+    ap.add_argument("--lean-halo", type=int, default=1,
+                    help="packed halo modes: no fp32 staging buffers (they are tens of GB per GPU at this scale)")
     ap.add_argument("--seed", type=int, default=20261130)
     args = ap.parse_args()
 
@@ -70,7 +72,9 @@ def main():
     nnz_rank = int(local.shape[1] + remote.shape[1])
     del src, dst
     dims = [args.in_channels] + [args.hidden] * (args.layers - 1) + [args.out_channels]
-    graph = build_graph(local, remote, begin, rank, world, max(dims), args.bits, bool(args.pre), device=device)
+    lean = bool(args.lean_halo) and args.bits in (2, 4, 8) and not args.pre and world > 1
+    graph = build_graph(local, remote, begin, rank, world, max(dims), args.bits, bool(args.pre), device=device,
+                        lean_halo=lean)
     del local, remote
     torch.cuda.empty_cache()
     n = graph.local_adj_t.sparse_size(0)
@@ -106,7 +110,7 @@ def main():
             "metric": "epoch_time", "value": epoch_s, "unit": "s", "higher_is_better": False, "n_gpus": world,
             "aggregated_edges_per_s": float(tsum[1]) * passes / epoch_s, "aggregation_passes_per_step": passes,
             "config": {"model": args.model, "dims": dims, "nodes": args.nodes, "directed_edges_after_symmetrising":
-                       int(tsum[1]), "halo": f"{args.bits}-bit" + (" pre/post" if args.pre else ""),
+                       int(tsum[1]), "halo": f"{args.bits}-bit" + (" pre/post" if args.pre else "") + (", no fp32 staging buffers" if lean else ""),
                        "halo_rows_sent_per_exchange": int(tsum[2]), "graph": "Chung-Lu gamma=2.1, relabelled",
                        "epochs_timed": len(times) - 1, "dropout": args.dropout, "optimizer": "Adam lr 0.01"},
             "losses": [round(x, 5) for x in losses], "epoch_times_s": [round(x, 4) for x in times],

@@ -75,7 +75,8 @@ class Communicator(object):
         training, bf16 for 16, packed codes for 2 (and here 4 and 8).  Returns an object with
         .wait() or None."""
         comm_handle = None
-        if self.num_bits == 32 or is_training is False:
+        lean = bool(getattr(comm_buf, "lean", False))  # no fp32 staging buffers: the halo stays packed in eval too
+        if self.num_bits == 32 or (is_training is False and not lean):
             comm_handle = self.comm_with_fp32(comm_splits, comm_buf, direction)
         elif self.num_bits == 16:
             comm_handle = self.comm_with_fp16(comm_splits, comm_buf, direction)

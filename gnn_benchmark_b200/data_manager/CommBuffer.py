@@ -13,11 +13,16 @@ class CommBuffer(object):
     """fp32 (and, for 16-bit mode, bf16) send / receive buffers of the halo exchange, allocated
     once for the widest layer and reshaped per layer (data_manager/CommBuffer.py:4-25)."""
 
-    def __init__(self, comm_splits: CommSplits, feat_len: int, bits: int, device=None) -> None:
+    def __init__(self, comm_splits: CommSplits, feat_len: int, bits: int, device=None, lean: bool = False) -> None:
+        """lean (an addition, packed halo modes only): the fp32 staging buffers get a shape but no
+        memory (meta tensors).  The fused gather+pack, per-peer pack and fused unpack paths of the
+        Aggregator never touch them; at 10^7 halo rows x 256 columns they would be tens of GB each."""
         size_send_buf = (sum(comm_splits.send_splits), feat_len)
         size_recv_buf = (sum(comm_splits.recv_splits), feat_len)
-        self.send_buf = torch.zeros(size_send_buf, dtype=torch.float32, device=device)
-        self.recv_buf = torch.zeros(size_recv_buf, dtype=torch.float32, device=device)
+        self.lean = bool(lean) and bits in (2, 4, 8)
+        buf_device = "meta" if self.lean else device
+        self.send_buf = torch.zeros(size_send_buf, dtype=torch.float32, device=buf_device)
+        self.recv_buf = torch.zeros(size_recv_buf, dtype=torch.float32, device=buf_device)
         self.send_buf_fp16 = None
         self.recv_buf_fp16 = None
         if bits == 16:

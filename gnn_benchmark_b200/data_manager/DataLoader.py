@@ -66,7 +66,8 @@ def _scatter_matrix(idx: torch.Tensor, num_local_nodes: int) -> SparseTensor:
 
 
 def get_distributed_graph(local_edges_list, remote_edges_list, local_nodes_list, nodes_range_on_each_subgraph,
-                          num_local_nodes: int, max_feat_len: int, world_size: int, bits: int, device=None):
+                          num_local_nodes: int, max_feat_len: int, world_size: int, bits: int, device=None,
+                          lean_halo: bool = False):
     """Plain halo path (DataLoader.py:64-122).  Edge lists may live on CPU or GPU; the plan is
     built where they are and the resulting graph is moved to `device`."""
     in_degrees = DataProcessor.get_in_degrees(local_edges_list, remote_edges_list, num_local_nodes)
@@ -91,7 +92,7 @@ def get_distributed_graph(local_edges_list, remote_edges_list, local_nodes_list,
         device = local_adj_t.device
     comm_splits = CommSplits(remote_nodes_num_from_each_subgraph.tolist(),
                              num_local_nodes_required_by_other.tolist(), world_size, bits)
-    comm_buf = CommBuffer(comm_splits, max_feat_len, bits, device)
+    comm_buf = CommBuffer(comm_splits, max_feat_len, bits, device, lean=lean_halo)
     comm_buf_for_quantization = None
     if bits in (2, 4, 8):
         comm_buf_for_quantization = CommBufferForQuantization(comm_splits, max_feat_len, bits, device)
@@ -156,7 +157,7 @@ def get_distributed_graph_for_pre_aggressive(local_edges_list, remote_edges_list
 
 
 def build_graph(local_edges_list, remote_edges_list, nodes_range_on_each_subgraph, rank, world_size, max_feat_len,
-                bits, is_pre_delay, device=None):
+                bits, is_pre_delay, device=None, lean_halo: bool = False):
     """Assemble a DistributedGraph[ForPre] from in-memory edge lists (what load_data does after
     reading the files).  local_edges_list / remote_edges_list: 2 x E int64 tensors or pairs."""
     local_edges_list = [local_edges_list[0], local_edges_list[1]]
@@ -168,7 +169,7 @@ def build_graph(local_edges_list, remote_edges_list, nodes_range_on_each_subgrap
                                                         max_feat_len, rank, world_size, bits, device)
     local_nodes_list = torch.tensor([[int(begin[rank]), 0]], dtype=torch.int64)
     return get_distributed_graph(local_edges_list, remote_edges_list, local_nodes_list, begin, num_local_nodes,
-                                 max_feat_len, world_size, bits, device)
+                                 max_feat_len, world_size, bits, device, lean_halo=lean_halo)
 
 
 def load_data(config):

@@ -229,3 +229,43 @@ def test_peer_pipelined_exchange(cuda_lib, monkeypatch, P, F):
         close(grad, results[False][r][1], scale_grad[b0:b1])
         # the backward halo blocks are the same numbers whichever way they travel
         np.testing.assert_array_equal(grad.shape, results[False][r][1].shape)
+
+
+@pytest.mark.parametrize("P,F,bits", [(2, 128, 2), (4, 256, 2), (3, 64, 8)])
+def test_lean_halo_buffers_give_identical_results(cuda_lib, P, F, bits):
+    """lean_halo=True: the fp32 staging buffers of the exchange have no memory (meta tensors); forward
+    goes gather+pack -> exchange -> fused unpack SpMM, backward packs the halo gradients peer by peer
+    through a peer-sized scratch.  Outputs, gradients and the codes on the wire are bit-identical to the
+    path that stages everything in fp32."""
+    from gnn_benchmark_b200 import Communicator, Quantizer_for_all_procs, TimeRecorder, graphgen
+    from gnn_benchmark_b200.aggregator import Aggregator
+    from gnn_benchmark_b200.data_manager.DataLoader import build_graph
+
+    begin_np, src, dst = make_graph(31 * P + F, P, 500, 6)
+    N = int(begin_np[-1])
+    begin = torch.from_numpy(begin_np)
+    rng = np.random.default_rng(3)
+    X = rng.standard_normal((N, F)).astype(np.float32)
+    G = rng.standard_normal((N, F)).astype(np.float32)
+    s_t, d_t = torch.from_numpy(src).cuda(), torch.from_numpy(dst).cuda()
+    Communicator(bits, is_async=True)
+    Quantizer_for_all_procs(P, bits)
+    TimeRecorder(1, 1)
+    results = {}
+    for lean in (False, True):
+        def rank_fn(rank):
+            local, remote = graphgen.partition_edges(s_t, d_t, begin, rank)
+            graph = build_graph(local, remote, begin, rank, P, F, bits, False, device="cuda", lean_halo=lean)
+            assert graph.comm_buf.send_buf.is_meta == lean and graph.comm_buf.recv_buf.is_meta == lean
+            b0, b1 = int(begin[rank]), int(begin[rank + 1])
+            ctx = SimpleNamespace()
+            out = Aggregator.forward(ctx, graph, torch.from_numpy(X[b0:b1]).cuda(), 0, bits, False, True)
+            grad = Aggregator.backward(ctx, torch.from_numpy(G[b0:b1]).cuda())[1]
+            q = graph.comm_buf_for_quantization
+            return (out.cpu().numpy(), grad.cpu().numpy(), q.quantized_recv_data_buf.cpu().numpy(),
+                    q.quantized_recv_params_buf_fp32.cpu().numpy())
+
+        results[lean] = FakeWorld(P).run(rank_fn)
+    for r in range(P):
+        for a, b in zip(results[False][r], results[True][r]):
+            np.testing.assert_array_equal(a, b)
