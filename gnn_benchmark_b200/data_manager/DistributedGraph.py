@@ -1,66 +1,62 @@
-from typing import Optional
+"""One rank's share of the partitioned graph.
 
-from torch import Tensor
-
-from ..sparse import SparseTensor
-from .CommBuffer import CommBuffer, CommBufferForQuantization
-from .CommSplits import CommSplits
-
-
-class DistributedGraph(object):
-    """One rank's share of the graph, plain halo path (data_manager/DistributedGraph.py:8-33).
-
-    Field names are the reference's; `idx_nodes_send_to_others_i32` and `scatter_adj_t` are
-    additions the CUDA path derives once: the int32 copy of the send index and the
-    (n_local x n_send) unit matrix whose accumulating SpMM is the deterministic form of
-    grad.index_add_(0, idx_nodes_send_to_others, buf) (model/layers/aggregator.py:197-199)."""
-
-    def __init__(
-        self,
-        local_adj_t: SparseTensor,
-        remote_adj_t: SparseTensor,
-        idx_nodes_send_to_others: Tensor,
-        num_nodes_send_to_others: list,
-        num_nodes_recv_from_others: list,
-        in_degrees: Tensor,
-        comm_splits: CommSplits,
-        comm_buf: CommBuffer,
-        comm_buf_for_quantization: Optional[CommBufferForQuantization],
-    ) -> None:
-        self.local_adj_t = local_adj_t
-        self.remote_adj_t = remote_adj_t
-        self.idx_nodes_send_to_others = idx_nodes_send_to_others
-        self.num_nodes_send_to_others = num_nodes_send_to_others
-        self.num_nodes_recv_from_others = num_nodes_recv_from_others
-        self.in_degrees = in_degrees
-        self.comm_splits = comm_splits
-        self.comm_buf = comm_buf
-        self.comm_buf_for_quantization = comm_buf_for_quantization
-        self.idx_nodes_send_to_others_i32 = None
-        self.scatter_adj_t = None
+`DistributedGraph` (plain halo path) and `DistributedGraphForPre` (pre/post-aggregation path) carry the
+attribute names of the reference's classes of the same names
+(self_benchmark/a64fx/data_manager/DistributedGraph.py:8-59) and accept the same positional or keyword
+arguments; the aggregation op reads nothing else from them.
+"""
+from typing import Tuple
 
 
-class DistributedGraphForPre(object):
-    """One rank's share of the graph, pre/post-aggregation path (DistributedGraph.py:35-59)."""
+class _GraphRecord(object):
+    """Record whose constructor binds positional / keyword arguments to `_fields`, in order."""
 
-    def __init__(
-        self,
-        local_adj_t: SparseTensor,
-        adj_t_pre_post_aggr_from: SparseTensor,
-        adj_t_pre_post_aggr_to: SparseTensor,
-        pre_post_aggr_from_splits: list,
-        pre_post_aggr_to_splits: list,
-        in_degrees: Tensor,
-        comm_splits: CommSplits,
-        comm_buf: CommBuffer,
-        comm_buf_for_quantization: Optional[CommBufferForQuantization],
-    ) -> None:
-        self.local_adj_t = local_adj_t
-        self.adj_t_pre_post_aggr_from = adj_t_pre_post_aggr_from
-        self.adj_t_pre_post_aggr_to = adj_t_pre_post_aggr_to
-        self.pre_post_aggr_from_splits = pre_post_aggr_from_splits
-        self.pre_post_aggr_to_splits = pre_post_aggr_to_splits
-        self.in_degrees = in_degrees
-        self.comm_splits = comm_splits
-        self.comm_buf = comm_buf
-        self.comm_buf_for_quantization = comm_buf_for_quantization
+    _fields: Tuple[str, ...] = ()
+    _derived: Tuple[str, ...] = ()
+
+    def __init__(self, *args, **kwargs) -> None:
+        if len(args) > len(self._fields):
+            raise TypeError(f"{type(self).__name__} takes {len(self._fields)} arguments, {len(args)} given")
+        values = dict(zip(self._fields, args))
+        for name, value in kwargs.items():
+            if name not in self._fields:
+                raise TypeError(f"{type(self).__name__} has no field {name!r}")
+            if name in values:
+                raise TypeError(f"{type(self).__name__}: {name!r} given twice")
+            values[name] = value
+        missing = [f for f in self._fields if f not in values]
+        if missing:
+            raise TypeError(f"{type(self).__name__} missing {missing}")
+        for name in self._fields:
+            setattr(self, name, values[name])
+        for name in self._derived:
+            setattr(self, name, None)
+
+    def __repr__(self) -> str:
+        return f"{type(self).__name__}(local_adj_t={self.local_adj_t!r})"
+
+
+_COMMON_TAIL = ("in_degrees", "comm_splits", "comm_buf", "comm_buf_for_quantization")
+
+
+class DistributedGraph(_GraphRecord):
+    """Plain halo path: local and remote adjacency (rows = local destinations; remote columns = halo
+    slots), the local ids to send (concatenated per requesting peer) and the per-peer counts.
+
+    Derived once by the CUDA path and cached here: `idx_nodes_send_to_others_i32` (int32 copy of the
+    send index) and `scatter_adj_t`, the (n_local x n_send) unit matrix whose accumulating SpMM is the
+    deterministic form of grad.index_add_(0, idx_nodes_send_to_others, buf)
+    (model/layers/aggregator.py:197-199 of the reference)."""
+
+    _fields = ("local_adj_t", "remote_adj_t", "idx_nodes_send_to_others", "num_nodes_send_to_others",
+               "num_nodes_recv_from_others") + _COMMON_TAIL
+    _derived = ("idx_nodes_send_to_others_i32", "scatter_adj_t")
+
+
+class DistributedGraphForPre(_GraphRecord):
+    """Pre/post-aggregation path: `adj_t_pre_post_aggr_to` (send slots x n_local) builds the send buffer,
+    `adj_t_pre_post_aggr_from` (n_local x receive slots) consumes the receive buffer; the two split
+    lists repeat comm_splits.recv_splits / send_splits."""
+
+    _fields = ("local_adj_t", "adj_t_pre_post_aggr_from", "adj_t_pre_post_aggr_to", "pre_post_aggr_from_splits",
+               "pre_post_aggr_to_splits") + _COMMON_TAIL
