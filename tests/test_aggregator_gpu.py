@@ -269,3 +269,63 @@ def test_lean_halo_buffers_give_identical_results(cuda_lib, P, F, bits):
     for r in range(P):
         for a, b in zip(results[False][r], results[True][r]):
             np.testing.assert_array_equal(a, b)
+
+
+@pytest.mark.parametrize("bits", [2, 8])
+def test_config3_downscaled_codes_bit_exact(cuda_lib, monkeypatch, bits):
+    """BASELINE configuration 3, down-scaled: R-MAT scale 16 (edge factor 16, symmetrised, randomly
+    relabelled), 8 contiguous partitions, F = 256.  The codes and parameters every rank puts on the wire
+    -- 2-bit (the reference's live layout, 4 rows per byte) and 8-bit (its generic row-packed layout) --
+    are compared byte for byte with the CPU oracle, and the fp32 / quantised aggregation results with the
+    global product."""
+    import gnn_benchmark_b200.aggregator as agg_mod
+    from gnn_benchmark_b200 import Communicator, Quantizer_for_all_procs, TimeRecorder, graphgen
+    from gnn_benchmark_b200.aggregator import Aggregator
+    from gnn_benchmark_b200.data_manager.DataLoader import build_graph
+
+    monkeypatch.setattr(agg_mod, "FUSE_UNPACK", True)
+    P, F, scale = 8, 256, 16
+    n = 1 << scale
+    s_t, d_t = graphgen.rmat_edges(scale, 16, seed=20261128, device="cuda")
+    s_t, d_t = graphgen.symmetrize(s_t, d_t, n, self_loops=True)
+    s_t, d_t = graphgen.relabel(s_t, d_t, n, seed=20261129)
+    begin = graphgen.contiguous_partitions(n, P)
+    rng = np.random.default_rng(bits)
+    X = rng.standard_normal((n, F)).astype(np.float32)
+    Communicator(bits, is_async=True)
+    Quantizer_for_all_procs(P, bits)
+    TimeRecorder(1, 1)
+
+    def rank_fn(rank):
+        local, remote = graphgen.partition_edges(s_t, d_t, begin, rank)
+        graph = build_graph(local, remote, begin, rank, P, F, bits, False, device="cuda")
+        b0, b1 = int(begin[rank]), int(begin[rank + 1])
+        ctx = SimpleNamespace()
+        out = Aggregator.forward(ctx, graph, torch.from_numpy(X[b0:b1]).cuda(), 0, bits, False, True)
+        q = graph.comm_buf_for_quantization
+        return (out.cpu().numpy(), q.quantized_send_data_buf.cpu().numpy(), q.quantized_send_params_buf_fp32.cpu().numpy(),
+                graph.idx_nodes_send_to_others.cpu().numpy(), list(graph.comm_splits.send_splits))
+
+    res = FakeWorld(P).run(rank_fn)
+    src, dst = s_t.cpu().numpy(), d_t.cpu().numpy()
+    rp, c, v = global_csr(src, dst, n)
+    want, scale_abs = oracle.spmm(rp, c, v, X), oracle.spmm(rp, c, v, np.abs(X))
+    epb = 8 // bits
+    for r in range(P):
+        out, codes, params, idx, send_splits = res[r]
+        b0, b1 = int(begin[r]), int(begin[r + 1])
+        rows = X[b0 + idx]
+        offs = np.concatenate([[0], np.cumsum(send_splits)]).astype(np.int32)
+        if bits == 2:
+            wc, wp = oracle.quantize_int2_for_all_procs(rows, offs)
+        else:
+            mn = rows.min(1)
+            sc = ((rows.max(1) - mn) / np.float32(2 ** bits - 1)).astype(np.float32)
+            sc[sc == 0] = 1
+            wp = np.stack([mn, sc], 1)
+            wc = np.concatenate([oracle.quantize_rowpacked(rows[a:b], mn[a:b], sc[a:b], bits)
+                                 for a, b in zip(offs[:-1], offs[1:]) if b > a])
+        np.testing.assert_array_equal(params, wp)
+        np.testing.assert_array_equal(codes, wc)
+        # the lossy halo keeps the aggregate within one quantisation step per remote term
+        assert np.abs(out - want[b0:b1]).max() <= (2.5 if bits == 2 else 0.05) * max(1.0, scale_abs[b0:b1].max())
