@@ -40,6 +40,10 @@ SIGNATURES = {
     "gnnagg_dequant_v1_rows": (ctypes.c_int, [_vp, _i64, _i32, _vp, _vp, _vp, _i64, _vp]),
     "gnnagg_cast_f32_to_bf16": (ctypes.c_int, [_vp, _vp, _i64, _vp]),
     "gnnagg_cast_bf16_to_f32": (ctypes.c_int, [_vp, _vp, _i64, _vp]),
+    "gnnagg_dense_workspace_bytes": (_sz, [_i32, _i32]),
+    "gnnagg_dense_tf32x3_f32": (ctypes.c_int, [_vp, _i64, _vp, _i64, _vp, _i64, _i64, _i32, _i32, _vp, _i32, _vp, _sz,
+                                               _vp]),
+    "gnnagg_dense_status": (ctypes.c_int, [_vp, _vp]),
 }
 
 

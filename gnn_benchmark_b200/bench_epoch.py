@@ -55,6 +55,9 @@ def main():
     ap.add_argument("--lean-halo", type=int, default=1,
                     help="packed halo modes: no fp32 staging buffers (they are tens of GB per GPU at this scale)")
     ap.add_argument("--seed", type=int, default=20261130)
+    ap.add_argument("--kernel-table", default="",
+                    help="after the timed epochs, run one more under torch.profiler and write rank 0's per-kernel "
+                         "device-time table to this file (a breakdown, never a timing)")
     args = ap.parse_args()
 
     comm = Communicator(args.bits, is_async=True)
@@ -116,6 +119,16 @@ def main():
             "losses": [round(x, 5) for x in losses], "epoch_times_s": [round(x, 4) for x in times],
             "peak_mem_gib_max_rank": float(tmax[3]), "setup_s": round(setup_s, 1), "data": "synthetic",
         }), flush=True)
+    if args.kernel_table:
+        from torch.profiler import ProfilerActivity, profile
+
+        TimeRecorder(args.layers, 1, enabled=False)
+        with profile(activities=[ProfilerActivity.CUDA]) as prof:
+            train(model, data, optimizer, 1, args.bits, eval_every_epoch=False, log=None)
+            torch.cuda.synchronize()
+        if rank == 0:
+            with open(args.kernel_table, "w") as fh:
+                fh.write(prof.key_averages().table(sort_by="cuda_time_total", row_limit=60, max_name_column_width=90))
     if world > 1:
         dist.barrier()
         dist.destroy_process_group()

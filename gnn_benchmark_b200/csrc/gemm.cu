@@ -1,0 +1,559 @@
+// Dense feature transform on the 5th-generation tensor cores (tcgen05 + TMEM + TMA), sm_100a only:
+//
+//     C[M,N] (+)= A[M,K] . B[N,K]^T (+ bias[N])          all fp32, row-major, B = an nn.Linear weight
+//
+// in fp32-grade accuracy: every operand is split into two TF32 pieces, x = hi + lo with
+// hi = tf32_rna(x), lo = tf32_rna(x - hi), and three tensor-core products a_lo.b_hi + a_hi.b_lo +
+// a_hi.b_hi are accumulated in fp32 in tensor memory (the dropped a_lo.b_lo term is below 2^-22
+// relative).  The weight is split once per call by a small kernel into a caller-provided workspace;
+// the activation panel is split inside the GEMM, in shared memory, between the TMA load and the MMA.
+//
+// One persistent CTA per SM, 10 warps:
+//   warp 0      lane 0 issues the TMA loads (A raw, B_hi, B_lo per 32-wide k-block; two stages) and
+//               prefetches the next row panel of A into L2;
+//   warp 1      allocates tensor memory; lane 0 issues tcgen05.mma (128 x N x 8 per instruction) and
+//               the commits that free a stage / publish an accumulator;
+//   warps 2-5   split the raw A tile of a stage into hi (in place) and lo (second buffer);
+//   warps 6-9   epilogue: tcgen05.ld of a finished accumulator (two of them in tensor memory, so the
+//               epilogue of one row panel runs under the MMAs of the next), 32x32 transposes through
+//               shared memory, coalesced stores with optional bias and accumulate.
+// Every wait is bounded (about a second); on a time-out the kernel records a code in the status
+// word of the workspace, drains its own copies and MMAs, frees tensor memory and returns.
+#include <cuda.h>
+
+#include <mutex>
+
+#include "common.cuh"
+
+namespace gnnagg {
+namespace {
+
+constexpr int BM = 128;                 // rows of A per tile = UMMA M = TMEM lanes
+constexpr int BK = 32;                  // fp32 per k-block: 128 bytes = one 128B-swizzle row
+constexpr int UMMA_K = 8;               // tf32 elements per tcgen05.mma
+constexpr int kStages = 2;
+constexpr int kMaxN = 256;
+constexpr int kTmemCols = 512;          // two accumulators of up to 256 columns
+constexpr int kAccStride = 256;         // column offset of the second accumulator
+constexpr int A_TILE_BYTES = BM * BK * 4;       // 16 KB
+constexpr int B_TILE_BYTES = kMaxN * BK * 4;    // 32 KB reserved per piece
+constexpr int STAGE_BYTES = 2 * A_TILE_BYTES + 2 * B_TILE_BYTES;  // a_hi, a_lo, b_hi, b_lo
+constexpr int kEpiPad = 33;
+constexpr int EPI_BYTES = 4 * 32 * kEpiPad * 4;
+constexpr int kNumBarriers = 3 * kStages + 4 + 1;
+constexpr int SMEM_BYTES = 1024 + kStages * STAGE_BYTES + EPI_BYTES + 256;
+constexpr int kThreads = 320;
+constexpr unsigned long long kWaitLimitNs = 1000ull * 1000ull * 1000ull;
+constexpr int kStatusBytes = 256;
+
+static_assert(SMEM_BYTES <= 227 * 1024, "shared memory budget");
+
+__device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ unsigned long long globaltimer_ns() {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n"
+        ".reg .pred p;\n"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+        "selp.u32 %0, 1, 0, p;\n"
+        "}\n"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+
+// Bounded wait.  Returns false when another role has raised `abort_flag` or when this wait ran out
+// of time (it then raises the flag and leaves `code` in the status word, first writer wins).
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int *abort_flag, int *status,
+                                          int code) {
+    if (mbar_try_wait(bar, parity)) return true;
+    const unsigned long long t0 = globaltimer_ns();
+    uint32_t n = 0;
+    while (!mbar_try_wait(bar, parity)) {
+        if ((++n & 31u) == 0) {
+            if (*abort_flag != 0) return false;
+            if (globaltimer_ns() - t0 > kWaitLimitNs) {
+                *abort_flag = 1;
+                atomicCAS(status, 0, code);
+                return false;
+            }
+        }
+    }
+    return true;
+}
+
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap *map, uint32_t bar, int x, int y) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cta.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];" ::"r"(dst),
+        "l"(map), "r"(bar), "r"(x), "r"(y)
+        : "memory");
+}
+__device__ __forceinline__ void tma_prefetch_2d(const CUtensorMap *map, int x, int y) {
+    asm volatile("cp.async.bulk.prefetch.tensor.2d.L2.global [%0, {%1, %2}];" ::"l"(map), "r"(x), "r"(y) : "memory");
+}
+
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void fence_generic_to_async_smem() {
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+}
+
+__device__ __forceinline__ void tc_commit(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+
+__device__ __forceinline__ void tc_mma_tf32(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
+                                            uint32_t accumulate) {
+    asm volatile(
+        "{\n"
+        ".reg .pred p;\n"
+        "setp.ne.b32 p, %4, 0;\n"
+        "tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, p;\n"
+        "}\n" ::"r"(tmem_d),
+        "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+
+// 32 lanes x 32 columns of fp32: thread t of the warp receives columns [c, c+32) of TMEM lane
+// (lane base of the address) + t.
+__device__ __forceinline__ void tc_ld_32x32(uint32_t taddr, uint32_t (&r)[32]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+          "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+          "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+          "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr)
+        : "memory");
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+
+__device__ __forceinline__ float tf32_rna(float x) {
+    uint32_t u;
+    asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(u) : "f"(x));
+    return __uint_as_float(u);
+}
+
+__device__ __forceinline__ void split_tf32(float x, float &hi, float &lo) {
+    hi = tf32_rna(x);
+    const float rest = x - hi;  // exact
+    lo = (fabsf(hi) <= 3.402823466e38f) ? tf32_rna(rest) : 0.0f;  // inf / nan stay in hi alone
+}
+
+// Shared-memory matrix descriptor of a K-major tile whose rows are 128 bytes, 128B-swizzled
+// (what TMA writes for a {32 fp32, rows} box): start address, 8-row group stride 1024 bytes,
+// descriptor version 1 (sm_100), layout type 2 (128-byte swizzle).
+__device__ __forceinline__ uint64_t make_smem_desc(uint32_t smem_addr) {
+    uint64_t d = 0;
+    d |= (uint64_t)((smem_addr & 0x3FFFFu) >> 4);       // bits [0,14)
+    d |= (uint64_t)1 << 16;                              // leading byte offset (unused for swizzled K-major)
+    d |= (uint64_t)(1024 >> 4) << 32;                    // stride byte offset
+    d |= (uint64_t)1 << 46;                              // descriptor version
+    d |= (uint64_t)2 << 61;                              // SWIZZLE_128B
+    return d;
+}
+
+// Instruction descriptor of kind::tf32: fp32 accumulator, TF32 A and B, both K-major, M = 128.
+__host__ __device__ inline uint32_t make_instr_desc(int n) {
+    uint32_t d = 0;
+    d |= 1u << 4;                    // D format: f32
+    d |= 2u << 7;                    // A format: tf32
+    d |= 2u << 10;                   // B format: tf32
+    d |= (uint32_t)(n >> 3) << 17;   // N / 8
+    d |= (uint32_t)(BM >> 4) << 24;  // M / 16
+    return d;
+}
+
+struct GemmParams {
+    float *C;
+    const float *bias;
+    int *status;
+    int64_t M, ldc;
+    int N, n_pad, K, accumulate, num_tiles;
+};
+
+enum : int {
+    kErrWaitEmpty = 1,      // TMA issuer waited for a free stage
+    kErrWaitFull = 2,       // split warps waited for a TMA load
+    kErrWaitSplit = 3,      // MMA issuer waited for the split tile
+    kErrWaitAccFree = 4,    // MMA issuer waited for the epilogue to release an accumulator
+    kErrWaitAccFull = 5,    // epilogue waited for an accumulator
+    kErrDrain = 6,          // bounded drain after an abort ran out
+};
+
+__global__ void __launch_bounds__(kThreads, 1)
+gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_bhi,
+                   const __grid_constant__ CUtensorMap map_blo, const GemmParams p) {
+    extern __shared__ uint8_t smem_raw[];
+    // 1024-byte alignment: the swizzle pattern and the descriptors assume it
+    uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+    uint8_t *stage_base = smem;
+    float *epi = reinterpret_cast<float *>(smem + kStages * STAGE_BYTES);
+    uint64_t *bars = reinterpret_cast<uint64_t *>(smem + kStages * STAGE_BYTES + EPI_BYTES);
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + kNumBarriers);
+    volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
+
+    const uint32_t bar0 = smem_u32(bars);
+    auto bar_full = [&](int s) { return bar0 + 8u * (uint32_t)s; };
+    auto bar_split = [&](int s) { return bar0 + 8u * (uint32_t)(kStages + s); };
+    auto bar_empty = [&](int s) { return bar0 + 8u * (uint32_t)(2 * kStages + s); };
+    auto bar_acc_full = [&](int b) { return bar0 + 8u * (uint32_t)(3 * kStages + b); };
+    auto bar_acc_empty = [&](int b) { return bar0 + 8u * (uint32_t)(3 * kStages + 2 + b); };
+    const uint32_t bar_drain = bar0 + 8u * (uint32_t)(3 * kStages + 4);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int KB = (p.K + BK - 1) / BK;
+    const uint32_t b_bytes = (uint32_t)p.n_pad * BK * 4;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < kStages; ++s) {
+            mbar_init(bar_full(s), 1);
+            mbar_init(bar_split(s), 128);
+            mbar_init(bar_empty(s), 1);
+        }
+        for (int b = 0; b < 2; ++b) {
+            mbar_init(bar_acc_full(b), 1);
+            mbar_init(bar_acc_empty(b), 128);
+        }
+        mbar_init(bar_drain, 1);
+        *abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)),
+                     "r"((uint32_t)kTmemCols)
+                     : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp == 0) {
+        // ---------------- TMA issuer ----------------
+        if (lane == 0) {
+            uint32_t it = 0;
+            bool ok = true;
+            for (int tile = blockIdx.x; tile < p.num_tiles && ok; tile += gridDim.x) {
+                const int m0 = tile * BM;
+                const int next = tile + (int)gridDim.x;
+                if (next < p.num_tiles)
+                    for (int kb = 0; kb < KB; ++kb) tma_prefetch_2d(&map_a, kb * BK, next * BM);
+                for (int kb = 0; kb < KB; ++kb, ++it) {
+                    const int s = it % kStages;
+                    const uint32_t ph = (it / kStages) & 1u;
+                    if (!mbar_wait(bar_empty(s), ph ^ 1u, abort_flag, p.status, kErrWaitEmpty)) {
+                        ok = false;
+                        break;
+                    }
+                    const uint32_t sa = smem_u32(stage_base + s * STAGE_BYTES);
+                    mbar_arrive_expect_tx(bar_full(s), (uint32_t)A_TILE_BYTES + 2u * b_bytes);
+                    tma_load_2d(sa, &map_a, bar_full(s), kb * BK, m0);
+                    tma_load_2d(sa + 2 * A_TILE_BYTES, &map_bhi, bar_full(s), kb * BK, 0);
+                    tma_load_2d(sa + 2 * A_TILE_BYTES + B_TILE_BYTES, &map_blo, bar_full(s), kb * BK, 0);
+                }
+            }
+            if (!ok) {
+                // copies of the last two k-blocks issued may still be landing: wait for them, bounded
+                for (uint32_t back = 1; back <= (uint32_t)kStages && back <= it; ++back) {
+                    const uint32_t j = it - back;
+                    const unsigned long long t0 = globaltimer_ns();
+                    while (!mbar_try_wait(bar_full(j % kStages), (j / kStages) & 1u)) {
+                        if (globaltimer_ns() - t0 > kWaitLimitNs) {
+                            atomicCAS(p.status, 0, (int)kErrDrain);
+                            break;
+                        }
+                    }
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ---------------- MMA issuer ----------------
+        if (lane == 0) {
+            const uint32_t idesc = make_instr_desc(p.n_pad);
+            uint32_t it = 0, t = 0;
+            bool ok = true;
+            for (int tile = blockIdx.x; tile < p.num_tiles && ok; tile += gridDim.x, ++t) {
+                const int b = t & 1;
+                if (!mbar_wait(bar_acc_empty(b), ((t >> 1) & 1u) ^ 1u, abort_flag, p.status, kErrWaitAccFree)) {
+                    ok = false;
+                    break;
+                }
+                tc_fence_after();
+                const uint32_t d_tmem = tmem_base + (uint32_t)(b * kAccStride);
+                for (int kb = 0; kb < KB; ++kb, ++it) {
+                    const int s = it % kStages;
+                    const uint32_t ph = (it / kStages) & 1u;
+                    if (!mbar_wait(bar_full(s), ph, abort_flag, p.status, kErrWaitFull) ||
+                        !mbar_wait(bar_split(s), ph, abort_flag, p.status, kErrWaitSplit)) {
+                        ok = false;
+                        break;
+                    }
+                    tc_fence_after();
+                    const uint32_t sa = smem_u32(stage_base + s * STAGE_BYTES);
+                    const uint64_t a_hi = make_smem_desc(sa);
+                    const uint64_t a_lo = make_smem_desc(sa + A_TILE_BYTES);
+                    const uint64_t b_hi = make_smem_desc(sa + 2 * A_TILE_BYTES);
+                    const uint64_t b_lo = make_smem_desc(sa + 2 * A_TILE_BYTES + B_TILE_BYTES);
+                    // small terms first, then the main product; k advances 32 bytes inside the swizzled row
+#pragma unroll
+                    for (int k = 0; k < BK / UMMA_K; ++k)
+                        tc_mma_tf32(d_tmem, a_lo + (uint64_t)(2 * k), b_hi + (uint64_t)(2 * k), idesc,
+                                    (kb > 0 || k > 0) ? 1u : 0u);
+#pragma unroll
+                    for (int k = 0; k < BK / UMMA_K; ++k)
+                        tc_mma_tf32(d_tmem, a_hi + (uint64_t)(2 * k), b_lo + (uint64_t)(2 * k), idesc, 1u);
+#pragma unroll
+                    for (int k = 0; k < BK / UMMA_K; ++k)
+                        tc_mma_tf32(d_tmem, a_hi + (uint64_t)(2 * k), b_hi + (uint64_t)(2 * k), idesc, 1u);
+                    tc_commit(bar_empty(s));  // the stage is free once these MMAs have read it
+                }
+                if (ok) tc_commit(bar_acc_full(b));
+            }
+            if (!ok) {
+                // MMAs already issued still read shared memory and write tensor memory: drain, bounded
+                tc_commit(bar_drain);
+                const unsigned long long t0 = globaltimer_ns();
+                while (!mbar_try_wait(bar_drain, 0)) {
+                    if (globaltimer_ns() - t0 > kWaitLimitNs) {
+                        atomicCAS(p.status, 0, (int)kErrDrain);
+                        break;
+                    }
+                }
+            }
+        }
+    } else if (warp < 6) {
+        // ---------------- split warps: raw A -> hi (in place), lo ----------------
+        const int tid = threadIdx.x - 64;  // 0..127
+        uint32_t it = 0;
+        bool ok = true;
+        for (int tile = blockIdx.x; tile < p.num_tiles && ok; tile += gridDim.x) {
+            for (int kb = 0; kb < KB; ++kb, ++it) {
+                const int s = it % kStages;
+                const uint32_t ph = (it / kStages) & 1u;
+                if (!mbar_wait(bar_full(s), ph, abort_flag, p.status, kErrWaitFull)) {
+                    ok = false;
+                    break;
+                }
+                float4 *hi = reinterpret_cast<float4 *>(stage_base + s * STAGE_BYTES);
+                float4 *lo = reinterpret_cast<float4 *>(stage_base + s * STAGE_BYTES + A_TILE_BYTES);
+#pragma unroll
+                for (int j = 0; j < A_TILE_BYTES / 16 / 128; ++j) {
+                    const int i = tid + 128 * j;
+                    const float4 v = hi[i];
+                    float4 h, l;
+                    split_tf32(v.x, h.x, l.x);
+                    split_tf32(v.y, h.y, l.y);
+                    split_tf32(v.z, h.z, l.z);
+                    split_tf32(v.w, h.w, l.w);
+                    hi[i] = h;
+                    lo[i] = l;
+                }
+                fence_generic_to_async_smem();
+                mbar_arrive(bar_split(s));
+            }
+        }
+    } else {
+        // ---------------- epilogue warps ----------------
+        const int q = warp & 3;  // TMEM lane quarter this warp may read
+        float *tr = epi + (warp - 6) * 32 * kEpiPad;
+        uint32_t t = 0;
+        bool ok = true;
+        const bool has_bias = p.bias != nullptr;
+        for (int tile = blockIdx.x; tile < p.num_tiles && ok; tile += gridDim.x, ++t) {
+            const int b = t & 1;
+            // warp-uniform outcome: the tensor-memory loads below are warp-collective
+            if (!__all_sync(kFullMask, mbar_wait(bar_acc_full(b), (t >> 1) & 1u, abort_flag, p.status, kErrWaitAccFull))) {
+                ok = false;
+                break;
+            }
+            tc_fence_after();
+            const int64_t row0 = (int64_t)tile * BM + q * 32;
+            for (int c0 = 0; c0 < p.N; c0 += 32) {
+                uint32_t r[32];
+                tc_ld_32x32(tmem_base + (uint32_t)(b * kAccStride + c0) + ((uint32_t)(q * 32) << 16), r);
+#pragma unroll
+                for (int j = 0; j < 32; ++j) tr[lane * kEpiPad + j] = __uint_as_float(r[j]);
+                __syncwarp();
+                const int col = c0 + lane;
+                const bool col_ok = col < p.N;
+                const float bv = (has_bias && col_ok) ? __ldg(p.bias + col) : 0.0f;
+                if (col_ok) {
+#pragma unroll 4
+                    for (int rr = 0; rr < 32; ++rr) {
+                        const int64_t row = row0 + rr;
+                        if (row >= p.M) break;
+                        float v = tr[rr * kEpiPad + lane] + bv;
+                        float *dst = p.C + row * p.ldc + col;
+                        if (p.accumulate) v += *dst;
+                        *dst = v;
+                    }
+                }
+                __syncwarp();
+            }
+            tc_fence_before();
+            mbar_arrive(bar_acc_empty(b));
+        }
+    }
+
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)kTmemCols)
+                     : "memory");
+    }
+}
+
+// W[N,K] (row stride ldb) -> hi / lo pieces with row stride ldw.
+__global__ void split_weight_kernel(const float *__restrict__ W, int64_t ldb, int N, int K, int ldw,
+                                    float *__restrict__ hi, float *__restrict__ lo) {
+    const int64_t total = (int64_t)N * ldw;
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+        const int n = (int)(i / ldw), k = (int)(i % ldw);
+        float h = 0.0f, l = 0.0f;
+        if (k < K) split_tf32(W[(int64_t)n * ldb + k], h, l);
+        hi[i] = h;
+        lo[i] = l;
+    }
+}
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
+                                  const cuuint64_t *, const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_fn() {
+    static EncodeTiledFn fn = nullptr;
+    static std::once_flag once;
+    std::call_once(once, [] {
+        void *ptr = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &q) == cudaSuccess &&
+            q == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<EncodeTiledFn>(ptr);
+    });
+    return fn;
+}
+
+// 2-D fp32 tensor map: `cols` contiguous elements per row, `rows` rows of stride ld elements;
+// box = {32 columns, box_rows}, 128-byte swizzle, out-of-range elements read as zero.
+int make_map(CUtensorMap *map, const float *base, int64_t rows, int64_t cols, int64_t ld, int box_rows) {
+    EncodeTiledFn fn = encode_fn();
+    if (fn == nullptr) return fail(GNNAGG_ERR_CUDA, "dense: cuTensorMapEncodeTiled is not available from the driver");
+    const cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
+    const cuuint64_t strides[1] = {(cuuint64_t)ld * 4};
+    const cuuint32_t box[2] = {(cuuint32_t)BK, (cuuint32_t)box_rows};
+    const cuuint32_t estr[2] = {1, 1};
+    const CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, const_cast<float *>(base), dims, strides, box, estr,
+                          CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                          CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return fail(GNNAGG_ERR_CUDA, "dense: cuTensorMapEncodeTiled failed with code %d", (int)r);
+    return GNNAGG_OK;
+}
+
+inline int round_up(int v, int m) { return (v + m - 1) / m * m; }
+inline size_t piece_bytes(int N, int K) { return ((size_t)N * round_up(K, 4) * 4 + 255) / 256 * 256; }
+
+}  // namespace
+}  // namespace gnnagg
+
+using namespace gnnagg;
+
+extern "C" size_t gnnagg_dense_workspace_bytes(int32_t N, int32_t K) {
+    if (N <= 0 || K <= 0) return kStatusBytes;
+    return kStatusBytes + 2 * piece_bytes(N, K);
+}
+
+extern "C" int gnnagg_dense_tf32x3_f32(const float *A, int64_t lda, const float *B, int64_t ldb, float *C, int64_t ldc,
+                                       int64_t M, int32_t N, int32_t K, const float *bias, int32_t accumulate,
+                                       void *workspace, size_t workspace_bytes, void *stream) {
+    if (M < 0 || N < 0 || K < 0 || (accumulate != 0 && accumulate != 1))
+        return fail(GNNAGG_ERR_ARG, "dense: negative size or bad accumulate flag");
+    if (M == 0 || N == 0) return GNNAGG_OK;
+    if (A == nullptr || B == nullptr || C == nullptr || workspace == nullptr)
+        return fail(GNNAGG_ERR_ARG, "dense: null pointer");
+    if (K == 0) return fail(GNNAGG_ERR_UNSUPPORTED, "dense: K = 0");
+    if (N > kMaxN) return fail(GNNAGG_ERR_UNSUPPORTED, "dense: N = %d exceeds %d output columns", N, kMaxN);
+    if (lda < K || ldb < K || ldc < N) return fail(GNNAGG_ERR_ARG, "dense: leading dimension smaller than the row");
+    if (!aligned16(A) || (lda % 4) != 0)
+        return fail(GNNAGG_ERR_UNSUPPORTED, "dense: A must be 16-byte aligned with a row stride that is a multiple of 4");
+    if (M > (int64_t)INT32_MAX - BM) return fail(GNNAGG_ERR_UNSUPPORTED, "dense: M too large for 32-bit tile coordinates");
+    if (!aligned16(workspace) || workspace_bytes < gnnagg_dense_workspace_bytes(N, K))
+        return fail(GNNAGG_ERR_SCRATCH, "dense: workspace too small or misaligned (need %zu bytes)",
+                    gnnagg_dense_workspace_bytes(N, K));
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+
+    const int ldw = round_up(K, 4);
+    const int n_pad = round_up(N, 16);
+    uint8_t *ws = static_cast<uint8_t *>(workspace);
+    float *w_hi = reinterpret_cast<float *>(ws + kStatusBytes);
+    float *w_lo = reinterpret_cast<float *>(ws + kStatusBytes + piece_bytes(N, K));
+
+    static std::once_flag attr_once;
+    static cudaError_t attr_err = cudaSuccess;
+    std::call_once(attr_once, [] {
+        attr_err = cudaFuncSetAttribute(gemm_tf32x3_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
+    });
+    if (attr_err != cudaSuccess)
+        return fail(GNNAGG_ERR_CUDA, "dense: cannot reserve %d bytes of shared memory: %s", SMEM_BYTES,
+                    cudaGetErrorString(attr_err));
+
+    CUtensorMap map_a, map_bhi, map_blo;
+    int rc = make_map(&map_a, A, M, K, lda, BM);
+    if (rc == GNNAGG_OK) rc = make_map(&map_bhi, w_hi, N, K, ldw, n_pad);
+    if (rc == GNNAGG_OK) rc = make_map(&map_blo, w_lo, N, K, ldw, n_pad);
+    if (rc != GNNAGG_OK) return rc;
+
+    {
+        const int64_t total = (int64_t)N * ldw;
+        const unsigned blocks = (unsigned)((total + 255) / 256 > 1024 ? 1024 : (total + 255) / 256);
+        split_weight_kernel<<<blocks, 256, 0, st>>>(B, ldb, N, K, ldw, w_hi, w_lo);
+        rc = check_launch("split_weight_kernel");
+        if (rc != GNNAGG_OK) return rc;
+    }
+
+    GemmParams p;
+    p.C = C;
+    p.bias = bias;
+    p.status = reinterpret_cast<int *>(ws);
+    p.M = M;
+    p.ldc = ldc;
+    p.N = N;
+    p.n_pad = n_pad;
+    p.K = K;
+    p.accumulate = accumulate;
+    p.num_tiles = (int)((M + BM - 1) / BM);
+    const int grid = p.num_tiles < kNumSMs ? p.num_tiles : kNumSMs;
+    gemm_tf32x3_kernel<<<grid, kThreads, SMEM_BYTES, st>>>(map_a, map_bhi, map_blo, p);
+    return check_launch("gemm_tf32x3_kernel");
+}
+
+extern "C" int gnnagg_dense_status(const void *workspace, void *stream) {
+    if (workspace == nullptr) return fail(GNNAGG_ERR_ARG, "dense_status: null workspace");
+    int code = 0;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    cudaError_t e = cudaMemcpyAsync(&code, workspace, sizeof(int), cudaMemcpyDeviceToHost, st);
+    if (e == cudaSuccess) e = cudaStreamSynchronize(st);
+    if (e != cudaSuccess) return fail(GNNAGG_ERR_CUDA, "dense_status: %s", cudaGetErrorString(e));
+    return code;
+}

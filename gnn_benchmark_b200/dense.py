@@ -1,0 +1,160 @@
+"""Dense feature transforms either side of the aggregation, on the tensor cores.
+
+The reference's layer computes lin_neigh(aggr / deg) + lin_self(x) + bias with two fp32 nn.Linear
+calls and two in-place adds (self_benchmark/a64fx/model/layers/sageconv.py:82-91).  Here the same
+arithmetic goes through `gnnagg_dense_tf32x3_f32`: a tcgen05 GEMM that keeps fp32-grade accuracy by
+splitting every operand into two TF32 pieces (three tensor-core products per fp32 product), with
+the bias and the second product accumulated in the kernel's epilogue.
+
+`linear(x, weight, bias, out, accumulate)` is the plain call; `SageDense` and `LinearTC` are the
+autograd nodes the models use.  Weight gradients (G^T X: a reduction over all rows into a small
+matrix) stay on cuBLAS.  Shapes the kernel does not take (more than 256 output columns, rows of
+the left operand not 16-byte aligned) also go to cuBLAS: `supported()` says which.
+"""
+import os
+
+import torch
+
+from . import _lib
+
+MAX_N = 256
+# "tf32x3": use the tensor-core kernel wherever `supported()`; "cublas": plain torch fp32 matmul.
+MODE = os.environ.get("GNNAGG_DENSE", "cublas")
+
+_workspaces = {}
+
+
+def enabled() -> bool:
+    return MODE == "tf32x3"
+
+
+def supported(a: torch.Tensor, n_out: int) -> bool:
+    """Can `a` (M x K fp32) be the left operand of the tensor-core kernel with n_out output columns?"""
+    return (a.is_cuda and a.dtype == torch.float32 and a.dim() == 2 and a.size(1) > 0 and a.stride(1) == 1
+            and a.stride(0) % 4 == 0 and a.data_ptr() % 16 == 0 and 0 < n_out <= MAX_N
+            and a.size(0) < 2 ** 31 - 128)
+
+
+def _workspace(device: torch.device, n: int, k: int) -> torch.Tensor:
+    key = (device.index, _lib.stream_ptr(device), n, k)
+    ws = _workspaces.get(key)
+    if ws is None:
+        nbytes = _lib.lib().gnnagg_dense_workspace_bytes(n, k)
+        ws = torch.zeros(nbytes, dtype=torch.uint8, device=device)  # zeroed: the status word starts at 0
+        _workspaces[key] = ws
+    return ws
+
+
+def linear(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor = None, out: torch.Tensor = None,
+           accumulate: bool = False) -> torch.Tensor:
+    """out (+)= x @ weight.T (+ bias) through the C ABI.  x (M,K), weight (N,K), out (M,N), all fp32."""
+    _lib.require_cuda(x, weight, bias, out)
+    if x.dim() != 2 or weight.dim() != 2 or x.size(1) != weight.size(1):
+        raise RuntimeError(f"dense.linear: shape mismatch x={tuple(x.shape)} weight={tuple(weight.shape)}")
+    if x.dtype != torch.float32 or weight.dtype != torch.float32:
+        raise RuntimeError("dense.linear: operands must be float32")
+    M, K = x.shape
+    N = weight.size(0)
+    if out is None:
+        if accumulate:
+            raise RuntimeError("dense.linear: accumulate needs an output to accumulate into")
+        out = torch.empty(M, N, dtype=torch.float32, device=x.device)
+    if out.shape != (M, N) or out.dtype != torch.float32 or out.stride(1) != 1:
+        raise RuntimeError("dense.linear: out must be (M,N) float32 with unit inner stride")
+    if not supported(x, N):
+        raise RuntimeError("dense.linear: operand not supported by the tensor-core kernel (see supported())")
+    if weight.stride(1) != 1:
+        weight = weight.contiguous()
+    if bias is not None and (bias.dtype != torch.float32 or bias.numel() != N or not bias.is_contiguous()):
+        raise RuntimeError("dense.linear: bias must be a contiguous float32 vector of N elements")
+    if M == 0:
+        return out
+    ws = _workspace(x.device, N, K)
+    rc = _lib.lib().gnnagg_dense_tf32x3_f32(x.data_ptr(), x.stride(0), weight.data_ptr(), weight.stride(0),
+                                            out.data_ptr(), out.stride(0), M, N, K, _lib.ptr(bias),
+                                            1 if accumulate else 0, ws.data_ptr(), ws.numel(),
+                                            _lib.stream_ptr(x.device))
+    _lib.check(rc, "dense_tf32x3_f32")
+    return out
+
+
+def check_status(device=None) -> None:
+    """Synchronise and raise if any dense kernel on `device` gave up on a wait (diagnostic)."""
+    for (dev, _stream, n, k), ws in list(_workspaces.items()):
+        if device is not None and torch.device(device).index not in (None, dev):
+            continue
+        code = _lib.lib().gnnagg_dense_status(ws.data_ptr(), _lib.stream_ptr(ws.device))
+        if code != 0:
+            raise RuntimeError(f"dense kernel (N={n}, K={k}) reported status {code}: "
+                               + ("a bounded wait inside the kernel ran out" if code > 0 else
+                                  _lib.lib().gnnagg_error_string(code).decode()))
+
+
+def _matmul_nt(a: torch.Tensor, w: torch.Tensor, bias=None, out=None, accumulate=False) -> torch.Tensor:
+    """a @ w.T (+bias), tensor-core kernel when it takes the shape, cuBLAS otherwise."""
+    if enabled() and supported(a, w.size(0)):
+        return linear(a, w, bias, out, accumulate)
+    r = a @ w.t()
+    if bias is not None:
+        r += bias
+    if out is None:
+        return r
+    if accumulate:
+        out += r
+    else:
+        out.copy_(r)
+    return out
+
+
+class LinearTC(torch.autograd.Function):
+    """y = x @ W^T (+ b) with the forward and the input gradient on the tensor-core kernel."""
+
+    @staticmethod
+    def forward(ctx, x, weight, bias):
+        ctx.save_for_backward(x, weight)
+        ctx.has_bias = bias is not None
+        return _matmul_nt(x, weight, bias)
+
+    @staticmethod
+    def backward(ctx, g):
+        x, weight = ctx.saved_tensors
+        g = g.contiguous()
+        gx = gw = gb = None
+        if ctx.needs_input_grad[0]:
+            gx = _matmul_nt(g, weight.t().contiguous())
+        if ctx.needs_input_grad[1]:
+            gw = g.t() @ x
+        if ctx.has_bias and ctx.needs_input_grad[2]:
+            gb = g.sum(0)
+        return gx, gw, gb
+
+
+class SageDense(torch.autograd.Function):
+    """out = aggr @ Wn^T + x @ Ws^T (+ b): the dense half of a GraphSAGE layer as one node (the second
+    product and the bias are accumulated by the kernel's epilogue instead of separate passes)."""
+
+    @staticmethod
+    def forward(ctx, aggr, x, w_neigh, w_self, bias):
+        ctx.save_for_backward(aggr, x, w_neigh, w_self)
+        ctx.has_bias = bias is not None
+        out = torch.empty(aggr.size(0), w_neigh.size(0), dtype=torch.float32, device=aggr.device)
+        _matmul_nt(aggr, w_neigh, None, out, False)
+        _matmul_nt(x, w_self, bias, out, True)
+        return out
+
+    @staticmethod
+    def backward(ctx, g):
+        aggr, x, w_neigh, w_self = ctx.saved_tensors
+        g = g.contiguous()
+        g_aggr = g_x = g_wn = g_ws = g_b = None
+        if ctx.needs_input_grad[0]:
+            g_aggr = _matmul_nt(g, w_neigh.t().contiguous())
+        if ctx.needs_input_grad[1]:
+            g_x = _matmul_nt(g, w_self.t().contiguous())
+        if ctx.needs_input_grad[2]:
+            g_wn = g.t() @ aggr
+        if ctx.needs_input_grad[3]:
+            g_ws = g.t() @ x
+        if ctx.has_bias and ctx.needs_input_grad[4]:
+            g_b = g.sum(0)
+        return g_aggr, g_x, g_wn, g_ws, g_b

@@ -184,6 +184,34 @@ int gnnagg_dequant_v1_rows(const uint8_t *codes, int64_t rows, int32_t F, const 
 int gnnagg_cast_f32_to_bf16(const float *src, void *dst_bf16, int64_t n, void *stream);
 int gnnagg_cast_bf16_to_f32(const void *src_bf16, float *dst, int64_t n, void *stream);
 
+/* ------------------------------------------------------------------------------------
+ * N1  dense feature transform on the tensor cores (the step either side of the aggregation)
+ *
+ *     C[M,N] (+)= A[M,K] . B[N,K]^T (+ bias[N])        fp32 in, fp32 out, row-major
+ *
+ * Replaces the fp32 nn.Linear calls of the layer around the aggregation op
+ * (model/layers/sageconv.py:82-91: lin_neigh(out) + lin_self(x) + bias) and their input
+ * gradients.  B is a Linear weight (out_features x in_features).  Every operand is split into two
+ * TF32 pieces and three tcgen05 products are accumulated in fp32 (error about 2^-21 per product
+ * relative to |a||b|: fp32-grade, not single-pass TF32).
+ *
+ *   N <= 256;  A 16-byte aligned with lda % 4 == 0 (TMA);  B, C, bias: any alignment.
+ *   workspace  gnnagg_dense_workspace_bytes(N, K) bytes, 16-byte aligned, ZEROED once by the
+ *              caller before its first use: the first 256 bytes hold a sticky status word, the
+ *              rest receives the split weight (rewritten by every call).
+ *   Calls sharing a workspace must be ordered on one stream.
+ *
+ * gnnagg_dense_status synchronises the stream and returns the status word: 0, or the positive
+ * code of the wait that ran out of time inside the kernel (1 free stage, 2 TMA load, 3 split
+ * tile, 4 accumulator release, 5 accumulator, 6 drain).  A kernel that gave up has freed its
+ * tensor memory and returned; C is then undefined.
+ * ---------------------------------------------------------------------------------- */
+size_t gnnagg_dense_workspace_bytes(int32_t N, int32_t K);
+int gnnagg_dense_tf32x3_f32(const float *A, int64_t lda, const float *B, int64_t ldb, float *C, int64_t ldc,
+                            int64_t M, int32_t N, int32_t K, const float *bias, int32_t accumulate,
+                            void *workspace, size_t workspace_bytes, void *stream);
+int gnnagg_dense_status(const void *workspace, void *stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -1,0 +1,104 @@
+"""Tensor-core dense transform (gnnagg_dense_tf32x3_f32) against an fp64 product.
+
+Tolerance: |C - C64| <= 2e-6 * (|A| |B|^T) element-wise.  A single-pass TF32 product misses this by
+two orders of magnitude (2^-11 per operand), fp32 FMA chains sit near 1e-7 * sqrt(K)."""
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def _case(M, N, K, bias, accumulate, lda_pad=0, ldc_pad=0, seed=0):
+    from gnn_benchmark_b200 import dense
+
+    g = torch.Generator(device="cuda").manual_seed(seed)
+    a_full = torch.randn(M, K + lda_pad, device="cuda", generator=g)
+    a = a_full[:, :K]
+    w = torch.randn(N, K, device="cuda", generator=g)
+    b = torch.randn(N, device="cuda", generator=g) if bias else None
+    c_full = torch.randn(M, N + ldc_pad, device="cuda", generator=g)
+    c = c_full[:, :N]
+    ref = a.double() @ w.double().t()
+    if bias:
+        ref += b.double()
+    if accumulate:
+        ref += c.double()
+    scale = a.abs().double() @ w.abs().double().t() + (c.abs().double() if accumulate else 0) + 1e-30
+    guard = c_full[:, N:].clone()
+    dense.linear(a, w, b, out=c, accumulate=accumulate)
+    dense.check_status()
+    err = ((c.double() - ref).abs() / scale).max().item()
+    assert err <= 2e-6, f"M={M} N={N} K={K}: relative error {err:.3e}"
+    assert torch.equal(c_full[:, N:], guard), "wrote outside the N output columns"
+
+
+@pytest.mark.parametrize("M,N,K", [
+    (128, 16, 32), (256, 64, 64), (1000, 256, 256), (128 * 148 * 2 + 77, 256, 100), (5000, 47, 256),
+    (3001, 100, 256), (4096, 172, 256), (70, 16, 8), (1, 256, 128), (129, 48, 36), (777, 128, 512),
+])
+def test_dense_matches_fp64(M, N, K):
+    _case(M, N, K, bias=False, accumulate=False)
+
+
+@pytest.mark.parametrize("bias,accumulate", [(True, False), (False, True), (True, True)])
+def test_dense_bias_and_accumulate(bias, accumulate):
+    _case(2500, 256, 256, bias, accumulate, seed=1)
+    _case(999, 47, 100, bias, accumulate, seed=2)
+
+
+def test_dense_strided_operands():
+    _case(1500, 172, 128, bias=True, accumulate=True, lda_pad=4, ldc_pad=3, seed=3)
+
+
+def test_dense_special_values():
+    from gnn_benchmark_b200 import dense
+
+    a = torch.randn(256, 64, device="cuda")
+    w = torch.randn(32, 64, device="cuda")
+    a[3, 5] = float("inf")
+    a[7, 0] = float("nan")
+    a[9] = 0
+    c = dense.linear(a, w)
+    dense.check_status()
+    ref = a @ w.t()
+    assert torch.isnan(c[7]).all() and torch.equal(torch.isnan(c), torch.isnan(ref))
+    assert torch.equal(torch.isinf(c), torch.isinf(ref)) and torch.equal(c[9], torch.zeros_like(c[9]))
+
+
+def test_dense_rejects_unsupported():
+    from gnn_benchmark_b200 import dense
+
+    a = torch.randn(64, 47, device="cuda")  # 188-byte rows: not TMA-addressable
+    w = torch.randn(16, 47, device="cuda")
+    assert not dense.supported(a, 16)
+    with pytest.raises(RuntimeError):
+        dense.linear(a, w)
+    assert not dense.supported(torch.randn(64, 64, device="cuda"), 300)
+
+
+def test_sage_dense_autograd_matches_torch():
+    from gnn_benchmark_b200 import dense
+
+    old = dense.MODE
+    dense.MODE = "tf32x3"
+    try:
+        g = torch.Generator(device="cuda").manual_seed(5)
+        aggr = torch.randn(3000, 100, device="cuda", generator=g, requires_grad=True)
+        x = torch.randn(3000, 100, device="cuda", generator=g, requires_grad=True)
+        wn = torch.randn(256, 100, device="cuda", generator=g, requires_grad=True)
+        ws = torch.randn(256, 100, device="cuda", generator=g, requires_grad=True)
+        b = torch.randn(256, device="cuda", generator=g, requires_grad=True)
+        go = torch.randn(3000, 256, device="cuda", generator=g)
+        out = dense.SageDense.apply(aggr, x, wn, ws, b)
+        out.backward(go)
+        got = [out.detach()] + [t.grad.clone() for t in (aggr, x, wn, ws, b)]
+        for t in (aggr, x, wn, ws, b):
+            t.grad = None
+        ref = aggr.double() @ wn.double().t() + x.double() @ ws.double().t() + b.double()
+        ref.backward(go.double())
+        want = [ref.detach()] + [t.grad for t in (aggr, x, wn, ws, b)]
+        dense.check_status()
+        for a_, b_ in zip(got, want):
+            torch.testing.assert_close(a_.double(), b_.double(), rtol=1e-5, atol=1e-3)
+    finally:
+        dense.MODE = old
