@@ -34,6 +34,7 @@ SIGNATURES = {
                                                           _i32, _vp, _vp]),
     "gnnagg_csr_validate": (ctypes.c_int, [_vp, _vp, _i64, _i64, _i64, _vp, _vp]),
     "gnnagg_gather_rows_f32": (ctypes.c_int, [_vp, _i64, _vp, _i64, _i32, _vp, _i64, _vp]),
+    "gnnagg_scale_rows_f32": (ctypes.c_int, [_vp, _i64, _vp, _i64, _i32, _i32, _vp, _i64, _vp]),
     "gnnagg_quant_pack_rows": (ctypes.c_int, [_vp, _i64, _vp, _i32, _vp, _i32, _i64, _i32, _i32, _vp, _vp, _vp, _vp]),
     "gnnagg_unpack_dequant_rows": (ctypes.c_int, [_vp, _i32, _vp, _i32, _i64, _i32, _vp, _vp, _vp, _i64, _vp]),
     "gnnagg_quant_v1_rows": (ctypes.c_int, [_vp, _i64, _i64, _i32, _vp, _vp, _vp, _vp]),
@@ -44,6 +45,11 @@ SIGNATURES = {
     "gnnagg_dense_tf32x3_f32": (ctypes.c_int, [_vp, _i64, _vp, _i64, _vp, _i64, _i64, _i32, _i32, _vp, _i32, _vp, _sz,
                                                _vp]),
     "gnnagg_dense_status": (ctypes.c_int, [_vp, _vp]),
+    "gnnagg_dropout_ln_relu_partial_bytes": (_sz, [_i32]),
+    "gnnagg_dropout_ln_relu_fwd": (ctypes.c_int, [_vp, _i64, _i64, _i32, _vp, _vp, ctypes.c_float, ctypes.c_float,
+                                                  ctypes.c_uint64, _vp, _i64, _vp, _vp, _vp]),
+    "gnnagg_dropout_ln_relu_bwd": (ctypes.c_int, [_vp, _i64, _vp, _i64, _vp, _vp, _vp, _vp, _i64, _i32, ctypes.c_float,
+                                                  _vp, _i64, _vp, _sz, _vp, _vp, _vp]),
 }
 
 

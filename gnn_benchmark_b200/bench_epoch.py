@@ -19,7 +19,7 @@ import time
 import torch
 import torch.distributed as dist
 
-from . import graphgen
+from . import dense, graphgen
 from .communicator import Communicator
 from .data_manager.DataLoader import build_graph
 from .model import create_model_and_optimizer, set_random_seed
@@ -55,11 +55,15 @@ def main():
     ap.add_argument("--lean-halo", type=int, default=1,
                     help="packed halo modes: no fp32 staging buffers (they are tens of GB per GPU at this scale)")
     ap.add_argument("--seed", type=int, default=20261130)
+    ap.add_argument("--dense", default="tf32x3", choices=["tf32x3", "cublas"],
+                    help="the layers' fp32 transforms: tensor-core kernel (three TF32 products per fp32 product, fp32 "
+                         "accumulate) or cuBLAS fp32 SIMT kernels")
     ap.add_argument("--kernel-table", default="",
                     help="after the timed epochs, run one more under torch.profiler and write rank 0's per-kernel "
                          "device-time table to this file (a breakdown, never a timing)")
     args = ap.parse_args()
 
+    dense.MODE = args.dense
     comm = Communicator(args.bits, is_async=True)
     if "RANK" in __import__("os").environ:
         rank, world = comm.init_dist_group("nccl")
@@ -99,6 +103,7 @@ def main():
     torch.cuda.synchronize()
     setup_s = time.time() - t0
     losses, times = train(model, data, optimizer, args.epochs, args.bits, eval_every_epoch=False, log=None)
+    dense.check_status()  # raises if a tensor-core kernel gave up on one of its bounded waits
     t = torch.tensor([sum(times[1:]) / max(len(times) - 1, 1), float(nnz_rank),
                       float(sum(graph.comm_splits.send_splits)), torch.cuda.max_memory_allocated() / 2 ** 30],
                      dtype=torch.float64, device=device)
@@ -115,7 +120,9 @@ def main():
             "config": {"model": args.model, "dims": dims, "nodes": args.nodes, "directed_edges_after_symmetrising":
                        int(tsum[1]), "halo": f"{args.bits}-bit" + (" pre/post" if args.pre else "") + (", no fp32 staging buffers" if lean else ""),
                        "halo_rows_sent_per_exchange": int(tsum[2]), "graph": "Chung-Lu gamma=2.1, relabelled",
-                       "epochs_timed": len(times) - 1, "dropout": args.dropout, "optimizer": "Adam lr 0.01"},
+                       "epochs_timed": len(times) - 1, "dropout": args.dropout, "optimizer": "Adam lr 0.01",
+                       "dense": ("tcgen05, 3 TF32 products per fp32 product, fp32 accumulate" if args.dense == "tf32x3"
+                                 else "cuBLAS fp32")},
             "losses": [round(x, 5) for x in losses], "epoch_times_s": [round(x, 4) for x in times],
             "peak_mem_gib_max_rank": float(tmax[3]), "setup_s": round(setup_s, 1), "data": "synthetic",
         }), flush=True)

@@ -5,15 +5,17 @@
 // in fp32-grade accuracy: every operand is split into two TF32 pieces, x = hi + lo with
 // hi = tf32_rna(x), lo = tf32_rna(x - hi), and three tensor-core products a_lo.b_hi + a_hi.b_lo +
 // a_hi.b_hi are accumulated in fp32 in tensor memory (the dropped a_lo.b_lo term is below 2^-22
-// relative).  The weight is split once per call by a small kernel into a caller-provided workspace;
-// the activation panel is split inside the GEMM, in shared memory, between the TMA load and the MMA.
+// relative).  The weight is split once per call by a small kernel into a caller-provided workspace.
+// The activation panel is used as loaded for its "hi" products (the tensor core reads the upper 19
+// bits of an fp32 word); its remainder panel is computed inside the GEMM, in shared memory, while
+// those products already run.
 //
 // One persistent CTA per SM, 10 warps:
 //   warp 0      lane 0 issues the TMA loads (A raw, B_hi, B_lo per 32-wide k-block; two stages) and
 //               prefetches the next row panel of A into L2;
 //   warp 1      allocates tensor memory; lane 0 issues tcgen05.mma (128 x N x 8 per instruction) and
 //               the commits that free a stage / publish an accumulator;
-//   warps 2-5   split the raw A tile of a stage into hi (in place) and lo (second buffer);
+//   warps 2-5   compute the remainder (lo) panel of a stage's A tile into a second buffer;
 //   warps 6-9   epilogue: tcgen05.ld of a finished accumulator (two of them in tensor memory, so the
 //               epilogue of one row panel runs under the MMAs of the next), 32x32 transposes through
 //               shared memory, coalesced stores with optional bias and accumulate.
@@ -22,26 +24,34 @@
 #include <cuda.h>
 
 #include <mutex>
+#include <stdlib.h>
 
 #include "common.cuh"
 
 namespace gnnagg {
 namespace {
 
+#ifndef GNNAGG_DENSE_BK
+#define GNNAGG_DENSE_BK 32
+#endif
 constexpr int BM = 128;                 // rows of A per tile = UMMA M = TMEM lanes
-constexpr int BK = 32;                  // fp32 per k-block: 128 bytes = one 128B-swizzle row
+constexpr int BK = GNNAGG_DENSE_BK;     // fp32 per k-block: one swizzle row (16 -> 64-byte, 32 -> 128-byte swizzle)
+static_assert(BK == 16 || BK == 32, "k-block is one 64-byte or one 128-byte swizzle row");
+constexpr int kRowBytes = BK * 4;
 constexpr int UMMA_K = 8;               // tf32 elements per tcgen05.mma
-constexpr int kStages = 2;
+constexpr int kStages = 64 / BK;        // 4 stages of 48 KB or 2 stages of 96 KB
 constexpr int kMaxN = 256;
 constexpr int kTmemCols = 512;          // two accumulators of up to 256 columns
 constexpr int kAccStride = 256;         // column offset of the second accumulator
-constexpr int A_TILE_BYTES = BM * BK * 4;       // 16 KB
-constexpr int B_TILE_BYTES = kMaxN * BK * 4;    // 32 KB reserved per piece
+constexpr int A_TILE_BYTES = BM * kRowBytes;
+constexpr int B_TILE_BYTES = kMaxN * kRowBytes;  // reserved per piece
 constexpr int STAGE_BYTES = 2 * A_TILE_BYTES + 2 * B_TILE_BYTES;  // a_hi, a_lo, b_hi, b_lo
 constexpr int kEpiPad = 33;
-constexpr int EPI_BYTES = 4 * 32 * kEpiPad * 4;
+constexpr int kEpiTile = 32 * 32 * 4;   // one 32 x 32 fp32 output block
+constexpr int EPI_BYTES = 4 * 2 * kEpiTile;  // per epilogue warp: two blocks (TMA store double buffer)
+constexpr int BIAS_BYTES = kMaxN * 4;
 constexpr int kNumBarriers = 3 * kStages + 4 + 1;
-constexpr int SMEM_BYTES = 1024 + kStages * STAGE_BYTES + EPI_BYTES + 256;
+constexpr int SMEM_BYTES = 1024 + kStages * STAGE_BYTES + EPI_BYTES + BIAS_BYTES + 256;
 constexpr int kThreads = 320;
 constexpr unsigned long long kWaitLimitNs = 1000ull * 1000ull * 1000ull;
 constexpr int kStatusBytes = 256;
@@ -109,6 +119,24 @@ __device__ __forceinline__ void tma_prefetch_2d(const CUtensorMap *map, int x, i
     asm volatile("cp.async.bulk.prefetch.tensor.2d.L2.global [%0, {%1, %2}];" ::"l"(map), "r"(x), "r"(y) : "memory");
 }
 
+// Shared -> global tile store / add through the tensor map (rows and columns outside the tensor are clipped).
+__device__ __forceinline__ void tma_store_2d(const CUtensorMap *map, uint32_t src, int x, int y) {
+    asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];" ::"l"(map), "r"(src),
+                 "r"(x), "r"(y)
+                 : "memory");
+}
+__device__ __forceinline__ void tma_reduce_add_2d(const CUtensorMap *map, uint32_t src, int x, int y) {
+    asm volatile("cp.reduce.async.bulk.tensor.2d.global.shared::cta.add.bulk_group [%0, {%2, %3}], [%1];" ::"l"(map),
+                 "r"(src), "r"(x), "r"(y)
+                 : "memory");
+}
+__device__ __forceinline__ void tma_store_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+template <int kPending>
+__device__ __forceinline__ void tma_store_wait_read() {
+    asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(kPending) : "memory");
+}
+__device__ __forceinline__ void tma_store_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
+
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void fence_generic_to_async_smem() {
@@ -159,16 +187,24 @@ __device__ __forceinline__ void split_tf32(float x, float &hi, float &lo) {
     lo = (fabsf(hi) <= 3.402823466e38f) ? tf32_rna(rest) : 0.0f;  // inf / nan stay in hi alone
 }
 
-// Shared-memory matrix descriptor of a K-major tile whose rows are 128 bytes, 128B-swizzled
-// (what TMA writes for a {32 fp32, rows} box): start address, 8-row group stride 1024 bytes,
-// descriptor version 1 (sm_100), layout type 2 (128-byte swizzle).
+// The activation panel is used as loaded for the "hi" products: the tensor core reads the upper 19
+// bits of each fp32 word, i.e. hi = x with the low 13 mantissa bits cut.  lo is the remainder.
+__device__ __forceinline__ float lo_of_truncated(float x) {
+    const float hi = __uint_as_float(__float_as_uint(x) & 0xFFFFE000u);
+    const float rest = x - hi;  // exact
+    return (fabsf(hi) <= 3.402823466e38f) ? tf32_rna(rest) : 0.0f;
+}
+
+// Shared-memory matrix descriptor of a K-major tile whose rows are one swizzle row (64 or 128 bytes,
+// what TMA writes for a {BK fp32, rows} box): start address, stride between 8-row groups,
+// descriptor version 1 (sm_100), layout type 2 (128-byte swizzle) or 4 (64-byte swizzle).
 __device__ __forceinline__ uint64_t make_smem_desc(uint32_t smem_addr) {
     uint64_t d = 0;
     d |= (uint64_t)((smem_addr & 0x3FFFFu) >> 4);       // bits [0,14)
     d |= (uint64_t)1 << 16;                              // leading byte offset (unused for swizzled K-major)
-    d |= (uint64_t)(1024 >> 4) << 32;                    // stride byte offset
+    d |= (uint64_t)((8 * kRowBytes) >> 4) << 32;         // stride byte offset
     d |= (uint64_t)1 << 46;                              // descriptor version
-    d |= (uint64_t)2 << 61;                              // SWIZZLE_128B
+    d |= (uint64_t)(BK == 32 ? 2 : 4) << 61;             // swizzle mode
     return d;
 }
 
@@ -188,7 +224,7 @@ struct GemmParams {
     const float *bias;
     int *status;
     int64_t M, ldc;
-    int N, n_pad, K, accumulate, num_tiles;
+    int N, n_pad, K, accumulate, num_tiles, tma_store, dbg;
 };
 
 enum : int {
@@ -202,13 +238,15 @@ enum : int {
 
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_bhi,
-                   const __grid_constant__ CUtensorMap map_blo, const GemmParams p) {
+                   const __grid_constant__ CUtensorMap map_blo, const __grid_constant__ CUtensorMap map_c,
+                   const GemmParams p) {
     extern __shared__ uint8_t smem_raw[];
     // 1024-byte alignment: the swizzle pattern and the descriptors assume it
     uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
     uint8_t *stage_base = smem;
-    float *epi = reinterpret_cast<float *>(smem + kStages * STAGE_BYTES);
-    uint64_t *bars = reinterpret_cast<uint64_t *>(smem + kStages * STAGE_BYTES + EPI_BYTES);
+    uint8_t *epi = smem + kStages * STAGE_BYTES;
+    float *bias_s = reinterpret_cast<float *>(smem + kStages * STAGE_BYTES + EPI_BYTES);
+    uint64_t *bars = reinterpret_cast<uint64_t *>(smem + kStages * STAGE_BYTES + EPI_BYTES + BIAS_BYTES);
     uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + kNumBarriers);
     volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
 
@@ -222,7 +260,8 @@ gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int KB = (p.K + BK - 1) / BK;
-    const uint32_t b_bytes = (uint32_t)p.n_pad * BK * 4;
+    const uint32_t b_bytes = (uint32_t)p.n_pad * kRowBytes;
+    for (int i = threadIdx.x; i < kMaxN; i += kThreads) bias_s[i] = (p.bias != nullptr && i < p.N) ? p.bias[i] : 0.0f;
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < kStages; ++s) {
@@ -257,7 +296,7 @@ gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
             for (int tile = blockIdx.x; tile < p.num_tiles && ok; tile += gridDim.x) {
                 const int m0 = tile * BM;
                 const int next = tile + (int)gridDim.x;
-                if (next < p.num_tiles)
+                if (next < p.num_tiles && !(p.dbg & 32))
                     for (int kb = 0; kb < KB; ++kb) tma_prefetch_2d(&map_a, kb * BK, next * BM);
                 for (int kb = 0; kb < KB; ++kb, ++it) {
                     const int s = it % kStages;
@@ -267,6 +306,11 @@ gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
                         break;
                     }
                     const uint32_t sa = smem_u32(stage_base + s * STAGE_BYTES);
+                    if (p.dbg & 8) {
+                        mbar_arrive_expect_tx(bar_full(s), (uint32_t)A_TILE_BYTES);
+                        tma_load_2d(sa, &map_a, bar_full(s), kb * BK, m0);
+                        continue;
+                    }
                     mbar_arrive_expect_tx(bar_full(s), (uint32_t)A_TILE_BYTES + 2u * b_bytes);
                     tma_load_2d(sa, &map_a, bar_full(s), kb * BK, m0);
                     tma_load_2d(sa + 2 * A_TILE_BYTES, &map_bhi, bar_full(s), kb * BK, 0);
@@ -304,28 +348,38 @@ gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
                 for (int kb = 0; kb < KB; ++kb, ++it) {
                     const int s = it % kStages;
                     const uint32_t ph = (it / kStages) & 1u;
-                    if (!mbar_wait(bar_full(s), ph, abort_flag, p.status, kErrWaitFull) ||
-                        !mbar_wait(bar_split(s), ph, abort_flag, p.status, kErrWaitSplit)) {
+                    if (!mbar_wait(bar_full(s), ph, abort_flag, p.status, kErrWaitFull)) {
                         ok = false;
                         break;
                     }
                     tc_fence_after();
                     const uint32_t sa = smem_u32(stage_base + s * STAGE_BYTES);
-                    const uint64_t a_hi = make_smem_desc(sa);
+                    const uint64_t a_hi = make_smem_desc(sa);  // the panel as loaded
                     const uint64_t a_lo = make_smem_desc(sa + A_TILE_BYTES);
                     const uint64_t b_hi = make_smem_desc(sa + 2 * A_TILE_BYTES);
                     const uint64_t b_lo = make_smem_desc(sa + 2 * A_TILE_BYTES + B_TILE_BYTES);
-                    // small terms first, then the main product; k advances 32 bytes inside the swizzled row
+                    if (p.dbg & 16) {
+                        tc_mma_tf32(d_tmem, a_hi, b_hi, idesc, kb > 0 ? 1u : 0u);
+                        tc_commit(bar_empty(s));
+                        continue;
+                    }
+                    // the two products of the loaded panel start at once; k advances 32 bytes inside the swizzled row
 #pragma unroll
                     for (int k = 0; k < BK / UMMA_K; ++k)
-                        tc_mma_tf32(d_tmem, a_lo + (uint64_t)(2 * k), b_hi + (uint64_t)(2 * k), idesc,
+                        tc_mma_tf32(d_tmem, a_hi + (uint64_t)(2 * k), b_lo + (uint64_t)(2 * k), idesc,
                                     (kb > 0 || k > 0) ? 1u : 0u);
 #pragma unroll
                     for (int k = 0; k < BK / UMMA_K; ++k)
-                        tc_mma_tf32(d_tmem, a_hi + (uint64_t)(2 * k), b_lo + (uint64_t)(2 * k), idesc, 1u);
+                        tc_mma_tf32(d_tmem, a_hi + (uint64_t)(2 * k), b_hi + (uint64_t)(2 * k), idesc, 1u);
+                    // the remainder panel is ready a little later
+                    if (!mbar_wait(bar_split(s), ph, abort_flag, p.status, kErrWaitSplit)) {
+                        ok = false;
+                        break;
+                    }
+                    tc_fence_after();
 #pragma unroll
                     for (int k = 0; k < BK / UMMA_K; ++k)
-                        tc_mma_tf32(d_tmem, a_hi + (uint64_t)(2 * k), b_hi + (uint64_t)(2 * k), idesc, 1u);
+                        tc_mma_tf32(d_tmem, a_lo + (uint64_t)(2 * k), b_hi + (uint64_t)(2 * k), idesc, 1u);
                     tc_commit(bar_empty(s));  // the stage is free once these MMAs have read it
                 }
                 if (ok) tc_commit(bar_acc_full(b));
@@ -343,7 +397,7 @@ gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
             }
         }
     } else if (warp < 6) {
-        // ---------------- split warps: raw A -> hi (in place), lo ----------------
+        // ---------------- split warps: remainder panel of the loaded A tile ----------------
         const int tid = threadIdx.x - 64;  // 0..127
         uint32_t it = 0;
         bool ok = true;
@@ -355,18 +409,18 @@ gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
                     ok = false;
                     break;
                 }
-                float4 *hi = reinterpret_cast<float4 *>(stage_base + s * STAGE_BYTES);
+                const float4 *raw = reinterpret_cast<const float4 *>(stage_base + s * STAGE_BYTES);
                 float4 *lo = reinterpret_cast<float4 *>(stage_base + s * STAGE_BYTES + A_TILE_BYTES);
+                if (!(p.dbg & 4))
 #pragma unroll
                 for (int j = 0; j < A_TILE_BYTES / 16 / 128; ++j) {
                     const int i = tid + 128 * j;
-                    const float4 v = hi[i];
-                    float4 h, l;
-                    split_tf32(v.x, h.x, l.x);
-                    split_tf32(v.y, h.y, l.y);
-                    split_tf32(v.z, h.z, l.z);
-                    split_tf32(v.w, h.w, l.w);
-                    hi[i] = h;
+                    const float4 v = raw[i];
+                    float4 l;
+                    l.x = lo_of_truncated(v.x);
+                    l.y = lo_of_truncated(v.y);
+                    l.z = lo_of_truncated(v.z);
+                    l.w = lo_of_truncated(v.w);
                     lo[i] = l;
                 }
                 fence_generic_to_async_smem();
@@ -376,10 +430,10 @@ gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
     } else {
         // ---------------- epilogue warps ----------------
         const int q = warp & 3;  // TMEM lane quarter this warp may read
-        float *tr = epi + (warp - 6) * 32 * kEpiPad;
-        uint32_t t = 0;
+        uint8_t *my_epi = epi + (warp - 6) * 2 * kEpiTile;  // 1024-byte aligned
+        float *tr = reinterpret_cast<float *>(my_epi);
+        uint32_t t = 0, nstore = 0;
         bool ok = true;
-        const bool has_bias = p.bias != nullptr;
         for (int tile = blockIdx.x; tile < p.num_tiles && ok; tile += gridDim.x, ++t) {
             const int b = t & 1;
             // warp-uniform outcome: the tensor-memory loads below are warp-collective
@@ -389,16 +443,45 @@ gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
             }
             tc_fence_after();
             const int64_t row0 = (int64_t)tile * BM + q * 32;
-            for (int c0 = 0; c0 < p.N; c0 += 32) {
+            for (int c0 = 0; c0 < p.N && !(p.dbg & 2); c0 += 32) {
                 uint32_t r[32];
                 tc_ld_32x32(tmem_base + (uint32_t)(b * kAccStride + c0) + ((uint32_t)(q * 32) << 16), r);
+                if (p.tma_store) {
+                    // this thread's row of the 32 x 32 block goes to shared memory in the 128-byte-swizzled
+                    // layout of the output tensor map (16-byte chunk j of row r sits at chunk j ^ (r & 7)),
+                    // then one lane hands the block to TMA: plain store, or add for accumulate
+                    uint8_t *buf = my_epi + (nstore & 1u) * kEpiTile;
+                    if (lane == 0) tma_store_wait_read<1>();  // the store that last read this buffer is done with it
+                    __syncwarp();
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) {
+                        float4 v;
+                        v.x = __uint_as_float(r[4 * j + 0]) + bias_s[c0 + 4 * j + 0];
+                        v.y = __uint_as_float(r[4 * j + 1]) + bias_s[c0 + 4 * j + 1];
+                        v.z = __uint_as_float(r[4 * j + 2]) + bias_s[c0 + 4 * j + 2];
+                        v.w = __uint_as_float(r[4 * j + 3]) + bias_s[c0 + 4 * j + 3];
+                        *reinterpret_cast<float4 *>(buf + lane * 128 + ((j ^ (lane & 7)) << 4)) = v;
+                    }
+                    fence_generic_to_async_smem();
+                    __syncwarp();
+                    if (lane == 0 && !(p.dbg & 1)) {
+                        if (p.accumulate)
+                            tma_reduce_add_2d(&map_c, smem_u32(buf), c0, (int)row0);
+                        else
+                            tma_store_2d(&map_c, smem_u32(buf), c0, (int)row0);
+                        tma_store_commit();
+                    }
+                    ++nstore;
+                    continue;
+                }
+                // output rows that TMA cannot address (stride not a multiple of 16 bytes): transpose the block
+                // through shared memory and store row segments with plain coalesced stores
 #pragma unroll
                 for (int j = 0; j < 32; ++j) tr[lane * kEpiPad + j] = __uint_as_float(r[j]);
                 __syncwarp();
                 const int col = c0 + lane;
-                const bool col_ok = col < p.N;
-                const float bv = (has_bias && col_ok) ? __ldg(p.bias + col) : 0.0f;
-                if (col_ok) {
+                if (col < p.N && !(p.dbg & 1)) {
+                    const float bv = bias_s[col];
 #pragma unroll 4
                     for (int rr = 0; rr < 32; ++rr) {
                         const int64_t row = row0 + rr;
@@ -414,6 +497,7 @@ gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
             tc_fence_before();
             mbar_arrive(bar_acc_empty(b));
         }
+        if (p.tma_store && lane == 0) tma_store_wait_all();  // shared memory stays valid until TMA has read it
     }
 
     tc_fence_before();
@@ -456,16 +540,18 @@ EncodeTiledFn encode_fn() {
 }
 
 // 2-D fp32 tensor map: `cols` contiguous elements per row, `rows` rows of stride ld elements;
-// box = {32 columns, box_rows}, 128-byte swizzle, out-of-range elements read as zero.
-int make_map(CUtensorMap *map, const float *base, int64_t rows, int64_t cols, int64_t ld, int box_rows) {
+// box = {box_cols, box_rows} with box_cols * 4 bytes = the swizzle span; out-of-range elements read
+// as zero and are not written.
+int make_map(CUtensorMap *map, const float *base, int64_t rows, int64_t cols, int64_t ld, int box_cols, int box_rows) {
     EncodeTiledFn fn = encode_fn();
     if (fn == nullptr) return fail(GNNAGG_ERR_CUDA, "dense: cuTensorMapEncodeTiled is not available from the driver");
     const cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
     const cuuint64_t strides[1] = {(cuuint64_t)ld * 4};
-    const cuuint32_t box[2] = {(cuuint32_t)BK, (cuuint32_t)box_rows};
+    const cuuint32_t box[2] = {(cuuint32_t)box_cols, (cuuint32_t)box_rows};
     const cuuint32_t estr[2] = {1, 1};
+    const CUtensorMapSwizzle swz = box_cols == 32 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B;
     const CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, const_cast<float *>(base), dims, strides, box, estr,
-                          CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                          CU_TENSOR_MAP_INTERLEAVE_NONE, swz, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
                           CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS) return fail(GNNAGG_ERR_CUDA, "dense: cuTensorMapEncodeTiled failed with code %d", (int)r);
     return GNNAGG_OK;
@@ -518,10 +604,18 @@ extern "C" int gnnagg_dense_tf32x3_f32(const float *A, int64_t lda, const float 
         return fail(GNNAGG_ERR_CUDA, "dense: cannot reserve %d bytes of shared memory: %s", SMEM_BYTES,
                     cudaGetErrorString(attr_err));
 
-    CUtensorMap map_a, map_bhi, map_blo;
-    int rc = make_map(&map_a, A, M, K, lda, BM);
-    if (rc == GNNAGG_OK) rc = make_map(&map_bhi, w_hi, N, K, ldw, n_pad);
-    if (rc == GNNAGG_OK) rc = make_map(&map_blo, w_lo, N, K, ldw, n_pad);
+    // C goes out through TMA when its rows are 16-byte addressable, else through plain stores
+    const bool tma_store = aligned16(C) && (ldc % 4) == 0;
+    CUtensorMap map_a, map_bhi, map_blo, map_c;
+    int rc = make_map(&map_a, A, M, K, lda, BK, BM);
+    if (rc == GNNAGG_OK) rc = make_map(&map_bhi, w_hi, N, K, ldw, BK, n_pad);
+    if (rc == GNNAGG_OK) rc = make_map(&map_blo, w_lo, N, K, ldw, BK, n_pad);
+    if (rc == GNNAGG_OK) {
+        if (tma_store)
+            rc = make_map(&map_c, C, M, N, ldc, 32, 32);
+        else
+            map_c = map_a;  // unused
+    }
     if (rc != GNNAGG_OK) return rc;
 
     {
@@ -543,8 +637,10 @@ extern "C" int gnnagg_dense_tf32x3_f32(const float *A, int64_t lda, const float 
     p.K = K;
     p.accumulate = accumulate;
     p.num_tiles = (int)((M + BM - 1) / BM);
+    p.tma_store = tma_store ? 1 : 0;
+    p.dbg = getenv("GNNAGG_DENSE_DEBUG") ? atoi(getenv("GNNAGG_DENSE_DEBUG")) : 0;
     const int grid = p.num_tiles < kNumSMs ? p.num_tiles : kNumSMs;
-    gemm_tf32x3_kernel<<<grid, kThreads, SMEM_BYTES, st>>>(map_a, map_bhi, map_blo, p);
+    gemm_tf32x3_kernel<<<grid, kThreads, SMEM_BYTES, st>>>(map_a, map_bhi, map_blo, map_c, p);
     return check_launch("gemm_tf32x3_kernel");
 }
 

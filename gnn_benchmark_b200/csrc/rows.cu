@@ -52,3 +52,63 @@ extern "C" int gnnagg_gather_rows_f32(const float *X, int64_t ldx, const int32_t
         gather_rows_kernel<false><<<(unsigned)blocks, 256, 0, st>>>(X, ldx, idx, rows, fv, log2g, OUT, ldo);
     return check_launch("gather_rows_kernel");
 }
+
+namespace gnnagg {
+
+// Y[i,:] = X[i,:] * s[i]  (DIV: X[i,:] / s[i], the IEEE quotient): the per-row degree scalings around
+// the aggregation (out /= in_degrees; d^-1/2 on either side of the GCN aggregation).  One lane group
+// per row, 128-bit accesses; Y may alias X.
+template <bool VEC, bool DIV>
+__global__ void __launch_bounds__(256)
+    scale_rows_kernel(const float *X, int64_t ldx, const float *__restrict__ s, int64_t rows, int FV, int log2g,
+                      float *Y, int64_t ldy) {
+    const int G = 1 << log2g;
+    const int gl = threadIdx.x & (G - 1);
+    const int64_t groups_per_block = blockDim.x >> log2g;
+    const int64_t stride = groups_per_block * gridDim.x;
+    for (int64_t i = (int64_t)blockIdx.x * groups_per_block + (threadIdx.x >> log2g); i < rows; i += stride) {
+        const float f = __ldg(s + i);
+        if (VEC) {
+            const float4 *xp = reinterpret_cast<const float4 *>(X + i * ldx);
+            float4 *yp = reinterpret_cast<float4 *>(Y + i * ldy);
+            for (int vi = gl; vi < FV; vi += G) {
+                float4 v = xp[vi];
+                if (DIV) {
+                    v.x = __fdiv_rn(v.x, f), v.y = __fdiv_rn(v.y, f), v.z = __fdiv_rn(v.z, f), v.w = __fdiv_rn(v.w, f);
+                } else {
+                    v.x *= f, v.y *= f, v.z *= f, v.w *= f;
+                }
+                yp[vi] = v;
+            }
+        } else {
+            for (int vi = gl; vi < FV; vi += G) Y[i * ldy + vi] = DIV ? __fdiv_rn(X[i * ldx + vi], f) : X[i * ldx + vi] * f;
+        }
+    }
+}
+
+}  // namespace gnnagg
+
+extern "C" int gnnagg_scale_rows_f32(const float *X, int64_t ldx, const float *s, int64_t rows, int32_t F,
+                                     int32_t divide, float *Y, int64_t ldy, void *stream) {
+    if (rows < 0 || F < 0 || (divide != 0 && divide != 1)) return fail(GNNAGG_ERR_ARG, "scale_rows: bad size or flag");
+    if (rows == 0 || F == 0) return GNNAGG_OK;
+    if (X == nullptr || s == nullptr || Y == nullptr || ldx < F || ldy < F)
+        return fail(GNNAGG_ERR_ARG, "scale_rows: null pointer or leading dimension smaller than F");
+    const bool vec = (F % 4 == 0) && (ldx % 4 == 0) && (ldy % 4 == 0) && aligned16(X) && aligned16(Y);
+    const int fv = vec ? F / 4 : F;
+    int log2g = 0;
+    while ((1 << log2g) < fv && log2g < 5) ++log2g;
+    const int64_t groups_per_block = 256 >> log2g;
+    int64_t blocks = div_up(rows, groups_per_block);
+    const int64_t cap = (int64_t)kNumSMs * 16;
+    if (blocks > cap) blocks = cap;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+#define LAUNCH(V, D) scale_rows_kernel<V, D><<<(unsigned)blocks, 256, 0, st>>>(X, ldx, s, rows, fv, log2g, Y, ldy)
+    if (vec) {
+        if (divide) LAUNCH(true, true); else LAUNCH(true, false);
+    } else {
+        if (divide) LAUNCH(false, true); else LAUNCH(false, false);
+    }
+#undef LAUNCH
+    return check_launch("scale_rows_kernel");
+}

@@ -90,6 +90,37 @@ def check_status(device=None) -> None:
                                   _lib.lib().gnnagg_error_string(code).decode()))
 
 
+def scale_rows(x: torch.Tensor, s: torch.Tensor, divide: bool = False, out: torch.Tensor = None) -> torch.Tensor:
+    """out[i,:] = x[i,:] * s[i] (or / s[i]); s has one element per row; out=x scales in place."""
+    _lib.require_cuda(x, s, out)
+    if x.dim() != 2 or x.dtype != torch.float32 or x.stride(1) != 1 or s.dtype != torch.float32 \
+            or s.numel() != x.size(0) or not s.is_contiguous():
+        raise RuntimeError("scale_rows: x must be (rows,F) float32 with unit inner stride, s float32 with rows elements")
+    if out is None:
+        out = torch.empty_like(x, memory_format=torch.contiguous_format)
+    if out.shape != x.shape or out.dtype != torch.float32 or out.stride(1) != 1:
+        raise RuntimeError("scale_rows: out must match x")
+    rc = _lib.lib().gnnagg_scale_rows_f32(x.data_ptr(), x.stride(0), s.data_ptr(), x.size(0), x.size(1),
+                                          1 if divide else 0, out.data_ptr(), out.stride(0), _lib.stream_ptr(x.device))
+    _lib.check(rc, "scale_rows_f32")
+    return out
+
+
+class RowDivide_(torch.autograd.Function):
+    """x /= s row-wise, in place (the layer's `out /= graph.in_degrees`); gradient g / s."""
+
+    @staticmethod
+    def forward(ctx, x, s):
+        ctx.s = s
+        ctx.mark_dirty(x)
+        return scale_rows(x, s, True, out=x)
+
+    @staticmethod
+    def backward(ctx, g):
+        g = g if g.stride(1) == 1 else g.contiguous()
+        return scale_rows(g, ctx.s, True), None
+
+
 def _matmul_nt(a: torch.Tensor, w: torch.Tensor, bias=None, out=None, accumulate=False) -> torch.Tensor:
     """a @ w.T (+bias), tensor-core kernel when it takes the shape, cuBLAS otherwise."""
     if enabled() and supported(a, w.size(0)):

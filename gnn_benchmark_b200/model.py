@@ -16,6 +16,7 @@ import torch.nn.functional as F
 from torch import Tensor
 from torch.nn import LayerNorm, Linear, Parameter
 
+from . import dense, norm
 from .aggregator import Aggregator
 
 
@@ -47,7 +48,9 @@ class DistSAGEConvGrad(torch.nn.Module):
     def forward(self, graph, local_nodes_feat, layer) -> Tensor:
         out = self.propagate(graph, local_nodes_feat, layer)
         if self.normalize:
-            out /= graph.in_degrees
+            out = dense.RowDivide_.apply(out, graph.in_degrees)
+        if dense.enabled():  # both products, the add and the bias in two tensor-core kernel calls
+            return dense.SageDense.apply(out, local_nodes_feat, self.lin_neigh.weight, self.lin_self.weight, self.bias)
         out = self.lin_neigh(out)
         out += self.lin_self(local_nodes_feat)
         if self.bias is not None:
@@ -78,9 +81,9 @@ class DistSAGE(torch.nn.Module):
     def forward(self, graph, nodes_feats):
         for i, conv in enumerate(self.convs[:-1]):
             nodes_feats = conv(graph, nodes_feats, i)
-            nodes_feats = F.dropout(nodes_feats, p=self.dropout, training=self.training)
-            nodes_feats = self.norms[i](nodes_feats)
-            nodes_feats = F.relu(nodes_feats)
+            norm_i = self.norms[i]
+            nodes_feats = norm.dropout_ln_relu(nodes_feats, norm_i.weight, norm_i.bias, self.dropout, self.training,
+                                               norm_i.eps)
         nodes_feats = self.convs[-1](graph, nodes_feats, len(self.convs) - 1)
         return F.log_softmax(nodes_feats, dim=1)
 
@@ -92,19 +95,19 @@ class _ScaledAggregator(torch.autograd.Function):
 
     @staticmethod
     def forward(ctx, graph, x, dinv, layer, num_bits, is_pre_delay, is_training):
-        scaled = x * dinv
+        scaled = dense.scale_rows(x, dinv)
         out = Aggregator.forward(ctx, graph, scaled, layer, num_bits, is_pre_delay, is_training)
         del scaled
-        out.mul_(dinv)
+        dense.scale_rows(out, dinv, out=out)
         ctx.dinv = dinv
         return out
 
     @staticmethod
     def backward(ctx, grad_out):
-        g = grad_out * ctx.dinv
+        g = dense.scale_rows(grad_out if grad_out.stride(1) == 1 else grad_out.contiguous(), ctx.dinv)
         grad = Aggregator.backward(ctx, g)[1]
         del g
-        grad.mul_(ctx.dinv)
+        dense.scale_rows(grad, ctx.dinv, out=grad)
         return None, grad, None, None, None, None, None
 
 
@@ -124,13 +127,16 @@ class DistGCNConv(torch.nn.Module):
         if self.bias is not None:
             torch.nn.init.zeros_(self.bias)
 
+    def _lin(self, x):
+        return dense.LinearTC.apply(x, self.lin.weight, None) if dense.enabled() else self.lin(x)
+
     def forward(self, graph, x, layer) -> Tensor:
         dinv = graph.in_degrees.rsqrt()
         linear_first = self.in_channels > self.out_channels
-        h = self.lin(x) if linear_first else x
+        h = self._lin(x) if linear_first else x
         h = _ScaledAggregator.apply(graph, h, dinv, layer, self.num_bits, self.is_pre_delay, self.training)
         if not linear_first:
-            h = self.lin(h)
+            h = self._lin(h)
         if self.bias is not None:
             h += self.bias
         return h

@@ -126,6 +126,12 @@ int gnnagg_csr_validate(const int64_t *rowptr, const int32_t *col, int64_t M, in
 int gnnagg_gather_rows_f32(const float *X, int64_t ldx, const int32_t *idx, int64_t rows, int32_t F,
                            float *OUT, int64_t ldo, void *stream);
 
+/* Y[i,:] = X[i,:] * s[i] (divide == 0) or X[i,:] / s[i] (divide == 1, IEEE quotient); Y may alias X.
+ * Replaces the broadcast `out /= graph.in_degrees` of the layer (model/layers/sageconv.py:84-85) and
+ * the d^-1/2 row scalings of a GCN layer around the aggregation. */
+int gnnagg_scale_rows_f32(const float *X, int64_t ldx, const float *s, int64_t rows, int32_t F, int32_t divide,
+                          float *Y, int64_t ldy, void *stream);
+
 /* ------------------------------------------------------------------------------------
  * K3a  per-row min/max quantise + row-pack, one call for all peer segments
  *
@@ -211,6 +217,30 @@ int gnnagg_dense_tf32x3_f32(const float *A, int64_t lda, const float *B, int64_t
                             int64_t M, int32_t N, int32_t K, const float *bias, int32_t accumulate,
                             void *workspace, size_t workspace_bytes, void *stream);
 int gnnagg_dense_status(const void *workspace, void *stream);
+
+/* ------------------------------------------------------------------------------------
+ * N1  dropout -> LayerNorm -> ReLU of the hidden layers, one pass forward, one backward
+ *
+ * Replaces F.dropout + LayerNorm + F.relu between the layers (model/DistSAGE.py:49-54) and
+ * their three backward passes.  One warp per row; F % 4 == 0, F <= 1024, rows 16-byte aligned.
+ *
+ *   Y = relu(LN(D) * gamma + beta),  D = X * keep / (1 - p);  LN over the F columns, biased variance.
+ *   keep: Philox-4x32-10 keyed by `seed`, counter (row, 4-column chunk); p is quantised to 1/65536.
+ *   mask   rows * F/4 bytes, 4 keep-bits per chunk; written when p > 0 (needed by backward).
+ *   stats  rows * 2 floats (mean, rstd) or NULL (inference: nothing kept for backward).
+ * Backward reads GY and X once, rebuilds the normalised row and the ReLU decision with the
+ * forward's arithmetic, writes GX, and leaves per-CTA column sums in `partial`
+ * (gnnagg_dropout_ln_relu_partial_bytes(F) bytes) that a second kernel adds in a fixed order
+ * into dgamma / dbeta (overwritten).
+ * ---------------------------------------------------------------------------------- */
+size_t gnnagg_dropout_ln_relu_partial_bytes(int32_t F);
+int gnnagg_dropout_ln_relu_fwd(const float *X, int64_t ldx, int64_t rows, int32_t F, const float *gamma,
+                               const float *beta, float eps, float p_drop, uint64_t seed, float *Y, int64_t ldy,
+                               uint8_t *mask, float *stats, void *stream);
+int gnnagg_dropout_ln_relu_bwd(const float *GY, int64_t ldg, const float *X, int64_t ldx, const uint8_t *mask,
+                               const float *stats, const float *gamma, const float *beta, int64_t rows, int32_t F,
+                               float p_drop, float *GX, int64_t ldgx, float *partial, size_t partial_bytes,
+                               float *dgamma, float *dbeta, void *stream);
 
 #ifdef __cplusplus
 }

@@ -162,11 +162,18 @@ def test_gcn_configuration_1_against_reference_aggregator_run(cuda_lib, tmp_path
         np.testing.assert_allclose(got, want, rtol=0, atol=1e-4)
 
 
+@pytest.mark.parametrize("dense_mode", ["cublas", "tf32x3"])
 @pytest.mark.parametrize("path", sorted(glob.glob(os.path.join(GOLD, "train_sage_*.npz"))),
                          ids=lambda p: os.path.basename(p)[6:-4])
-def test_loss_curve_against_reference_run(cuda_lib, tmp_path, path):
+def test_loss_curve_against_reference_run(cuda_lib, tmp_path, path, dense_mode, monkeypatch):
+    """dense_mode "cublas": the layer's fp32 transforms on cuBLAS SIMT kernels (bar 1e-4);
+    "tf32x3": on the tensor-core kernel, whose accumulator rounds once per instruction and is a few
+    times less accurate than an fp32 FMA chain (about 1e-6 instead of 3e-7 of sum |a||b|): the same
+    20-epoch curve then stays within 3e-4 (largest deviation measured: 1.3e-4)."""
     import torch.multiprocessing as mp
 
+    monkeypatch.setenv("GNNAGG_DENSE", dense_mode)  # read by the spawned ranks at import
+    tol = 1e-4 if dense_mode == "cublas" else 3e-4
     g = np.load(path)
     P = sum(1 for k in g.files if k.endswith("_losses"))
     port = 29700 + (os.getpid() % 200)
@@ -177,12 +184,12 @@ def test_loss_curve_against_reference_run(cuda_lib, tmp_path, path):
         want = g[f"r{r}_losses"]
         assert got["losses"].shape == want.shape == (20,)
         if int(dict(zip(g["cfg_keys"], g["cfg_vals"]))["num_bits"]) == 32:
-            np.testing.assert_allclose(got["losses"], want, rtol=0, atol=1e-4)
+            np.testing.assert_allclose(got["losses"], want, rtol=0, atol=tol)
         else:
             # 2-bit halo: a one-ulp difference in a dense transform (cuBLAS here, the CPU BLAS there)
             # moves a value across a rounding boundary now and then, and a flipped code changes that
             # halo element by a whole quantisation step -- a perturbation that two runs of the
             # reference on different BLAS builds show as well.  Until the first flips the curves
             # agree to fp32 noise; afterwards they stay within 2e-2.
-            np.testing.assert_allclose(got["losses"][:2], want[:2], rtol=0, atol=1e-4)
+            np.testing.assert_allclose(got["losses"][:2], want[:2], rtol=0, atol=tol)
             np.testing.assert_allclose(got["losses"], want, rtol=0, atol=2e-2)
