@@ -45,6 +45,8 @@ SIGNATURES = {
     "gnnagg_dense_tf32x3_f32": (ctypes.c_int, [_vp, _i64, _vp, _i64, _vp, _i64, _i64, _i32, _i32, _vp, _i32, _vp, _sz,
                                                _vp]),
     "gnnagg_dense_status": (ctypes.c_int, [_vp, _vp]),
+    "gnnagg_dense_wgrad_workspace_bytes": (_sz, [_i32, _i32]),
+    "gnnagg_dense_wgrad_tf32x3_f32": (ctypes.c_int, [_vp, _i64, _vp, _i64, _i64, _i32, _i32, _vp, _i64, _vp, _sz, _vp]),
     "gnnagg_dropout_ln_relu_partial_bytes": (_sz, [_i32]),
     "gnnagg_dropout_ln_relu_fwd": (ctypes.c_int, [_vp, _i64, _i64, _i32, _vp, _vp, ctypes.c_float, ctypes.c_float,
                                                   ctypes.c_uint64, _vp, _i64, _vp, _vp, _vp]),

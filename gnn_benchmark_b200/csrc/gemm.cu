@@ -509,6 +509,264 @@ gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
     }
 }
 
+// ---------------------------------------------------------------------------------------------
+// Weight gradient  dW[N,K] = G[M,N]^T . X[M,K]: a reduction over all M rows into a small matrix.
+//
+// Both operands are "MN-major" for the tensor core (the reduction index, the row, is the slow
+// dimension in memory), which tcgen05 takes directly.  For 32-bit elements that needs the 128-byte
+// swizzle with 32-byte atoms, both in the tensor map (SWIZZLE_128B_ATOM_32B) and in the shared-memory
+// descriptor (layout type 1; with the plain 128-byte swizzle the MMA returns zeros): a {32 columns,
+// 16 rows} TMA box lands as 16 k-rows of 128 bytes, groups of 4 k-rows 512 bytes apart (stride byte
+// offset), the boxes of one operand 2 KB apart (leading byte offset); one MMA consumes 8 k-rows.
+// Each CTA owns a contiguous block of rows, accumulates its 256 x 256 partial product in tensor
+// memory (two 128-lane halves), and writes it to scratch; a second kernel adds the per-CTA partials
+// in a fixed order.  The remainder (lo) panels of both operands are computed in shared memory as in
+// the forward kernel; products: G.X + G_lo.X + G.X_lo.
+constexpr int WG_ROWS = 16;                           // rows (k) per stage: two MMAs of k = 8
+constexpr int WG_BOX_BYTES = WG_ROWS * 128;           // one {32 columns, 16 rows} box
+constexpr int WG_PANEL_BYTES = 8 * WG_BOX_BYTES;      // up to 256 columns of one operand: 16 KB
+constexpr int WG_STAGE_BYTES = 4 * WG_PANEL_BYTES;    // g, g_lo, x, x_lo
+constexpr int WG_STAGES = 3;
+constexpr int WG_THREADS = 320;
+constexpr int WG_SMEM_BYTES = 1024 + WG_STAGES * WG_STAGE_BYTES + 256;
+static_assert(WG_SMEM_BYTES <= 227 * 1024, "shared memory budget");
+
+__device__ __forceinline__ uint64_t make_smem_desc_mn(uint32_t smem_addr, uint64_t tmpl) {
+    return tmpl | (uint64_t)((smem_addr & 0x3FFFFu) >> 4);
+}
+// everything but the start address: leading / stride byte offsets, version 1, layout type
+inline uint64_t smem_desc_mn_template(int lbo_bytes, int sbo_bytes, int layout) {
+    uint64_t d = 0;
+    d |= (uint64_t)(lbo_bytes >> 4) << 16;
+    d |= (uint64_t)(sbo_bytes >> 4) << 32;
+    d |= (uint64_t)1 << 46;
+    d |= (uint64_t)layout << 61;
+    return d;
+}
+
+struct WgradParams {
+    float *partial;   // [grid][n_rows][kp]
+    int *status;
+    int64_t M;
+    int N, K, n_pad, kp, blocks_per_cta, total_blocks, dbg;
+    uint64_t desc;   // shared-memory descriptor without the start address
+};
+
+__global__ void __launch_bounds__(WG_THREADS, 1)
+wgrad_tf32x3_kernel(const __grid_constant__ CUtensorMap map_g, const __grid_constant__ CUtensorMap map_x,
+                    const WgradParams p) {
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+    uint64_t *bars = reinterpret_cast<uint64_t *>(smem + WG_STAGES * WG_STAGE_BYTES);
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 3 * WG_STAGES + 2);
+    volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
+    const uint32_t bar0 = smem_u32(bars);
+    auto bar_full = [&](int s) { return bar0 + 8u * (uint32_t)s; };
+    auto bar_split = [&](int s) { return bar0 + 8u * (uint32_t)(WG_STAGES + s); };
+    auto bar_empty = [&](int s) { return bar0 + 8u * (uint32_t)(2 * WG_STAGES + s); };
+    const uint32_t bar_acc = bar0 + 8u * (uint32_t)(3 * WG_STAGES);
+    const uint32_t bar_drain = bar0 + 8u * (uint32_t)(3 * WG_STAGES + 1);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int nb_g = (p.N + 31) / 32, nb_x = (p.n_pad + 31) / 32;   // boxes per operand
+    const int halves = p.N > 128 ? 2 : 1;
+    const int kb0 = blockIdx.x * p.blocks_per_cta;
+    const int kb1 = min(kb0 + p.blocks_per_cta, p.total_blocks);
+    const int nkb = kb1 - kb0;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < WG_STAGES; ++s) {
+            mbar_init(bar_full(s), 1);
+            mbar_init(bar_split(s), 256);
+            mbar_init(bar_empty(s), 1);
+        }
+        mbar_init(bar_acc, 1);
+        mbar_init(bar_drain, 1);
+        *abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)),
+                     "r"((uint32_t)kTmemCols)
+                     : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp == 0) {
+        if (lane == 0) {
+            bool ok = true;
+            int it = 0;
+            for (; it < nkb; ++it) {
+                const int s = it % WG_STAGES;
+                const uint32_t ph = (uint32_t)(it / WG_STAGES) & 1u;
+                if (!mbar_wait(bar_empty(s), ph ^ 1u, abort_flag, p.status, kErrWaitEmpty)) {
+                    ok = false;
+                    break;
+                }
+                const uint32_t sa = smem_u32(smem + s * WG_STAGE_BYTES);
+                const int row = (kb0 + it) * WG_ROWS;
+                mbar_arrive_expect_tx(bar_full(s), (uint32_t)(nb_g + nb_x) * WG_BOX_BYTES);
+                for (int b = 0; b < nb_g; ++b) tma_load_2d(sa + b * WG_BOX_BYTES, &map_g, bar_full(s), 32 * b, row);
+                for (int b = 0; b < nb_x; ++b)
+                    tma_load_2d(sa + 2 * WG_PANEL_BYTES + b * WG_BOX_BYTES, &map_x, bar_full(s), 32 * b, row);
+            }
+            if (!ok) {
+                for (int back = 1; back <= WG_STAGES && back <= it; ++back) {
+                    const int j = it - back;
+                    const unsigned long long t0 = globaltimer_ns();
+                    while (!mbar_try_wait(bar_full(j % WG_STAGES), (uint32_t)(j / WG_STAGES) & 1u)) {
+                        if (globaltimer_ns() - t0 > kWaitLimitNs) {
+                            atomicCAS(p.status, 0, (int)kErrDrain);
+                            break;
+                        }
+                    }
+                }
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {
+            // kind::tf32, fp32 accumulate, A and B both MN-major (bits 15, 16), M = 128, N = n_pad
+            const uint32_t idesc = make_instr_desc(p.n_pad) | (1u << 15) | (1u << 16);
+            bool ok = true;
+            for (int it = 0; it < nkb; ++it) {
+                const int s = it % WG_STAGES;
+                const uint32_t ph = (uint32_t)(it / WG_STAGES) & 1u;
+                if (!mbar_wait(bar_full(s), ph, abort_flag, p.status, kErrWaitFull)) {
+                    ok = false;
+                    break;
+                }
+                tc_fence_after();
+                const uint32_t sa = smem_u32(smem + s * WG_STAGE_BYTES);
+                const uint32_t g_raw = sa, g_lo = sa + WG_PANEL_BYTES, x_raw = sa + 2 * WG_PANEL_BYTES,
+                               x_lo = sa + 3 * WG_PANEL_BYTES;
+#pragma unroll
+                for (int ks = 0; ks < WG_ROWS / UMMA_K; ++ks)
+                    for (int h = 0; h < halves; ++h)
+                        tc_mma_tf32(tmem_base + (uint32_t)(h * kAccStride),
+                                    make_smem_desc_mn(g_raw + h * 4 * WG_BOX_BYTES + ks * 1024, p.desc),
+                                    make_smem_desc_mn(x_raw + ks * 1024, p.desc), idesc, (it > 0 || ks > 0) ? 1u : 0u);
+                if (!mbar_wait(bar_split(s), ph, abort_flag, p.status, kErrWaitSplit)) {
+                    ok = false;
+                    break;
+                }
+                tc_fence_after();
+                if (!(p.dbg & 16)) {
+#pragma unroll
+                    for (int ks = 0; ks < WG_ROWS / UMMA_K; ++ks)
+                        for (int h = 0; h < halves; ++h) {
+                            const uint32_t d = tmem_base + (uint32_t)(h * kAccStride);
+                            tc_mma_tf32(d, make_smem_desc_mn(g_lo + h * 4 * WG_BOX_BYTES + ks * 1024, p.desc),
+                                        make_smem_desc_mn(x_raw + ks * 1024, p.desc), idesc, 1u);
+                            tc_mma_tf32(d, make_smem_desc_mn(g_raw + h * 4 * WG_BOX_BYTES + ks * 1024, p.desc),
+                                        make_smem_desc_mn(x_lo + ks * 1024, p.desc), idesc, 1u);
+                        }
+                }
+                tc_commit(bar_empty(s));
+            }
+            if (ok) {
+                tc_commit(bar_acc);
+            } else {
+                tc_commit(bar_drain);
+                const unsigned long long t0 = globaltimer_ns();
+                while (!mbar_try_wait(bar_drain, 0)) {
+                    if (globaltimer_ns() - t0 > kWaitLimitNs) {
+                        atomicCAS(p.status, 0, (int)kErrDrain);
+                        break;
+                    }
+                }
+            }
+        }
+    } else {
+        // ---- warps 2-9: remainder panels; afterwards warps 2-5 write the accumulator out ----
+        const int tid = threadIdx.x - 64;  // 0..255
+        bool ok = true;
+        for (int it = 0; it < nkb; ++it) {
+            const int s = it % WG_STAGES;
+            const uint32_t ph = (uint32_t)(it / WG_STAGES) & 1u;
+            if (!mbar_wait(bar_full(s), ph, abort_flag, p.status, kErrWaitFull)) {
+                ok = false;
+                break;
+            }
+            uint8_t *st = smem + s * WG_STAGE_BYTES;
+            const int ng4 = nb_g * (WG_BOX_BYTES / 16), nx4 = nb_x * (WG_BOX_BYTES / 16);
+            if (!(p.dbg & 4)) {
+                const float4 *graw = reinterpret_cast<const float4 *>(st);
+                float4 *glo = reinterpret_cast<float4 *>(st + WG_PANEL_BYTES);
+                for (int i = tid; i < ng4; i += 256) {
+                    const float4 v = graw[i];
+                    glo[i] = make_float4(lo_of_truncated(v.x), lo_of_truncated(v.y), lo_of_truncated(v.z),
+                                         lo_of_truncated(v.w));
+                }
+                const float4 *xraw = reinterpret_cast<const float4 *>(st + 2 * WG_PANEL_BYTES);
+                float4 *xlo = reinterpret_cast<float4 *>(st + 3 * WG_PANEL_BYTES);
+                for (int i = tid; i < nx4; i += 256) {
+                    const float4 v = xraw[i];
+                    xlo[i] = make_float4(lo_of_truncated(v.x), lo_of_truncated(v.y), lo_of_truncated(v.z),
+                                         lo_of_truncated(v.w));
+                }
+            }
+            fence_generic_to_async_smem();
+            mbar_arrive(bar_split(s));
+        }
+        if (warp < 6) {
+            const int q = warp & 3;
+            const bool ready = ok && mbar_wait(bar_acc, 0, abort_flag, p.status, kErrWaitAccFull);
+            if (__all_sync(kFullMask, ready)) {
+                tc_fence_after();
+                float *out = p.partial + (int64_t)blockIdx.x * p.N * p.kp;
+                for (int h = 0; h < halves; ++h) {
+                    const int n = h * 128 + q * 32 + lane;
+                    for (int c0 = 0; c0 < p.K; c0 += 32) {
+                        uint32_t r[32];
+                        tc_ld_32x32(tmem_base + (uint32_t)(h * kAccStride + c0) + ((uint32_t)(q * 32) << 16), r);
+                        if (n < p.N) {
+#pragma unroll
+                            for (int j = 0; j < 8; ++j)
+                                if (c0 + 4 * j < p.kp)
+                                    *reinterpret_cast<float4 *>(out + (int64_t)n * p.kp + c0 + 4 * j) =
+                                        make_float4(__uint_as_float(r[4 * j]), __uint_as_float(r[4 * j + 1]),
+                                                    __uint_as_float(r[4 * j + 2]), __uint_as_float(r[4 * j + 3]));
+                        }
+                    }
+                }
+            }
+        }
+    }
+
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)kTmemCols)
+                     : "memory");
+    }
+}
+
+// dW[n,k] = sum over CTAs of partial[cta][n][k], fixed order.
+__global__ void wgrad_reduce_kernel(const float *__restrict__ partial, int nparts, int N, int K, int kp,
+                                    float *__restrict__ dW, int64_t ldw) {
+    const int total = N * K;
+    for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < total; i += gridDim.x * blockDim.x) {
+        const int n = i / K, k = i % K;
+        const float *src = partial + (int64_t)n * kp + k;
+        const int64_t step = (int64_t)N * kp;
+        float s0 = 0.0f, s1 = 0.0f, s2 = 0.0f, s3 = 0.0f;
+        int c = 0;
+        for (; c + 3 < nparts; c += 4) {
+            s0 += src[(int64_t)(c + 0) * step];
+            s1 += src[(int64_t)(c + 1) * step];
+            s2 += src[(int64_t)(c + 2) * step];
+            s3 += src[(int64_t)(c + 3) * step];
+        }
+        for (; c < nparts; ++c) s0 += src[(int64_t)c * step];
+        dW[(int64_t)n * ldw + k] = (s0 + s1) + (s2 + s3);
+    }
+}
+
 // W[N,K] (row stride ldb) -> hi / lo pieces with row stride ldw.
 __global__ void split_weight_kernel(const float *__restrict__ W, int64_t ldb, int N, int K, int ldw,
                                     float *__restrict__ hi, float *__restrict__ lo) {
@@ -542,14 +800,16 @@ EncodeTiledFn encode_fn() {
 // 2-D fp32 tensor map: `cols` contiguous elements per row, `rows` rows of stride ld elements;
 // box = {box_cols, box_rows} with box_cols * 4 bytes = the swizzle span; out-of-range elements read
 // as zero and are not written.
-int make_map(CUtensorMap *map, const float *base, int64_t rows, int64_t cols, int64_t ld, int box_cols, int box_rows) {
+int make_map(CUtensorMap *map, const float *base, int64_t rows, int64_t cols, int64_t ld, int box_cols, int box_rows,
+             int swizzle = -1) {
     EncodeTiledFn fn = encode_fn();
     if (fn == nullptr) return fail(GNNAGG_ERR_CUDA, "dense: cuTensorMapEncodeTiled is not available from the driver");
     const cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
     const cuuint64_t strides[1] = {(cuuint64_t)ld * 4};
     const cuuint32_t box[2] = {(cuuint32_t)box_cols, (cuuint32_t)box_rows};
     const cuuint32_t estr[2] = {1, 1};
-    const CUtensorMapSwizzle swz = box_cols == 32 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B;
+    const CUtensorMapSwizzle swz = swizzle >= 0 ? (CUtensorMapSwizzle)swizzle
+                                   : (box_cols == 32 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B);
     const CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, const_cast<float *>(base), dims, strides, box, estr,
                           CU_TENSOR_MAP_INTERLEAVE_NONE, swz, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
                           CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
@@ -642,6 +902,77 @@ extern "C" int gnnagg_dense_tf32x3_f32(const float *A, int64_t lda, const float 
     const int grid = p.num_tiles < kNumSMs ? p.num_tiles : kNumSMs;
     gemm_tf32x3_kernel<<<grid, kThreads, SMEM_BYTES, st>>>(map_a, map_bhi, map_blo, map_c, p);
     return check_launch("gemm_tf32x3_kernel");
+}
+
+
+extern "C" size_t gnnagg_dense_wgrad_workspace_bytes(int32_t N, int32_t K) {
+    if (N <= 0 || K <= 0) return kStatusBytes;
+    return kStatusBytes + (size_t)kNumSMs * (size_t)N * (size_t)round_up(K, 4) * sizeof(float);
+}
+
+extern "C" int gnnagg_dense_wgrad_tf32x3_f32(const float *G, int64_t ldg, const float *X, int64_t ldx, int64_t M,
+                                             int32_t N, int32_t K, float *dW, int64_t ldw, void *workspace,
+                                             size_t workspace_bytes, void *stream) {
+    if (M < 0 || N < 0 || K < 0) return fail(GNNAGG_ERR_ARG, "dense_wgrad: negative size");
+    if (N == 0 || K == 0) return GNNAGG_OK;
+    if (G == nullptr || X == nullptr || dW == nullptr || workspace == nullptr)
+        return fail(GNNAGG_ERR_ARG, "dense_wgrad: null pointer");
+    if (N > kMaxN || K > kMaxN)
+        return fail(GNNAGG_ERR_UNSUPPORTED, "dense_wgrad: %d x %d exceeds %d x %d", N, K, kMaxN, kMaxN);
+    if (ldg < N || ldx < K || ldw < K) return fail(GNNAGG_ERR_ARG, "dense_wgrad: leading dimension smaller than the row");
+    if (!aligned16(G) || !aligned16(X) || (ldg % 4) != 0 || (ldx % 4) != 0)
+        return fail(GNNAGG_ERR_UNSUPPORTED, "dense_wgrad: operands must be 16-byte aligned with row strides multiple of 4");
+    if (M > (int64_t)INT32_MAX - WG_ROWS) return fail(GNNAGG_ERR_UNSUPPORTED, "dense_wgrad: M too large");
+    if (!aligned16(workspace) || workspace_bytes < gnnagg_dense_wgrad_workspace_bytes(N, K))
+        return fail(GNNAGG_ERR_SCRATCH, "dense_wgrad: workspace too small or misaligned (need %zu bytes)",
+                    gnnagg_dense_wgrad_workspace_bytes(N, K));
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    uint8_t *ws = static_cast<uint8_t *>(workspace);
+    float *partial = reinterpret_cast<float *>(ws + kStatusBytes);
+    if (M == 0) {
+        for (int n = 0; n < N; ++n) {
+            const cudaError_t e = cudaMemsetAsync(dW + (int64_t)n * ldw, 0, (size_t)K * 4, st);
+            if (e != cudaSuccess) return fail(GNNAGG_ERR_CUDA, "dense_wgrad: %s", cudaGetErrorString(e));
+        }
+        return GNNAGG_OK;
+    }
+
+    static std::once_flag attr_once;
+    static cudaError_t attr_err = cudaSuccess;
+    std::call_once(attr_once, [] {
+        attr_err = cudaFuncSetAttribute(wgrad_tf32x3_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, WG_SMEM_BYTES);
+    });
+    if (attr_err != cudaSuccess)
+        return fail(GNNAGG_ERR_CUDA, "dense_wgrad: cannot reserve %d bytes of shared memory: %s", WG_SMEM_BYTES,
+                    cudaGetErrorString(attr_err));
+
+    // 32-bit MN-major operands use the 128-byte swizzle with 32-byte atoms, in the tensor map and in the
+    // shared-memory descriptor (layout type 1); groups of 4 k-rows lie 512 bytes apart, boxes 2 KB apart
+    const int swz = (int)CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B;
+    CUtensorMap map_g, map_x;
+    int rc = make_map(&map_g, G, M, N, ldg, 32, WG_ROWS, swz);
+    if (rc == GNNAGG_OK) rc = make_map(&map_x, X, M, K, ldx, 32, WG_ROWS, swz);
+    if (rc != GNNAGG_OK) return rc;
+
+    WgradParams p;
+    p.partial = partial;
+    p.status = reinterpret_cast<int *>(ws);
+    p.M = M;
+    p.N = N;
+    p.K = K;
+    p.n_pad = round_up(K, 16);
+    p.kp = round_up(K, 4);
+    p.total_blocks = (int)((M + WG_ROWS - 1) / WG_ROWS);
+    p.blocks_per_cta = (p.total_blocks + kNumSMs - 1) / kNumSMs;
+    p.dbg = getenv("GNNAGG_DENSE_DEBUG") ? atoi(getenv("GNNAGG_DENSE_DEBUG")) : 0;
+    p.desc = smem_desc_mn_template(WG_BOX_BYTES, 512, 1);
+    const int grid = (p.total_blocks + p.blocks_per_cta - 1) / p.blocks_per_cta;
+    wgrad_tf32x3_kernel<<<grid, WG_THREADS, WG_SMEM_BYTES, st>>>(map_g, map_x, p);
+    rc = check_launch("wgrad_tf32x3_kernel");
+    if (rc != GNNAGG_OK) return rc;
+    const int total = N * K;
+    wgrad_reduce_kernel<<<(total + 255) / 256, 256, 0, st>>>(partial, grid, N, K, p.kp, dW, ldw);
+    return check_launch("wgrad_reduce_kernel");
 }
 
 extern "C" int gnnagg_dense_status(const void *workspace, void *stream) {

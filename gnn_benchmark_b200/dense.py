@@ -7,9 +7,10 @@ splitting every operand into two TF32 pieces (three tensor-core products per fp3
 the bias and the second product accumulated in the kernel's epilogue.
 
 `linear(x, weight, bias, out, accumulate)` is the plain call; `SageDense` and `LinearTC` are the
-autograd nodes the models use.  Weight gradients (G^T X: a reduction over all rows into a small
-matrix) stay on cuBLAS.  Shapes the kernel does not take (more than 256 output columns, rows of
-the left operand not 16-byte aligned) also go to cuBLAS: `supported()` says which.
+autograd nodes the models use; `wgrad(g, x)` is the weight gradient G^T X (a reduction over all rows
+into a small matrix) on the same tensor-core scheme.  Shapes the kernels do not take (more than 256
+output columns, operand rows not 16-byte aligned) go to cuBLAS: `supported()` / `wgrad_supported()`
+say which.
 """
 import os
 
@@ -78,9 +79,47 @@ def linear(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor = None, out
     return out
 
 
+def wgrad_supported(g: torch.Tensor, x: torch.Tensor) -> bool:
+    def ok(t):
+        return (t.is_cuda and t.dtype == torch.float32 and t.dim() == 2 and t.stride(1) == 1 and t.stride(0) % 4 == 0
+                and t.data_ptr() % 16 == 0 and 0 < t.size(1) <= MAX_N)
+    return ok(g) and ok(x) and g.size(0) == x.size(0) and g.size(0) < 2 ** 31 - 128
+
+
+def wgrad(g: torch.Tensor, x: torch.Tensor, out: torch.Tensor = None) -> torch.Tensor:
+    """out = g.T @ x through the C ABI: g (M,N), x (M,K) -> (N,K), the gradient of a Linear weight."""
+    _lib.require_cuda(g, x, out)
+    if not wgrad_supported(g, x):
+        raise RuntimeError("dense.wgrad: operands not supported by the tensor-core kernel (see wgrad_supported())")
+    M, N = g.shape
+    K = x.size(1)
+    if out is None:
+        out = torch.empty(N, K, dtype=torch.float32, device=g.device)
+    if out.shape != (N, K) or out.dtype != torch.float32 or out.stride(1) != 1:
+        raise RuntimeError("dense.wgrad: out must be (N,K) float32 with unit inner stride")
+    key = (g.device.index, _lib.stream_ptr(g.device), "w", N, K)
+    ws = _workspaces.get(key)
+    if ws is None:
+        ws = torch.zeros(_lib.lib().gnnagg_dense_wgrad_workspace_bytes(N, K), dtype=torch.uint8, device=g.device)
+        _workspaces[key] = ws
+    rc = _lib.lib().gnnagg_dense_wgrad_tf32x3_f32(g.data_ptr(), g.stride(0), x.data_ptr(), x.stride(0), M, N, K,
+                                                  out.data_ptr(), out.stride(0), ws.data_ptr(), ws.numel(),
+                                                  _lib.stream_ptr(g.device))
+    _lib.check(rc, "dense_wgrad_tf32x3_f32")
+    return out
+
+
+def _matmul_tn(g: torch.Tensor, x: torch.Tensor) -> torch.Tensor:
+    """g.T @ x, tensor-core kernel when it takes the shapes, cuBLAS otherwise."""
+    if enabled() and wgrad_supported(g, x):
+        return wgrad(g, x)
+    return g.t() @ x
+
+
 def check_status(device=None) -> None:
     """Synchronise and raise if any dense kernel on `device` gave up on a wait (diagnostic)."""
-    for (dev, _stream, n, k), ws in list(_workspaces.items()):
+    for key, ws in list(_workspaces.items()):
+        dev, n, k = key[0], key[-2], key[-1]
         if device is not None and torch.device(device).index not in (None, dev):
             continue
         code = _lib.lib().gnnagg_dense_status(ws.data_ptr(), _lib.stream_ptr(ws.device))
@@ -137,6 +176,33 @@ def _matmul_nt(a: torch.Tensor, w: torch.Tensor, bias=None, out=None, accumulate
     return out
 
 
+def _tma_rows(g: torch.Tensor) -> torch.Tensor:
+    """`g` itself when its rows are 16-byte addressable, else a copy whose rows are padded with zero
+    columns to a multiple of 4 (an upstream gradient of 47 columns has 188-byte rows, which TMA cannot
+    address; the extra columns meet zero rows of the weight / are dropped from the weight gradient)."""
+    if not enabled() or not g.is_cuda or g.dim() != 2 or g.size(1) % 4 == 0 or g.size(1) > MAX_N - 3:
+        return g
+    pad = torch.zeros(g.size(0), (g.size(1) + 3) // 4 * 4, dtype=g.dtype, device=g.device)
+    pad[:, :g.size(1)] = g
+    return pad
+
+
+def _input_grad(g: torch.Tensor, weight: torch.Tensor) -> torch.Tensor:
+    """g @ weight for an upstream gradient g (M,N) (possibly column-padded) and a Linear weight (N,K)."""
+    wt = weight.t()
+    if g.size(1) != weight.size(0):  # padded gradient: pad the transposed weight with zero columns
+        wt_p = torch.zeros(weight.size(1), g.size(1), dtype=weight.dtype, device=weight.device)
+        wt_p[:, :weight.size(0)] = wt
+        return _matmul_nt(g, wt_p)
+    return _matmul_nt(g, wt.contiguous())
+
+
+def _weight_grad(g: torch.Tensor, x: torch.Tensor, n_out: int) -> torch.Tensor:
+    """g^T @ x, dropping the rows that belong to padding columns of g."""
+    gw = _matmul_tn(g, x)
+    return gw if gw.size(0) == n_out else gw[:n_out].contiguous()
+
+
 class LinearTC(torch.autograd.Function):
     """y = x @ W^T (+ b) with the forward and the input gradient on the tensor-core kernel."""
 
@@ -151,12 +217,13 @@ class LinearTC(torch.autograd.Function):
         x, weight = ctx.saved_tensors
         g = g.contiguous()
         gx = gw = gb = None
-        if ctx.needs_input_grad[0]:
-            gx = _matmul_nt(g, weight.t().contiguous())
-        if ctx.needs_input_grad[1]:
-            gw = g.t() @ x
         if ctx.has_bias and ctx.needs_input_grad[2]:
             gb = g.sum(0)
+        g = _tma_rows(g)
+        if ctx.needs_input_grad[0]:
+            gx = _input_grad(g, weight)
+        if ctx.needs_input_grad[1]:
+            gw = _weight_grad(g, x, weight.size(0))
         return gx, gw, gb
 
 
@@ -178,14 +245,16 @@ class SageDense(torch.autograd.Function):
         aggr, x, w_neigh, w_self = ctx.saved_tensors
         g = g.contiguous()
         g_aggr = g_x = g_wn = g_ws = g_b = None
-        if ctx.needs_input_grad[0]:
-            g_aggr = _matmul_nt(g, w_neigh.t().contiguous())
-        if ctx.needs_input_grad[1]:
-            g_x = _matmul_nt(g, w_self.t().contiguous())
-        if ctx.needs_input_grad[2]:
-            g_wn = g.t() @ aggr
-        if ctx.needs_input_grad[3]:
-            g_ws = g.t() @ x
         if ctx.has_bias and ctx.needs_input_grad[4]:
             g_b = g.sum(0)
+        g = _tma_rows(g)
+        n_out = w_neigh.size(0)
+        if ctx.needs_input_grad[0]:
+            g_aggr = _input_grad(g, w_neigh)
+        if ctx.needs_input_grad[1]:
+            g_x = _input_grad(g, w_self)
+        if ctx.needs_input_grad[2]:
+            g_wn = _weight_grad(g, aggr, n_out)
+        if ctx.needs_input_grad[3]:
+            g_ws = _weight_grad(g, x, n_out)
         return g_aggr, g_x, g_wn, g_ws, g_b

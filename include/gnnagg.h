@@ -218,6 +218,17 @@ int gnnagg_dense_tf32x3_f32(const float *A, int64_t lda, const float *B, int64_t
                             void *workspace, size_t workspace_bytes, void *stream);
 int gnnagg_dense_status(const void *workspace, void *stream);
 
+/* Weight gradient of the same layer, dW[N,K] = G[M,N]^T . X[M,K] (overwritten), on the tensor cores
+ * with the same three-product TF32 split; replaces the `grad_out.t() @ input` products of the
+ * Linear layers' backward.  N, K <= 256; G and X 16-byte aligned with row strides % 4 == 0.
+ * workspace: gnnagg_dense_wgrad_workspace_bytes(N, K) bytes, 16-byte aligned, zeroed once before
+ * first use (status word as above, then one partial product per SM that a second kernel adds in a
+ * fixed order). */
+size_t gnnagg_dense_wgrad_workspace_bytes(int32_t N, int32_t K);
+int gnnagg_dense_wgrad_tf32x3_f32(const float *G, int64_t ldg, const float *X, int64_t ldx, int64_t M, int32_t N,
+                                  int32_t K, float *dW, int64_t ldw, void *workspace, size_t workspace_bytes,
+                                  void *stream);
+
 /* ------------------------------------------------------------------------------------
  * N1  dropout -> LayerNorm -> ReLU of the hidden layers, one pass forward, one backward
  *

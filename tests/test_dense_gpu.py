@@ -100,19 +100,22 @@ def test_dense_rejects_unsupported():
     assert not dense.supported(torch.randn(64, 64, device="cuda"), 300)
 
 
-def test_sage_dense_autograd_matches_torch():
+@pytest.mark.parametrize("k_in,n_out", [(100, 256), (256, 47)])
+def test_sage_dense_autograd_matches_torch(k_in, n_out):
+    """Forward and all five gradients of the layer's dense half; n_out = 47 exercises the zero-padded
+    upstream gradient (rows of 47 floats are not TMA-addressable)."""
     from gnn_benchmark_b200 import dense
 
     old = dense.MODE
     dense.MODE = "tf32x3"
     try:
         g = torch.Generator(device="cuda").manual_seed(5)
-        aggr = torch.randn(3000, 100, device="cuda", generator=g, requires_grad=True)
-        x = torch.randn(3000, 100, device="cuda", generator=g, requires_grad=True)
-        wn = torch.randn(256, 100, device="cuda", generator=g, requires_grad=True)
-        ws = torch.randn(256, 100, device="cuda", generator=g, requires_grad=True)
-        b = torch.randn(256, device="cuda", generator=g, requires_grad=True)
-        go = torch.randn(3000, 256, device="cuda", generator=g)
+        aggr = torch.randn(3000, k_in, device="cuda", generator=g, requires_grad=True)
+        x = torch.randn(3000, k_in, device="cuda", generator=g, requires_grad=True)
+        wn = torch.randn(n_out, k_in, device="cuda", generator=g, requires_grad=True)
+        ws = torch.randn(n_out, k_in, device="cuda", generator=g, requires_grad=True)
+        b = torch.randn(n_out, device="cuda", generator=g, requires_grad=True)
+        go = torch.randn(3000, n_out, device="cuda", generator=g)
         out = dense.SageDense.apply(aggr, x, wn, ws, b)
         out.backward(go)
         got = [out.detach()] + [t.grad.clone() for t in (aggr, x, wn, ws, b)]
@@ -126,3 +129,32 @@ def test_sage_dense_autograd_matches_torch():
             torch.testing.assert_close(a_.double(), b_.double(), rtol=1e-5, atol=1e-3)
     finally:
         dense.MODE = old
+
+
+@pytest.mark.parametrize("M,N,K", [
+    (16, 32, 32), (1000, 256, 256), (40000, 256, 100), (5000, 128, 256), (3333, 172, 256), (777, 100, 48),
+    (200000, 256, 256), (15, 256, 128),
+])
+def test_wgrad_matches_fp64(M, N, K):
+    """dW = G^T X against fp64; same element-wise bound as the forward product."""
+    from gnn_benchmark_b200 import dense
+
+    g = torch.Generator(device="cuda").manual_seed(M + N)
+    G = torch.randn(M, N, device="cuda", generator=g)
+    X = torch.randn(M, K, device="cuda", generator=g)
+    out = dense.wgrad(G, X)
+    dense.check_status()
+    ref = G.double().t() @ X.double()
+    scale = G.abs().double().t() @ X.abs().double() + 1e-30
+    err = ((out.double() - ref).abs() / scale).max().item()
+    assert err <= 2e-6, f"M={M} N={N} K={K}: relative error {err:.3e}"
+
+
+def test_wgrad_rejects_unsupported():
+    from gnn_benchmark_b200 import dense
+
+    g = torch.randn(64, 47, device="cuda")
+    x = torch.randn(64, 64, device="cuda")
+    assert not dense.wgrad_supported(g, x)
+    with pytest.raises(RuntimeError):
+        dense.wgrad(g, x)
