@@ -24,7 +24,6 @@
 #include <cuda.h>
 
 #include <mutex>
-#include <stdlib.h>
 
 #include "common.cuh"
 
@@ -224,7 +223,7 @@ struct GemmParams {
     const float *bias;
     int *status;
     int64_t M, ldc;
-    int N, n_pad, K, accumulate, num_tiles, tma_store, dbg;
+    int N, n_pad, K, accumulate, num_tiles, tma_store;
 };
 
 enum : int {
@@ -296,7 +295,7 @@ gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
             for (int tile = blockIdx.x; tile < p.num_tiles && ok; tile += gridDim.x) {
                 const int m0 = tile * BM;
                 const int next = tile + (int)gridDim.x;
-                if (next < p.num_tiles && !(p.dbg & 32))
+                if (next < p.num_tiles)
                     for (int kb = 0; kb < KB; ++kb) tma_prefetch_2d(&map_a, kb * BK, next * BM);
                 for (int kb = 0; kb < KB; ++kb, ++it) {
                     const int s = it % kStages;
@@ -306,11 +305,6 @@ gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
                         break;
                     }
                     const uint32_t sa = smem_u32(stage_base + s * STAGE_BYTES);
-                    if (p.dbg & 8) {
-                        mbar_arrive_expect_tx(bar_full(s), (uint32_t)A_TILE_BYTES);
-                        tma_load_2d(sa, &map_a, bar_full(s), kb * BK, m0);
-                        continue;
-                    }
                     mbar_arrive_expect_tx(bar_full(s), (uint32_t)A_TILE_BYTES + 2u * b_bytes);
                     tma_load_2d(sa, &map_a, bar_full(s), kb * BK, m0);
                     tma_load_2d(sa + 2 * A_TILE_BYTES, &map_bhi, bar_full(s), kb * BK, 0);
@@ -358,11 +352,6 @@ gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
                     const uint64_t a_lo = make_smem_desc(sa + A_TILE_BYTES);
                     const uint64_t b_hi = make_smem_desc(sa + 2 * A_TILE_BYTES);
                     const uint64_t b_lo = make_smem_desc(sa + 2 * A_TILE_BYTES + B_TILE_BYTES);
-                    if (p.dbg & 16) {
-                        tc_mma_tf32(d_tmem, a_hi, b_hi, idesc, kb > 0 ? 1u : 0u);
-                        tc_commit(bar_empty(s));
-                        continue;
-                    }
                     // the two products of the loaded panel start at once; k advances 32 bytes inside the swizzled row
 #pragma unroll
                     for (int k = 0; k < BK / UMMA_K; ++k)
@@ -411,7 +400,6 @@ gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
                 }
                 const float4 *raw = reinterpret_cast<const float4 *>(stage_base + s * STAGE_BYTES);
                 float4 *lo = reinterpret_cast<float4 *>(stage_base + s * STAGE_BYTES + A_TILE_BYTES);
-                if (!(p.dbg & 4))
 #pragma unroll
                 for (int j = 0; j < A_TILE_BYTES / 16 / 128; ++j) {
                     const int i = tid + 128 * j;
@@ -443,7 +431,7 @@ gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
             }
             tc_fence_after();
             const int64_t row0 = (int64_t)tile * BM + q * 32;
-            for (int c0 = 0; c0 < p.N && !(p.dbg & 2); c0 += 32) {
+            for (int c0 = 0; c0 < p.N; c0 += 32) {
                 uint32_t r[32];
                 tc_ld_32x32(tmem_base + (uint32_t)(b * kAccStride + c0) + ((uint32_t)(q * 32) << 16), r);
                 if (p.tma_store) {
@@ -464,7 +452,7 @@ gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
                     }
                     fence_generic_to_async_smem();
                     __syncwarp();
-                    if (lane == 0 && !(p.dbg & 1)) {
+                    if (lane == 0) {
                         if (p.accumulate)
                             tma_reduce_add_2d(&map_c, smem_u32(buf), c0, (int)row0);
                         else
@@ -480,7 +468,7 @@ gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
                 for (int j = 0; j < 32; ++j) tr[lane * kEpiPad + j] = __uint_as_float(r[j]);
                 __syncwarp();
                 const int col = c0 + lane;
-                if (col < p.N && !(p.dbg & 1)) {
+                if (col < p.N) {
                     const float bv = bias_s[col];
 #pragma unroll 4
                     for (int rr = 0; rr < 32; ++rr) {
@@ -548,7 +536,7 @@ struct WgradParams {
     float *partial;   // [grid][n_rows][kp]
     int *status;
     int64_t M;
-    int N, K, n_pad, kp, blocks_per_cta, total_blocks, dbg;
+    int N, K, n_pad, kp, blocks_per_cta, total_blocks;
     uint64_t desc;   // shared-memory descriptor without the start address
 };
 
@@ -654,17 +642,15 @@ wgrad_tf32x3_kernel(const __grid_constant__ CUtensorMap map_g, const __grid_cons
                     break;
                 }
                 tc_fence_after();
-                if (!(p.dbg & 16)) {
 #pragma unroll
-                    for (int ks = 0; ks < WG_ROWS / UMMA_K; ++ks)
-                        for (int h = 0; h < halves; ++h) {
-                            const uint32_t d = tmem_base + (uint32_t)(h * kAccStride);
-                            tc_mma_tf32(d, make_smem_desc_mn(g_lo + h * 4 * WG_BOX_BYTES + ks * 1024, p.desc),
-                                        make_smem_desc_mn(x_raw + ks * 1024, p.desc), idesc, 1u);
-                            tc_mma_tf32(d, make_smem_desc_mn(g_raw + h * 4 * WG_BOX_BYTES + ks * 1024, p.desc),
-                                        make_smem_desc_mn(x_lo + ks * 1024, p.desc), idesc, 1u);
-                        }
-                }
+                for (int ks = 0; ks < WG_ROWS / UMMA_K; ++ks)
+                    for (int h = 0; h < halves; ++h) {
+                        const uint32_t d = tmem_base + (uint32_t)(h * kAccStride);
+                        tc_mma_tf32(d, make_smem_desc_mn(g_lo + h * 4 * WG_BOX_BYTES + ks * 1024, p.desc),
+                                    make_smem_desc_mn(x_raw + ks * 1024, p.desc), idesc, 1u);
+                        tc_mma_tf32(d, make_smem_desc_mn(g_raw + h * 4 * WG_BOX_BYTES + ks * 1024, p.desc),
+                                    make_smem_desc_mn(x_lo + ks * 1024, p.desc), idesc, 1u);
+                    }
                 tc_commit(bar_empty(s));
             }
             if (ok) {
@@ -693,7 +679,7 @@ wgrad_tf32x3_kernel(const __grid_constant__ CUtensorMap map_g, const __grid_cons
             }
             uint8_t *st = smem + s * WG_STAGE_BYTES;
             const int ng4 = nb_g * (WG_BOX_BYTES / 16), nx4 = nb_x * (WG_BOX_BYTES / 16);
-            if (!(p.dbg & 4)) {
+            {
                 const float4 *graw = reinterpret_cast<const float4 *>(st);
                 float4 *glo = reinterpret_cast<float4 *>(st + WG_PANEL_BYTES);
                 for (int i = tid; i < ng4; i += 256) {
@@ -898,7 +884,6 @@ extern "C" int gnnagg_dense_tf32x3_f32(const float *A, int64_t lda, const float 
     p.accumulate = accumulate;
     p.num_tiles = (int)((M + BM - 1) / BM);
     p.tma_store = tma_store ? 1 : 0;
-    p.dbg = getenv("GNNAGG_DENSE_DEBUG") ? atoi(getenv("GNNAGG_DENSE_DEBUG")) : 0;
     const int grid = p.num_tiles < kNumSMs ? p.num_tiles : kNumSMs;
     gemm_tf32x3_kernel<<<grid, kThreads, SMEM_BYTES, st>>>(map_a, map_bhi, map_blo, map_c, p);
     return check_launch("gemm_tf32x3_kernel");
@@ -964,7 +949,6 @@ extern "C" int gnnagg_dense_wgrad_tf32x3_f32(const float *G, int64_t ldg, const 
     p.kp = round_up(K, 4);
     p.total_blocks = (int)((M + WG_ROWS - 1) / WG_ROWS);
     p.blocks_per_cta = (p.total_blocks + kNumSMs - 1) / kNumSMs;
-    p.dbg = getenv("GNNAGG_DENSE_DEBUG") ? atoi(getenv("GNNAGG_DENSE_DEBUG")) : 0;
     p.desc = smem_desc_mn_template(WG_BOX_BYTES, 512, 1);
     const int grid = (p.total_blocks + p.blocks_per_cta - 1) / p.blocks_per_cta;
     wgrad_tf32x3_kernel<<<grid, WG_THREADS, WG_SMEM_BYTES, st>>>(map_g, map_x, p);
