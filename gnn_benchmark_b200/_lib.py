@@ -50,6 +50,8 @@ SIGNATURES = {
     "gnnagg_dropout_ln_relu_partial_bytes": (_sz, [_i32]),
     "gnnagg_dropout_ln_relu_fwd": (ctypes.c_int, [_vp, _i64, _i64, _i32, _vp, _vp, ctypes.c_float, ctypes.c_float,
                                                   ctypes.c_uint64, _vp, _i64, _vp, _vp, _vp]),
+    "gnnagg_relu_dropout_fwd": (ctypes.c_int, [_vp, _i64, _i64, _i32, ctypes.c_float, ctypes.c_uint64, _vp, _i64, _vp, _vp]),
+    "gnnagg_relu_dropout_bwd": (ctypes.c_int, [_vp, _i64, _vp, _i64, _i32, ctypes.c_float, _vp, _i64, _vp]),
     "gnnagg_dropout_ln_relu_bwd": (ctypes.c_int, [_vp, _i64, _vp, _i64, _vp, _vp, _vp, _vp, _i64, _i32, ctypes.c_float,
                                                   _vp, _i64, _vp, _sz, _vp, _vp, _vp]),
 }

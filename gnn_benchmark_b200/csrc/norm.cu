@@ -254,6 +254,47 @@ __global__ void ln_param_grad_kernel(const float *__restrict__ partial, int nblo
         dbeta[c - F] = s;
 }
 
+
+// y = relu(x) * keep / (1 - p) in one pass (Y may alias X); mask gets 4 bits per float4 chunk:
+// bit i set = element i was positive and kept, i.e. the gradient passes (scaled).  F % 4 == 0.
+__global__ void __launch_bounds__(256)
+relu_dropout_fwd_kernel(const float *X, int64_t ldx, int64_t rows, int chunks, float keep_scale, uint32_t thresh16,
+                        uint32_t k0, uint32_t k1, float *Y, int64_t ldy, uint8_t *__restrict__ mask) {
+    const Philox rng{k0, k1};
+    const int64_t total = rows * chunks;
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+        const int64_t row = i / chunks;
+        const int c = (int)(i - row * chunks);
+        float4 v = *(reinterpret_cast<const float4 *>(X + row * ldx) + c);
+        uint32_t kb = thresh16 != 0 ? keep_bits(rng, row, c, thresh16) : 15u;
+        kb &= (v.x > 0.0f ? 1u : 0u) | (v.y > 0.0f ? 2u : 0u) | (v.z > 0.0f ? 4u : 0u) | (v.w > 0.0f ? 8u : 0u);
+        v.x = (kb & 1u) ? v.x * keep_scale : 0.0f;
+        v.y = (kb & 2u) ? v.y * keep_scale : 0.0f;
+        v.z = (kb & 4u) ? v.z * keep_scale : 0.0f;
+        v.w = (kb & 8u) ? v.w * keep_scale : 0.0f;
+        *(reinterpret_cast<float4 *>(Y + row * ldy) + c) = v;
+        if (mask != nullptr) mask[i] = (uint8_t)kb;
+    }
+}
+
+// gx = gy * mask * keep_scale (GX may alias GY).
+__global__ void __launch_bounds__(256)
+relu_dropout_bwd_kernel(const float *GY, int64_t ldg, const uint8_t *__restrict__ mask, int64_t rows, int chunks,
+                        float keep_scale, float *GX, int64_t ldgx) {
+    const int64_t total = rows * chunks;
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+        const int64_t row = i / chunks;
+        const int c = (int)(i - row * chunks);
+        float4 v = *(reinterpret_cast<const float4 *>(GY + row * ldg) + c);
+        const uint32_t kb = mask[i];
+        v.x = (kb & 1u) ? v.x * keep_scale : 0.0f;
+        v.y = (kb & 2u) ? v.y * keep_scale : 0.0f;
+        v.z = (kb & 4u) ? v.z * keep_scale : 0.0f;
+        v.w = (kb & 8u) ? v.w * keep_scale : 0.0f;
+        *(reinterpret_cast<float4 *>(GX + row * ldgx) + c) = v;
+    }
+}
+
 constexpr int kNormGrid = kNumSMs * 8;
 
 int norm_grid(int64_t rows) {
@@ -342,4 +383,46 @@ extern "C" int gnnagg_dropout_ln_relu_bwd(const float *GY, int64_t ldg, const fl
     if (rc != GNNAGG_OK) return rc;
     ln_param_grad_kernel<<<(2 * F + 127) / 128, 128, 0, st>>>(partial, grid, F, dgamma, dbeta);
     return check_launch("ln_param_grad_kernel");
+}
+
+static uint32_t drop_threshold(float p_drop) {
+    uint32_t thresh = (uint32_t)(p_drop * 65536.0f + 0.5f);
+    if (p_drop > 0.0f && thresh == 0) thresh = 1;
+    return thresh;
+}
+
+extern "C" int gnnagg_relu_dropout_fwd(const float *X, int64_t ldx, int64_t rows, int32_t F, float p_drop, uint64_t seed,
+                                       float *Y, int64_t ldy, uint8_t *mask, void *stream) {
+    if (rows < 0 || F < 0) return fail(GNNAGG_ERR_ARG, "relu_dropout_fwd: negative size");
+    if (rows == 0 || F == 0) return GNNAGG_OK;
+    if (X == nullptr || Y == nullptr) return fail(GNNAGG_ERR_ARG, "relu_dropout_fwd: null pointer");
+    if (!(p_drop >= 0.0f && p_drop < 1.0f)) return fail(GNNAGG_ERR_ARG, "relu_dropout_fwd: p must be in [0,1)");
+    if ((F & 3) != 0 || (ldx & 3) != 0 || (ldy & 3) != 0 || ldx < F || ldy < F || !aligned16(X) || !aligned16(Y))
+        return fail(GNNAGG_ERR_UNSUPPORTED, "relu_dropout_fwd: F and row strides must be multiples of 4, rows 16-byte aligned");
+    const uint32_t thresh = drop_threshold(p_drop);
+    const float keep_scale = thresh ? 65536.0f / (float)(65536u - thresh) : 1.0f;
+    const int64_t total = rows * (F >> 2);
+    const int64_t want = div_up(total, 256);
+    const int grid = (int)(want < (int64_t)kNumSMs * 16 ? want : (int64_t)kNumSMs * 16);
+    relu_dropout_fwd_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+        X, ldx, rows, F >> 2, keep_scale, thresh, (uint32_t)seed, (uint32_t)(seed >> 32), Y, ldy, mask);
+    return check_launch("relu_dropout_fwd_kernel");
+}
+
+extern "C" int gnnagg_relu_dropout_bwd(const float *GY, int64_t ldg, const uint8_t *mask, int64_t rows, int32_t F,
+                                       float p_drop, float *GX, int64_t ldgx, void *stream) {
+    if (rows < 0 || F < 0) return fail(GNNAGG_ERR_ARG, "relu_dropout_bwd: negative size");
+    if (rows == 0 || F == 0) return GNNAGG_OK;
+    if (GY == nullptr || GX == nullptr || mask == nullptr) return fail(GNNAGG_ERR_ARG, "relu_dropout_bwd: null pointer");
+    if (!(p_drop >= 0.0f && p_drop < 1.0f)) return fail(GNNAGG_ERR_ARG, "relu_dropout_bwd: p must be in [0,1)");
+    if ((F & 3) != 0 || (ldg & 3) != 0 || (ldgx & 3) != 0 || ldg < F || ldgx < F || !aligned16(GY) || !aligned16(GX))
+        return fail(GNNAGG_ERR_UNSUPPORTED, "relu_dropout_bwd: F and row strides must be multiples of 4, rows 16-byte aligned");
+    const uint32_t thresh = drop_threshold(p_drop);
+    const float keep_scale = thresh ? 65536.0f / (float)(65536u - thresh) : 1.0f;
+    const int64_t total = rows * (F >> 2);
+    const int64_t want = div_up(total, 256);
+    const int grid = (int)(want < (int64_t)kNumSMs * 16 ? want : (int64_t)kNumSMs * 16);
+    relu_dropout_bwd_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(GY, ldg, mask, rows, F >> 2,
+                                                                               keep_scale, GX, ldgx);
+    return check_launch("relu_dropout_bwd_kernel");
 }

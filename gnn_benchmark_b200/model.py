@@ -157,9 +157,7 @@ class DistGCN(torch.nn.Module):
 
     def forward(self, graph, x):
         for i, conv in enumerate(self.convs[:-1]):
-            x = F.relu(conv(graph, x, i), inplace=True)
-            if self.dropout > 0:
-                x = F.dropout(x, p=self.dropout, training=self.training)
+            x = norm.relu_dropout_(conv(graph, x, i), self.dropout, self.training)
         return F.log_softmax(self.convs[-1](graph, x, len(self.convs) - 1), dim=1)
 
 

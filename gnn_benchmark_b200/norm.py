@@ -78,3 +78,42 @@ def dropout_ln_relu(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor, p
         return _DropoutLayerNormReLU.apply(x, weight, bias, p, training, eps)
     x = F.dropout(x, p=p, training=training)
     return F.relu(F.layer_norm(x, (x.size(-1),), weight, bias, eps))
+
+
+class _ReluDropout_(torch.autograd.Function):
+    """relu followed by dropout, in place on x, one pass each way."""
+
+    @staticmethod
+    def forward(ctx, x, p, training):
+        rows, f = x.shape
+        p = float(p) if training else 0.0
+        need_grad = x.requires_grad
+        mask = torch.empty(rows * (f // 4), dtype=torch.uint8, device=x.device) if need_grad else None
+        seed = int(torch.empty((), dtype=torch.int64).random_()) if p > 0 else 0
+        rc = _lib.lib().gnnagg_relu_dropout_fwd(x.data_ptr(), x.stride(0), rows, f, p, seed, x.data_ptr(), x.stride(0),
+                                                _lib.ptr(mask), _lib.stream_ptr(x.device))
+        _lib.check(rc, "relu_dropout_fwd")
+        ctx.mark_dirty(x)
+        ctx.p = p
+        if need_grad:
+            ctx.save_for_backward(mask)
+        return x
+
+    @staticmethod
+    def backward(ctx, gy):
+        (mask,) = ctx.saved_tensors
+        if gy.stride(1) != 1 or gy.stride(0) % 4 != 0 or gy.data_ptr() % 16 != 0:
+            gy = gy.contiguous()
+        gx = torch.empty(gy.shape, dtype=torch.float32, device=gy.device)
+        rc = _lib.lib().gnnagg_relu_dropout_bwd(gy.data_ptr(), gy.stride(0), mask.data_ptr(), gy.size(0), gy.size(1), ctx.p,
+                                                gx.data_ptr(), gx.stride(0), _lib.stream_ptr(gy.device))
+        _lib.check(rc, "relu_dropout_bwd")
+        return gx, None, None
+
+
+def relu_dropout_(x: torch.Tensor, p: float, training: bool) -> torch.Tensor:
+    """dropout(relu(x)) written over x (x must not be needed by the backward of the op that made it)."""
+    if supported(x):
+        return _ReluDropout_.apply(x, p, training)
+    x = F.relu(x, inplace=True)
+    return F.dropout(x, p=p, training=training) if p > 0 else x

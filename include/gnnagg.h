@@ -253,6 +253,14 @@ int gnnagg_dropout_ln_relu_bwd(const float *GY, int64_t ldg, const float *X, int
                                float p_drop, float *GX, int64_t ldgx, float *partial, size_t partial_bytes,
                                float *dgamma, float *dbeta, void *stream);
 
+/* y = relu(x) * keep / (1 - p), one pass, Y may alias X (the GCN layers' relu followed by dropout); the same
+ * counter-based keep-bits as above.  mask: rows * F/4 bytes, bit i of a chunk set = element i positive and
+ * kept; backward is gx = gy * mask / (1 - p) (GX may alias GY).  F % 4 == 0, rows 16-byte aligned. */
+int gnnagg_relu_dropout_fwd(const float *X, int64_t ldx, int64_t rows, int32_t F, float p_drop, uint64_t seed,
+                            float *Y, int64_t ldy, uint8_t *mask, void *stream);
+int gnnagg_relu_dropout_bwd(const float *GY, int64_t ldg, const uint8_t *mask, int64_t rows, int32_t F, float p_drop,
+                            float *GX, int64_t ldgx, void *stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -84,3 +84,28 @@ def test_unsupported_shapes_fall_back():
     w, b = torch.ones(50, device="cuda"), torch.zeros(50, device="cuda")
     y = norm.dropout_ln_relu(x, w, b, 0.0, True)
     torch.testing.assert_close(y, F.relu(F.layer_norm(x, (50,), w, b)))
+
+
+@pytest.mark.parametrize("p", [0.0, 0.5])
+def test_relu_dropout_inplace(p):
+    from gnn_benchmark_b200 import norm
+
+    g = torch.Generator(device="cuda").manual_seed(3)
+    base = torch.randn(2000, 172, device="cuda", generator=g, requires_grad=True)
+    x = base * 1.0
+    x0 = x.detach().clone()
+    torch.manual_seed(11)
+    y = norm.relu_dropout_(x, p, True)
+    assert y.data_ptr() == x.data_ptr()
+    keep = _unpack_mask(y.grad_fn.saved_tensors[0], 2000, 172).float()
+    scale = 1.0 / (1.0 - round(p * 65536) / 65536)
+    assert torch.equal(keep, keep * (x0 > 0))  # a passed gradient implies a positive input
+    torch.testing.assert_close(y.detach(), torch.relu(x0) * keep * scale + 0.0 * x0, rtol=1e-6, atol=0)
+    if p > 0:
+        frac = (keep.sum() / (x0 > 0).sum()).item()
+        assert abs(frac - (1 - p)) < 0.02
+    else:
+        assert torch.equal(keep, (x0 > 0).float())
+    gy = torch.randn(2000, 172, device="cuda", generator=g)
+    y.backward(gy)
+    torch.testing.assert_close(base.grad, gy * keep * scale, rtol=1e-6, atol=0)
