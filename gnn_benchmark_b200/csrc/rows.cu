@@ -55,13 +55,13 @@ extern "C" int gnnagg_gather_rows_f32(const float *X, int64_t ldx, const int32_t
 
 namespace gnnagg {
 
-// Y[i,:] = X[i,:] * s[i]  (DIV: X[i,:] / s[i], the IEEE quotient): the per-row degree scalings around
-// the aggregation (out /= in_degrees; d^-1/2 on either side of the GCN aggregation).  One lane group
-// per row, 128-bit accesses; Y may alias X.
+// Y[i,:] = X[i,:] * s[i] (+ bias)  (DIV: X[i,:] / s[i], the IEEE quotient): the per-row degree scalings
+// around the aggregation (out /= in_degrees; d^-1/2 on either side of the GCN aggregation, where the
+// layer's bias rides along).  One lane group per row, 128-bit accesses; Y may alias X.
 template <bool VEC, bool DIV>
 __global__ void __launch_bounds__(256)
-    scale_rows_kernel(const float *X, int64_t ldx, const float *__restrict__ s, int64_t rows, int FV, int log2g,
-                      float *Y, int64_t ldy) {
+    scale_rows_kernel(const float *X, int64_t ldx, const float *__restrict__ s, const float *__restrict__ bias,
+                      int64_t rows, int FV, int log2g, float *Y, int64_t ldy) {
     const int G = 1 << log2g;
     const int gl = threadIdx.x & (G - 1);
     const int64_t groups_per_block = blockDim.x >> log2g;
@@ -78,10 +78,17 @@ __global__ void __launch_bounds__(256)
                 } else {
                     v.x *= f, v.y *= f, v.z *= f, v.w *= f;
                 }
+                if (bias != nullptr) {
+                    const float4 b = __ldg(reinterpret_cast<const float4 *>(bias) + vi);
+                    v.x += b.x, v.y += b.y, v.z += b.z, v.w += b.w;
+                }
                 yp[vi] = v;
             }
         } else {
-            for (int vi = gl; vi < FV; vi += G) Y[i * ldy + vi] = DIV ? __fdiv_rn(X[i * ldx + vi], f) : X[i * ldx + vi] * f;
+            for (int vi = gl; vi < FV; vi += G) {
+                const float v = DIV ? __fdiv_rn(X[i * ldx + vi], f) : X[i * ldx + vi] * f;
+                Y[i * ldy + vi] = bias != nullptr ? v + __ldg(bias + vi) : v;
+            }
         }
     }
 }
@@ -89,12 +96,13 @@ __global__ void __launch_bounds__(256)
 }  // namespace gnnagg
 
 extern "C" int gnnagg_scale_rows_f32(const float *X, int64_t ldx, const float *s, int64_t rows, int32_t F,
-                                     int32_t divide, float *Y, int64_t ldy, void *stream) {
+                                     int32_t divide, const float *bias, float *Y, int64_t ldy, void *stream) {
     if (rows < 0 || F < 0 || (divide != 0 && divide != 1)) return fail(GNNAGG_ERR_ARG, "scale_rows: bad size or flag");
     if (rows == 0 || F == 0) return GNNAGG_OK;
     if (X == nullptr || s == nullptr || Y == nullptr || ldx < F || ldy < F)
         return fail(GNNAGG_ERR_ARG, "scale_rows: null pointer or leading dimension smaller than F");
-    const bool vec = (F % 4 == 0) && (ldx % 4 == 0) && (ldy % 4 == 0) && aligned16(X) && aligned16(Y);
+    const bool vec = (F % 4 == 0) && (ldx % 4 == 0) && (ldy % 4 == 0) && aligned16(X) && aligned16(Y) &&
+                     (bias == nullptr || aligned16(bias));
     const int fv = vec ? F / 4 : F;
     int log2g = 0;
     while ((1 << log2g) < fv && log2g < 5) ++log2g;
@@ -103,7 +111,7 @@ extern "C" int gnnagg_scale_rows_f32(const float *X, int64_t ldx, const float *s
     const int64_t cap = (int64_t)kNumSMs * 16;
     if (blocks > cap) blocks = cap;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
-#define LAUNCH(V, D) scale_rows_kernel<V, D><<<(unsigned)blocks, 256, 0, st>>>(X, ldx, s, rows, fv, log2g, Y, ldy)
+#define LAUNCH(V, D) scale_rows_kernel<V, D><<<(unsigned)blocks, 256, 0, st>>>(X, ldx, s, bias, rows, fv, log2g, Y, ldy)
     if (vec) {
         if (divide) LAUNCH(true, true); else LAUNCH(true, false);
     } else {

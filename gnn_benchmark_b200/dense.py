@@ -129,9 +129,12 @@ def check_status(device=None) -> None:
                                   _lib.lib().gnnagg_error_string(code).decode()))
 
 
-def scale_rows(x: torch.Tensor, s: torch.Tensor, divide: bool = False, out: torch.Tensor = None) -> torch.Tensor:
-    """out[i,:] = x[i,:] * s[i] (or / s[i]); s has one element per row; out=x scales in place."""
-    _lib.require_cuda(x, s, out)
+def scale_rows(x: torch.Tensor, s: torch.Tensor, divide: bool = False, out: torch.Tensor = None,
+               bias: torch.Tensor = None) -> torch.Tensor:
+    """out[i,:] = x[i,:] * s[i] (or / s[i]) (+ bias); s has one element per row; out=x scales in place."""
+    _lib.require_cuda(x, s, out, bias)
+    if bias is not None and (bias.dtype != torch.float32 or bias.numel() != x.size(1) or not bias.is_contiguous()):
+        raise RuntimeError("scale_rows: bias must be a contiguous float32 vector with one element per column")
     if x.dim() != 2 or x.dtype != torch.float32 or x.stride(1) != 1 or s.dtype != torch.float32 \
             or s.numel() != x.size(0) or not s.is_contiguous():
         raise RuntimeError("scale_rows: x must be (rows,F) float32 with unit inner stride, s float32 with rows elements")
@@ -140,7 +143,8 @@ def scale_rows(x: torch.Tensor, s: torch.Tensor, divide: bool = False, out: torc
     if out.shape != x.shape or out.dtype != torch.float32 or out.stride(1) != 1:
         raise RuntimeError("scale_rows: out must match x")
     rc = _lib.lib().gnnagg_scale_rows_f32(x.data_ptr(), x.stride(0), s.data_ptr(), x.size(0), x.size(1),
-                                          1 if divide else 0, out.data_ptr(), out.stride(0), _lib.stream_ptr(x.device))
+                                          1 if divide else 0, _lib.ptr(bias), out.data_ptr(), out.stride(0),
+                                          _lib.stream_ptr(x.device))
     _lib.check(rc, "scale_rows_f32")
     return out
 

@@ -94,12 +94,13 @@ class _ScaledAggregator(torch.autograd.Function):
     GPU every saved activation is 14 GB)."""
 
     @staticmethod
-    def forward(ctx, graph, x, dinv, layer, num_bits, is_pre_delay, is_training):
+    def forward(ctx, graph, x, dinv, layer, num_bits, is_pre_delay, is_training, bias=None):
         scaled = dense.scale_rows(x, dinv)
         out = Aggregator.forward(ctx, graph, scaled, layer, num_bits, is_pre_delay, is_training)
         del scaled
-        dense.scale_rows(out, dinv, out=out)
+        dense.scale_rows(out, dinv, out=out, bias=bias)  # the layer's bias rides on the second scaling
         ctx.dinv = dinv
+        ctx.has_bias = bias is not None
         return out
 
     @staticmethod
@@ -108,7 +109,7 @@ class _ScaledAggregator(torch.autograd.Function):
         grad = Aggregator.backward(ctx, g)[1]
         del g
         dense.scale_rows(grad, ctx.dinv, out=grad)
-        return None, grad, None, None, None, None, None
+        return None, grad, None, None, None, None, None, (grad_out.sum(0) if ctx.has_bias else None)
 
 
 class DistGCNConv(torch.nn.Module):
@@ -127,16 +128,20 @@ class DistGCNConv(torch.nn.Module):
         if self.bias is not None:
             torch.nn.init.zeros_(self.bias)
 
-    def _lin(self, x):
-        return dense.LinearTC.apply(x, self.lin.weight, None) if dense.enabled() else self.lin(x)
-
     def forward(self, graph, x, layer) -> Tensor:
         dinv = graph.in_degrees.rsqrt()
         linear_first = self.in_channels > self.out_channels
-        h = self._lin(x) if linear_first else x
+        if dense.enabled():  # the bias goes into the epilogue of whichever kernel runs last
+            if linear_first:
+                h = dense.LinearTC.apply(x, self.lin.weight, None)
+                return _ScaledAggregator.apply(graph, h, dinv, layer, self.num_bits, self.is_pre_delay, self.training,
+                                               self.bias)
+            h = _ScaledAggregator.apply(graph, x, dinv, layer, self.num_bits, self.is_pre_delay, self.training)
+            return dense.LinearTC.apply(h, self.lin.weight, self.bias)
+        h = self.lin(x) if linear_first else x
         h = _ScaledAggregator.apply(graph, h, dinv, layer, self.num_bits, self.is_pre_delay, self.training)
         if not linear_first:
-            h = self._lin(h)
+            h = self.lin(h)
         if self.bias is not None:
             h += self.bias
         return h

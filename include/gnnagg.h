@@ -126,11 +126,12 @@ int gnnagg_csr_validate(const int64_t *rowptr, const int32_t *col, int64_t M, in
 int gnnagg_gather_rows_f32(const float *X, int64_t ldx, const int32_t *idx, int64_t rows, int32_t F,
                            float *OUT, int64_t ldo, void *stream);
 
-/* Y[i,:] = X[i,:] * s[i] (divide == 0) or X[i,:] / s[i] (divide == 1, IEEE quotient); Y may alias X.
- * Replaces the broadcast `out /= graph.in_degrees` of the layer (model/layers/sageconv.py:84-85) and
- * the d^-1/2 row scalings of a GCN layer around the aggregation. */
+/* Y[i,:] = X[i,:] * s[i] (divide == 0) or X[i,:] / s[i] (divide == 1, IEEE quotient), plus bias[F] when
+ * bias != NULL; Y may alias X.  Replaces the broadcast `out /= graph.in_degrees` of the layer
+ * (model/layers/sageconv.py:84-85) and the d^-1/2 row scalings (and bias add) of a GCN layer around
+ * the aggregation. */
 int gnnagg_scale_rows_f32(const float *X, int64_t ldx, const float *s, int64_t rows, int32_t F, int32_t divide,
-                          float *Y, int64_t ldy, void *stream);
+                          const float *bias, float *Y, int64_t ldy, void *stream);
 
 /* ------------------------------------------------------------------------------------
  * K3a  per-row min/max quantise + row-pack, one call for all peer segments

@@ -82,6 +82,8 @@ def test_scale_rows_matches_torch():
     y = x.clone()
     dense.scale_rows(y, s, out=y)
     assert torch.equal(y, x * s)
+    b = torch.randn(172, device="cuda")
+    assert torch.equal(dense.scale_rows(x, s, bias=b), x * s + b)
     x2 = torch.randn(77, 47, device="cuda", requires_grad=True)  # scalar path, through autograd
     s2 = torch.rand(77, 1, device="cuda") + 1.0
     out = dense.RowDivide_.apply(x2 * 1.0, s2)
