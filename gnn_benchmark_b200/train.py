@@ -96,6 +96,9 @@ def main():
     data = load_data(config)
     TimeRecorder(config["num_layers"], config["num_epochs"], enabled=bool(config.get("record_phases", False)))
     train(model, data, optimizer, config["num_epochs"], config["num_bits"])
+    from . import dense
+
+    dense.check_status()  # raises if a tensor-core kernel gave up on one of its bounded waits
     TimeRecorder.ctx.print_total_time()
 
 
