@@ -1,6 +1,6 @@
 """Generate the golden fixtures under tests/golden/ by running the REFERENCE's own code.
 
-Run once, in a container that has the reference checkout (default /root/reference) and the
+Run once, in a container that has the reference checkout (its root is the optional argument) and the
 compiled reference module (python oracle/build_ref.py):
 
     python tests/golden/make_golden.py [reference_root]
