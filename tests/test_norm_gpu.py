@@ -109,3 +109,32 @@ def test_relu_dropout_inplace(p):
     gy = torch.randn(2000, 172, device="cuda", generator=g)
     y.backward(gy)
     torch.testing.assert_close(base.grad, gy * keep * scale, rtol=1e-6, atol=0)
+
+
+def test_keep_bits_match_philox_restatement():
+    """Bit-exact: the kernels' dropout decisions against the numpy Philox-4x32-10 restatement
+    (tests/util.py, pinned to the generator's published known-answer vectors)."""
+    import numpy as np
+
+    from gnn_benchmark_b200 import norm
+    from util import dropout_keep_bits
+
+    rows, f = 300, 256
+    x = torch.randn(rows, f, device="cuda", requires_grad=True)
+    w, b = torch.ones(f, device="cuda"), torch.zeros(f, device="cuda")
+    for p in (0.5, 0.1):
+        torch.manual_seed(7)
+        y = norm.dropout_ln_relu(x, w, b, p, True)
+        got = y.grad_fn.saved_tensors[3].cpu().numpy().reshape(rows, f // 4)
+        torch.manual_seed(7)
+        seed = int(torch.empty((), dtype=torch.int64).random_())
+        assert np.array_equal(got, dropout_keep_bits(rows, f // 4, seed, p))
+    h = (x * 1.0)
+    positive = (h.detach() > 0).cpu().numpy().reshape(rows, f // 4, 4)
+    pos_bits = (positive * np.array([1, 2, 4, 8])).sum(-1).astype(np.uint8)
+    torch.manual_seed(9)
+    z = norm.relu_dropout_(h, 0.5, True)
+    got = z.grad_fn.saved_tensors[0].cpu().numpy().reshape(rows, f // 4)
+    torch.manual_seed(9)
+    seed = int(torch.empty((), dtype=torch.int64).random_())
+    assert np.array_equal(got, dropout_keep_bits(rows, f // 4, seed, 0.5) & pos_bits)

@@ -31,3 +31,39 @@ def rel_err(a, b):
     a = np.asarray(a, dtype=np.float64)
     b = np.asarray(b, dtype=np.float64)
     return np.abs(a - b).max() / max(np.abs(b).max(), 1e-30)
+
+
+def philox4x32_10(counter, key):
+    """Philox-4x32-10 (Salmon et al., SC'11) on numpy uint32 arrays: counter (..., 4), key (2,).
+    The keep-bits of the fused dropout kernels are defined on this generator."""
+    import numpy as np
+
+    c = [np.asarray(counter[..., i], dtype=np.uint64) for i in range(4)]
+    k0, k1 = np.uint64(int(key[0]) & 0xFFFFFFFF), np.uint64(int(key[1]) & 0xFFFFFFFF)
+    m0, m1, mask = np.uint64(0xD2511F53), np.uint64(0xCD9E8D57), np.uint64(0xFFFFFFFF)
+    for _ in range(10):
+        p0, p1 = m0 * c[0], m1 * c[2]
+        hi0, lo0, hi1, lo1 = p0 >> np.uint64(32), p0 & mask, p1 >> np.uint64(32), p1 & mask
+        c = [hi1 ^ c[1] ^ k0, lo1, hi0 ^ c[3] ^ k1, lo0]
+        k0 = (k0 + np.uint64(0x9E3779B9)) & mask
+        k1 = (k1 + np.uint64(0xBB67AE85)) & mask
+    return np.stack([x.astype(np.uint32) for x in c], axis=-1)
+
+
+def dropout_keep_bits(rows, chunks, seed, p):
+    """(rows, chunks) uint8: the 4 keep-bits of every float4 chunk as the kernels draw them:
+    counter = (row low, row high, chunk, 0x6e6f726d), key = (seed low, seed high); element i of a chunk
+    is kept when its 16-bit draw (x low, x high, y low, y high) is >= round(p * 65536)."""
+    import numpy as np
+
+    thresh = max(int(p * 65536.0 + 0.5), 1 if p > 0 else 0)
+    r = np.arange(rows, dtype=np.uint64)[:, None] + np.zeros((1, chunks), dtype=np.uint64)
+    c = np.arange(chunks, dtype=np.uint64)[None, :] + np.zeros((rows, 1), dtype=np.uint64)
+    ctr = np.stack([r & np.uint64(0xFFFFFFFF), r >> np.uint64(32), c, np.full_like(r, 0x6E6F726D)], axis=-1)
+    out = philox4x32_10(ctr, (seed & 0xFFFFFFFF, (seed >> 32) & 0xFFFFFFFF))
+    x, y = out[..., 0], out[..., 1]
+    draws = [x & 0xFFFF, x >> 16, y & 0xFFFF, y >> 16]
+    bits = np.zeros((rows, chunks), dtype=np.uint8)
+    for i, d in enumerate(draws):
+        bits |= ((d >= thresh).astype(np.uint8) << i)
+    return bits
