@@ -222,14 +222,44 @@ def run_single_gpu(args):
         v, _ = arm.run(steps=2, warmup=1)
         cpu = {"value": v, "unit": "edges/s", "cores": arm.cores, "kind": arm.kind, "sample": arm.sample}
 
+    config = workload_config(1, A)
+    epoch = None
+    if not args.no_epoch:
+        del A
+        torch.cuda.empty_cache()
+        epoch = run_epoch_leg()
+
     line = {
         "metric": "aggregated_edges_per_s", "value": value, "unit": "edges/s", "n_gpus": 1, "steps": args.steps,
         "warmup": max(args.warmup, 3), "ms_per_step": t_step * 1e3, "higher_is_better": True, "scaling": "weak",
-        "vs_baseline": None, "dtype": "f32", "data": "synthetic", "config": workload_config(1, A),
+        "vs_baseline": None, "dtype": "f32", "data": "synthetic", "config": config,
         "clocks": clocks, "e2e": e2e, "gpu_launches": launches_per_step * args.steps, "roofline": roofline,
-        "cpu_baseline": cpu,
+        "cpu_baseline": cpu, "epoch": epoch,
     }
     print(json.dumps(line), flush=True)
+
+
+def run_epoch_leg():
+    """The other half of the metric: full-batch epoch time of the products-shaped 3-layer GraphSAGE
+    (2.45 M nodes, 61.9 M undirected Chung-Lu edges, 100 -> 256 -> 256 -> 47) on this GPU, measured by
+    `gnn_benchmark_b200.bench_epoch` in a process of its own after this one has released its buffers."""
+    cmd = [sys.executable, "-m", "gnn_benchmark_b200.bench_epoch", "--model", "sage", "--nodes", "2450000",
+           "--edges", "61900000", "--in-channels", "100", "--hidden", "256", "--out-channels", "47",
+           "--train-frac", "0.08", "--bits", "32", "--epochs", "5"]
+    env = {k: v for k, v in os.environ.items() if k not in ("RANK", "LOCAL_RANK", "WORLD_SIZE")}
+    try:
+        out = subprocess.run(cmd, capture_output=True, text=True, timeout=900, env=env,
+                             cwd=os.path.dirname(os.path.abspath(__file__)))
+        lines = [ln for ln in out.stdout.splitlines() if ln.startswith("{")]
+        if out.returncode != 0 or not lines:
+            return {"error": (out.stderr or out.stdout)[-300:]}
+        d = json.loads(lines[-1])
+        return {"workload": "sage_chunglu_2.45M_nodes_124M_edges_100-256-256-47", "epoch_s": d["value"],
+                "aggregated_edges_per_s": d["aggregated_edges_per_s"],
+                "aggregation_passes_per_step": d["aggregation_passes_per_step"], "epochs_timed":
+                d["config"]["epochs_timed"], "dense": d["config"]["dense"], "dropout": d["config"]["dropout"]}
+    except Exception as exc:  # the SpMM line above must not depend on this leg
+        return {"error": repr(exc)[:300]}
 
 
 def run_e2e_single(A, args, device):
@@ -288,6 +318,7 @@ def main():
     ap.add_argument("--impl", type=str, default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer leg (profiler captures)")
+    ap.add_argument("--no-epoch", action="store_true", help="skip the full-batch epoch leg (N = 1 only)")
     args = ap.parse_args()
 
     if args.impl == "reference":
