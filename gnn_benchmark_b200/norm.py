@@ -74,6 +74,7 @@ class _DropoutLayerNormReLU(torch.autograd.Function):
 def dropout_ln_relu(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor, p: float, training: bool,
                     eps: float = 1e-5) -> torch.Tensor:
     """relu(layer_norm(dropout(x, p, training))) over the last dimension."""
+    _lib.require_cuda(x, weight, bias)
     if supported(x) and weight is not None and bias is not None:
         return _DropoutLayerNormReLU.apply(x, weight, bias, p, training, eps)
     x = F.dropout(x, p=p, training=training)
@@ -113,6 +114,7 @@ class _ReluDropout_(torch.autograd.Function):
 
 def relu_dropout_(x: torch.Tensor, p: float, training: bool) -> torch.Tensor:
     """dropout(relu(x)) written over x (x must not be needed by the backward of the op that made it)."""
+    _lib.require_cuda(x)
     if supported(x):
         return _ReluDropout_.apply(x, p, training)
     x = F.relu(x, inplace=True)

@@ -68,3 +68,19 @@ def test_cpu_tensors_are_refused():
     a = SparseTensor(row=torch.tensor([0, 1]), col=torch.tensor([1, 0]), sparse_sizes=(2, 2))
     with pytest.raises(RuntimeError, match="CUDA tensors only"):
         SPMM_forward(a, torch.ones(2, 4), torch.zeros(2, 4))
+
+
+def test_dense_side_wrappers_refuse_cpu_tensors():
+    """The dense-side front-ends have no CPU path either."""
+    import pytest
+    import torch
+
+    from gnn_benchmark_b200 import dense, norm
+
+    x, w = torch.randn(8, 16), torch.randn(4, 16)
+    for call in (lambda: dense.linear(x, w), lambda: dense.wgrad(torch.randn(8, 4), x),
+                 lambda: dense.scale_rows(x, torch.ones(8)),
+                 lambda: norm.dropout_ln_relu(x, torch.ones(16), torch.zeros(16), 0.0, False),
+                 lambda: norm.relu_dropout_(x, 0.0, False)):
+        with pytest.raises(RuntimeError):
+            call()
