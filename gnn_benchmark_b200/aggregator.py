@@ -145,7 +145,11 @@ class Aggregator(torch.autograd.Function):
         world_size = _world_size()
         rec = _rec()
         t_total = rec.start() if rec else None
-        x = local_nodes_feat.contiguous()
+        # rows may be padded (row stride > F, e.g. 100-wide features kept in 128-float rows so that every
+        # gathered row starts on a 128-byte line); every kernel on the path takes a leading dimension
+        x = local_nodes_feat
+        if x.dim() != 2 or x.stride(1) != 1 or x.stride(0) < x.size(1):
+            x = x.contiguous()
         feat_len = x.size(-1)
         lean = bool(getattr(graph.comm_buf, "lean", False))  # no fp32 staging buffers: the halo stays packed
         packed = world_size > 1 and (is_training or lean) and _packed(num_bits, graph)

@@ -88,7 +88,9 @@ def main():
     g = torch.Generator(device=device).manual_seed(args.seed + 17 * rank)
     data = {
         "graph": graph,
-        "nodes_features": torch.randn(n, args.in_channels, device=device, generator=g),
+        # rows padded to a multiple of 32 floats: every gathered feature row starts on a 128-byte line
+        "nodes_features": torch.randn(n, (args.in_channels + 31) // 32 * 32, device=device,
+                                      generator=g)[:, :args.in_channels],
         "nodes_labels": torch.randint(0, args.out_channels, (n,), device=device, generator=g),
         "nodes_train_masks": torch.nonzero(torch.rand(n, device=device, generator=g) < args.train_frac).view(-1),
         "nodes_valid_masks": torch.zeros(0, dtype=torch.int64, device=device),

@@ -58,6 +58,17 @@ def load_dataset_mask(input_dir, graph_name, rank):
                  for k in ("train", "valid", "test"))
 
 
+def pad_feature_rows(feat: torch.Tensor, multiple: int = 32) -> torch.Tensor:
+    """The same (n, F) values as a view into rows of ceil(F / multiple) * multiple floats, so that every
+    feature row starts on a 128-byte line of HBM (the aggregation gathers whole rows)."""
+    n, f = feat.shape
+    if f % multiple == 0:
+        return feat.contiguous()
+    store = torch.zeros(n, (f + multiple - 1) // multiple * multiple, dtype=feat.dtype, device=feat.device)
+    store[:, :f] = feat
+    return store[:, :f]
+
+
 def _scatter_matrix(idx: torch.Tensor, num_local_nodes: int) -> SparseTensor:
     """(n_local x n_send) unit matrix S with S[idx[i], i] = 1: grad += S @ buf is
     grad.index_add_(0, idx, buf) with the additions of a row applied in increasing i."""
@@ -212,7 +223,7 @@ def load_data(config):
     train_mask, valid_mask, test_mask = load_dataset_mask(input_dir, graph_name, rank)
     data = dict()
     data["graph"] = distributed_graph
-    data["nodes_features"] = load_nodes_features(input_dir, graph_name, rank).to(device)
+    data["nodes_features"] = pad_feature_rows(load_nodes_features(input_dir, graph_name, rank).to(device))
     data["nodes_labels"] = load_nodes_labels(input_dir, graph_name, rank).to(device)
     data["nodes_train_masks"] = train_mask.to(device)
     data["nodes_valid_masks"] = valid_mask.to(device)

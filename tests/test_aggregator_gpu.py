@@ -231,6 +231,48 @@ def test_peer_pipelined_exchange(cuda_lib, monkeypatch, P, F):
         np.testing.assert_array_equal(grad.shape, results[False][r][1].shape)
 
 
+@pytest.mark.parametrize("P,bits,is_pre", [(1, 32, False), (3, 32, False), (2, 2, False), (3, 32, True), (2, 2, True)])
+def test_padded_feature_rows_give_identical_results(cuda_lib, P, bits, is_pre):
+    """Features kept in rows padded to 128 floats (row stride > F) go through the path without a copy
+    and give bit-identical outputs and gradients."""
+    from gnn_benchmark_b200 import Communicator, Quantizer_for_all_procs, TimeRecorder, graphgen
+    from gnn_benchmark_b200.aggregator import Aggregator
+    from gnn_benchmark_b200.data_manager.DataLoader import build_graph
+
+    F = 100
+    begin_np, src, dst = make_graph(31 * P + bits, P, 500, 6)
+    N = int(begin_np[-1])
+    begin = torch.from_numpy(begin_np)
+    rng = np.random.default_rng(4)
+    X = rng.standard_normal((N, F)).astype(np.float32)
+    G = rng.standard_normal((N, F)).astype(np.float32)
+    s_t, d_t = torch.from_numpy(src).cuda(), torch.from_numpy(dst).cuda()
+    Quantizer_for_all_procs(P, bits)
+    TimeRecorder(1, 1)
+    Communicator(bits, is_async=True)
+    results = {}
+    for padded in (False, True):
+        def rank_fn(rank):
+            local, remote = graphgen.partition_edges(s_t, d_t, begin, rank)
+            graph = build_graph(local, remote, begin, rank, P, F, bits, is_pre, device="cuda")
+            b0, b1 = int(begin[rank]), int(begin[rank + 1])
+            x = torch.from_numpy(X[b0:b1]).cuda()
+            if padded:
+                store = torch.full((b1 - b0, 128), float("nan"), device="cuda")
+                store[:, :F] = x
+                x = store[:, :F]
+                assert x.stride(0) == 128
+            ctx = SimpleNamespace()
+            out = Aggregator.forward(ctx, graph, x, 0, bits, is_pre, True)
+            grad = Aggregator.backward(ctx, torch.from_numpy(G[b0:b1]).cuda())[1]
+            return out.cpu().numpy(), grad.cpu().numpy()
+
+        results[padded] = FakeWorld(P).run(rank_fn)
+    for r in range(P):
+        np.testing.assert_array_equal(results[True][r][0], results[False][r][0])
+        np.testing.assert_array_equal(results[True][r][1], results[False][r][1])
+
+
 @pytest.mark.parametrize("P,F,bits", [(2, 128, 2), (4, 256, 2), (3, 64, 8)])
 def test_lean_halo_buffers_give_identical_results(cuda_lib, P, F, bits):
     """lean_halo=True: the fp32 staging buffers of the exchange have no memory (meta tensors); forward
