@@ -2,13 +2,14 @@
 //
 //     C[M,N] (+)= A[M,K] . B[N,K]^T (+ bias[N])          all fp32, row-major, B = an nn.Linear weight
 //
-// in fp32-grade accuracy: every operand is split into two TF32 pieces, x = hi + lo with
-// hi = tf32_rna(x), lo = tf32_rna(x - hi), and three tensor-core products a_lo.b_hi + a_hi.b_lo +
-// a_hi.b_hi are accumulated in fp32 in tensor memory (the dropped a_lo.b_lo term is below 2^-22
-// relative).  The weight is split once per call by a small kernel into a caller-provided workspace.
-// The activation panel is used as loaded for its "hi" products (the tensor core reads the upper 19
-// bits of an fp32 word); its remainder panel is computed inside the GEMM, in shared memory, while
-// those products already run.
+// in fp32-grade accuracy: every operand is split into two TF32 pieces, x = hi + lo, and three
+// tensor-core products a_hi.b_lo + a_hi.b_hi + a_lo.b_hi are accumulated in fp32 in tensor memory (the
+// dropped a_lo.b_lo term is below 2^-21 relative).  The weight is split once per call by a small
+// kernel into a caller-provided workspace (hi = tf32_rna(w), lo = tf32_rna(w - hi)).  The activation
+// panel is used as loaded for its "hi" products (the tensor core reads the upper 19 bits of an fp32
+// word, i.e. hi = x truncated); its remainder panel lo = tf32_rna(x - hi) is computed inside the GEMM,
+// in shared memory, while those products already run.  What limits the accuracy is the accumulator,
+// which rounds toward zero once per MMA: about 1e-6 of sum |a||b| at K = 256 (an fp32 FMA chain: 3e-7).
 //
 // One persistent CTA per SM, 10 warps:
 //   warp 0      lane 0 issues the TMA loads (A raw, B_hi, B_lo per 32-wide k-block; two stages) and
@@ -17,8 +18,9 @@
 //               the commits that free a stage / publish an accumulator;
 //   warps 2-5   compute the remainder (lo) panel of a stage's A tile into a second buffer;
 //   warps 6-9   epilogue: tcgen05.ld of a finished accumulator (two of them in tensor memory, so the
-//               epilogue of one row panel runs under the MMAs of the next), 32x32 transposes through
-//               shared memory, coalesced stores with optional bias and accumulate.
+//               epilogue of one row panel runs under the MMAs of the next), bias add, 32 x 32 blocks
+//               through swizzled shared memory to TMA stores (TMA reduce-add for accumulate); output
+//               rows that TMA cannot address go through a shared-memory transpose and plain stores.
 // Every wait is bounded (about a second); on a time-out the kernel records a code in the status
 // word of the workspace, drains its own copies and MMAs, frees tensor memory and returns.
 #include <cuda.h>
