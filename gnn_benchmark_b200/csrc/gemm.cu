@@ -508,15 +508,18 @@ gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
 // descriptor (layout type 1; with the plain 128-byte swizzle the MMA returns zeros): a {32 columns,
 // 16 rows} TMA box lands as 16 k-rows of 128 bytes, groups of 4 k-rows 512 bytes apart (stride byte
 // offset), the boxes of one operand 2 KB apart (leading byte offset); one MMA consumes 8 k-rows.
-// Each CTA owns a contiguous block of rows, accumulates its 256 x 256 partial product in tensor
-// memory (two 128-lane halves), and writes it to scratch; a second kernel adds the per-CTA partials
-// in a fixed order.  The remainder (lo) panels of both operands are computed in shared memory as in
+// Each CTA owns a contiguous block of rows and accumulates its 256 x 256 partial product in tensor
+// memory (two 128-lane halves).  The tensor-memory accumulator rounds toward zero once per MMA, a
+// one-sided error that grows with the length of the chain, so every 2048 rows the accumulator is
+// moved out and added (round to nearest, CUDA cores) to the CTA's partial in scratch; a second kernel
+// adds the per-CTA partials in a fixed order.  The remainder (lo) panels of both operands are computed in shared memory as in
 // the forward kernel; products: G.X + G_lo.X + G.X_lo.
 constexpr int WG_ROWS = 16;                           // rows (k) per stage: two MMAs of k = 8
 constexpr int WG_BOX_BYTES = WG_ROWS * 128;           // one {32 columns, 16 rows} box
 constexpr int WG_PANEL_BYTES = 8 * WG_BOX_BYTES;      // up to 256 columns of one operand: 16 KB
 constexpr int WG_STAGE_BYTES = 4 * WG_PANEL_BYTES;    // g, g_lo, x, x_lo
 constexpr int WG_STAGES = 3;
+constexpr int WG_FLUSH = 128;                         // stages (2048 rows) per accumulation block, see below
 constexpr int WG_THREADS = 320;
 constexpr int WG_SMEM_BYTES = 1024 + WG_STAGES * WG_STAGE_BYTES + 256;
 static_assert(WG_SMEM_BYTES <= 227 * 1024, "shared memory budget");
@@ -548,14 +551,15 @@ wgrad_tf32x3_kernel(const __grid_constant__ CUtensorMap map_g, const __grid_cons
     extern __shared__ uint8_t smem_raw[];
     uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
     uint64_t *bars = reinterpret_cast<uint64_t *>(smem + WG_STAGES * WG_STAGE_BYTES);
-    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 3 * WG_STAGES + 2);
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 3 * WG_STAGES + 3);
     volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
     const uint32_t bar0 = smem_u32(bars);
     auto bar_full = [&](int s) { return bar0 + 8u * (uint32_t)s; };
     auto bar_split = [&](int s) { return bar0 + 8u * (uint32_t)(WG_STAGES + s); };
     auto bar_empty = [&](int s) { return bar0 + 8u * (uint32_t)(2 * WG_STAGES + s); };
-    const uint32_t bar_acc = bar0 + 8u * (uint32_t)(3 * WG_STAGES);
+    const uint32_t bar_acc = bar0 + 8u * (uint32_t)(3 * WG_STAGES);        // an accumulation block is complete
     const uint32_t bar_drain = bar0 + 8u * (uint32_t)(3 * WG_STAGES + 1);
+    const uint32_t bar_flushed = bar0 + 8u * (uint32_t)(3 * WG_STAGES + 2);  // ... and has been moved out
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int nb_g = (p.N + 31) / 32, nb_x = (p.n_pad + 31) / 32;   // boxes per operand
@@ -572,6 +576,7 @@ wgrad_tf32x3_kernel(const __grid_constant__ CUtensorMap map_g, const __grid_cons
         }
         mbar_init(bar_acc, 1);
         mbar_init(bar_drain, 1);
+        mbar_init(bar_flushed, 128);
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -625,6 +630,17 @@ wgrad_tf32x3_kernel(const __grid_constant__ CUtensorMap map_g, const __grid_cons
             for (int it = 0; it < nkb; ++it) {
                 const int s = it % WG_STAGES;
                 const uint32_t ph = (uint32_t)(it / WG_STAGES) & 1u;
+                const bool first = (it % WG_FLUSH) == 0;  // first stage of an accumulation block
+                if (first && it > 0) {
+                    // publish the finished block and wait until warps 2-5 have moved it out
+                    tc_commit(bar_acc);
+                    if (!mbar_wait(bar_flushed, (uint32_t)(it / WG_FLUSH - 1) & 1u, abort_flag, p.status,
+                                   kErrWaitAccFree)) {
+                        ok = false;
+                        break;
+                    }
+                    tc_fence_after();
+                }
                 if (!mbar_wait(bar_full(s), ph, abort_flag, p.status, kErrWaitFull)) {
                     ok = false;
                     break;
@@ -638,7 +654,7 @@ wgrad_tf32x3_kernel(const __grid_constant__ CUtensorMap map_g, const __grid_cons
                     for (int h = 0; h < halves; ++h)
                         tc_mma_tf32(tmem_base + (uint32_t)(h * kAccStride),
                                     make_smem_desc_mn(g_raw + h * 4 * WG_BOX_BYTES + ks * 1024, p.desc),
-                                    make_smem_desc_mn(x_raw + ks * 1024, p.desc), idesc, (it > 0 || ks > 0) ? 1u : 0u);
+                                    make_smem_desc_mn(x_raw + ks * 1024, p.desc), idesc, (!first || ks > 0) ? 1u : 0u);
                 if (!mbar_wait(bar_split(s), ph, abort_flag, p.status, kErrWaitSplit)) {
                     ok = false;
                     break;
@@ -669,10 +685,46 @@ wgrad_tf32x3_kernel(const __grid_constant__ CUtensorMap map_g, const __grid_cons
             }
         }
     } else {
-        // ---- warps 2-9: remainder panels; afterwards warps 2-5 write the accumulator out ----
+        // ---- warps 2-9: remainder panels; warps 2-5 also move finished accumulation blocks out ----
         const int tid = threadIdx.x - 64;  // 0..255
+        const int q = warp & 3;            // TMEM lane quarter of warps 2-5
+        float *out = p.partial + (int64_t)blockIdx.x * p.N * p.kp;
+        // block `fidx` of this CTA is complete in tensor memory: add it to the partial in scratch
+        auto flush = [&](int fidx) -> bool {
+            const bool ready = mbar_wait(bar_acc, (uint32_t)fidx & 1u, abort_flag, p.status, kErrWaitAccFull);
+            if (!__all_sync(kFullMask, ready)) return false;
+            tc_fence_after();
+            for (int h = 0; h < halves; ++h) {
+                const int n = h * 128 + q * 32 + lane;
+                for (int c0 = 0; c0 < p.K; c0 += 32) {
+                    uint32_t r[32];
+                    tc_ld_32x32(tmem_base + (uint32_t)(h * kAccStride + c0) + ((uint32_t)(q * 32) << 16), r);
+                    if (n < p.N) {
+#pragma unroll
+                        for (int j = 0; j < 8; ++j)
+                            if (c0 + 4 * j < p.kp) {
+                                float4 *dst = reinterpret_cast<float4 *>(out + (int64_t)n * p.kp + c0 + 4 * j);
+                                float4 v = make_float4(__uint_as_float(r[4 * j]), __uint_as_float(r[4 * j + 1]),
+                                                       __uint_as_float(r[4 * j + 2]), __uint_as_float(r[4 * j + 3]));
+                                if (fidx > 0) {
+                                    const float4 o = *dst;
+                                    v.x += o.x, v.y += o.y, v.z += o.z, v.w += o.w;
+                                }
+                                *dst = v;
+                            }
+                    }
+                }
+            }
+            tc_fence_before();
+            mbar_arrive(bar_flushed);
+            return true;
+        };
         bool ok = true;
         for (int it = 0; it < nkb; ++it) {
+            if (warp < 6 && it > 0 && (it % WG_FLUSH) == 0 && !flush(it / WG_FLUSH - 1)) {
+                ok = false;
+                break;
+            }
             const int s = it % WG_STAGES;
             const uint32_t ph = (uint32_t)(it / WG_STAGES) & 1u;
             if (!mbar_wait(bar_full(s), ph, abort_flag, p.status, kErrWaitFull)) {
@@ -700,29 +752,7 @@ wgrad_tf32x3_kernel(const __grid_constant__ CUtensorMap map_g, const __grid_cons
             fence_generic_to_async_smem();
             mbar_arrive(bar_split(s));
         }
-        if (warp < 6) {
-            const int q = warp & 3;
-            const bool ready = ok && mbar_wait(bar_acc, 0, abort_flag, p.status, kErrWaitAccFull);
-            if (__all_sync(kFullMask, ready)) {
-                tc_fence_after();
-                float *out = p.partial + (int64_t)blockIdx.x * p.N * p.kp;
-                for (int h = 0; h < halves; ++h) {
-                    const int n = h * 128 + q * 32 + lane;
-                    for (int c0 = 0; c0 < p.K; c0 += 32) {
-                        uint32_t r[32];
-                        tc_ld_32x32(tmem_base + (uint32_t)(h * kAccStride + c0) + ((uint32_t)(q * 32) << 16), r);
-                        if (n < p.N) {
-#pragma unroll
-                            for (int j = 0; j < 8; ++j)
-                                if (c0 + 4 * j < p.kp)
-                                    *reinterpret_cast<float4 *>(out + (int64_t)n * p.kp + c0 + 4 * j) =
-                                        make_float4(__uint_as_float(r[4 * j]), __uint_as_float(r[4 * j + 1]),
-                                                    __uint_as_float(r[4 * j + 2]), __uint_as_float(r[4 * j + 3]));
-                        }
-                    }
-                }
-            }
-        }
+        if (warp < 6 && ok) flush((nkb - 1) / WG_FLUSH);  // the last block
     }
 
     tc_fence_before();

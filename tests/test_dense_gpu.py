@@ -135,10 +135,11 @@ def test_sage_dense_autograd_matches_torch(k_in, n_out):
 
 @pytest.mark.parametrize("M,N,K", [
     (16, 32, 32), (1000, 256, 256), (40000, 256, 100), (5000, 128, 256), (3333, 172, 256), (777, 100, 48),
-    (200000, 256, 256), (15, 256, 128),
+    (200000, 256, 256), (15, 256, 128), (700000, 64, 96), (148 * 2048 + 16, 172, 32),
 ])
 def test_wgrad_matches_fp64(M, N, K):
-    """dW = G^T X against fp64; same element-wise bound as the forward product."""
+    """dW = G^T X against fp64; same element-wise bound as the forward product.  The last two shapes
+    give every CTA more than 2048 rows, so the periodic move of the accumulator to scratch runs."""
     from gnn_benchmark_b200 import dense
 
     g = torch.Generator(device="cuda").manual_seed(M + N)
