@@ -32,21 +32,19 @@
 namespace gnnagg {
 namespace {
 
-#ifndef GNNAGG_DENSE_BK
-#define GNNAGG_DENSE_BK 32
-#endif
 constexpr int BM = 128;                 // rows of A per tile = UMMA M = TMEM lanes
-constexpr int BK = GNNAGG_DENSE_BK;     // fp32 per k-block: one swizzle row (16 -> 64-byte, 32 -> 128-byte swizzle)
-static_assert(BK == 16 || BK == 32, "k-block is one 64-byte or one 128-byte swizzle row");
+constexpr int BN = 128;                 // output columns per pass over a row panel (N <= 256: one or two passes)
+constexpr int BK = 32;                  // fp32 per k-block: 128 bytes = one 128-byte swizzle row
 constexpr int kRowBytes = BK * 4;
 constexpr int UMMA_K = 8;               // tf32 elements per tcgen05.mma
-constexpr int kStages = 64 / BK;        // 4 stages of 48 KB or 2 stages of 96 KB
+constexpr int kStages = 3;
 constexpr int kMaxN = 256;
-constexpr int kTmemCols = 512;          // two accumulators of up to 256 columns
-constexpr int kAccStride = 256;         // column offset of the second accumulator
-constexpr int A_TILE_BYTES = BM * kRowBytes;
-constexpr int B_TILE_BYTES = kMaxN * kRowBytes;  // reserved per piece
-constexpr int STAGE_BYTES = 2 * A_TILE_BYTES + 2 * B_TILE_BYTES;  // a_hi, a_lo, b_hi, b_lo
+constexpr int kTmemCols = 512;          // two buffers of (main, small) accumulators, 128 columns each
+constexpr int kAccStride = 256;         // column offset of the second buffer
+constexpr int kSmallOffset = 128;       // column offset of a buffer's small-terms accumulator
+constexpr int A_TILE_BYTES = BM * kRowBytes;     // 16 KB
+constexpr int B_TILE_BYTES = BN * kRowBytes;     // 16 KB per piece
+constexpr int STAGE_BYTES = 2 * A_TILE_BYTES + 2 * B_TILE_BYTES;  // a (loaded), a_lo, b_hi, b_lo: 64 KB
 constexpr int kEpiPad = 33;
 constexpr int kEpiTile = 32 * 32 * 4;   // one 32 x 32 fp32 output block
 constexpr int EPI_BYTES = 4 * 2 * kEpiTile;  // per epilogue warp: two blocks (TMA store double buffer)
@@ -196,16 +194,16 @@ __device__ __forceinline__ float lo_of_truncated(float x) {
     return (fabsf(hi) <= 3.402823466e38f) ? tf32_rna(rest) : 0.0f;
 }
 
-// Shared-memory matrix descriptor of a K-major tile whose rows are one swizzle row (64 or 128 bytes,
-// what TMA writes for a {BK fp32, rows} box): start address, stride between 8-row groups,
-// descriptor version 1 (sm_100), layout type 2 (128-byte swizzle) or 4 (64-byte swizzle).
+// Shared-memory matrix descriptor of a K-major tile whose rows are 128 bytes, 128-byte-swizzled (what
+// TMA writes for a {32 fp32, rows} box): start address, 8-row group stride 1024 bytes, descriptor
+// version 1 (sm_100), layout type 2 (128-byte swizzle).
 __device__ __forceinline__ uint64_t make_smem_desc(uint32_t smem_addr) {
     uint64_t d = 0;
     d |= (uint64_t)((smem_addr & 0x3FFFFu) >> 4);       // bits [0,14)
     d |= (uint64_t)1 << 16;                              // leading byte offset (unused for swizzled K-major)
-    d |= (uint64_t)((8 * kRowBytes) >> 4) << 32;         // stride byte offset
+    d |= (uint64_t)(1024 >> 4) << 32;                    // stride byte offset
     d |= (uint64_t)1 << 46;                              // descriptor version
-    d |= (uint64_t)(BK == 32 ? 2 : 4) << 61;             // swizzle mode
+    d |= (uint64_t)2 << 61;                              // SWIZZLE_128B
     return d;
 }
 
@@ -225,7 +223,7 @@ struct GemmParams {
     const float *bias;
     int *status;
     int64_t M, ldc;
-    int N, n_pad, K, accumulate, num_tiles, tma_store;
+    int N, n_pad, K, accumulate, num_tiles, tma_store, b_box_rows;
 };
 
 enum : int {
@@ -261,7 +259,8 @@ gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int KB = (p.K + BK - 1) / BK;
-    const uint32_t b_bytes = (uint32_t)p.n_pad * kRowBytes;
+    const int passes = (p.n_pad + BN - 1) / BN;  // column passes over a row panel: 1 or 2
+    const uint32_t b_bytes = (uint32_t)p.b_box_rows * kRowBytes;
     for (int i = threadIdx.x; i < kMaxN; i += kThreads) bias_s[i] = (p.bias != nullptr && i < p.N) ? p.bias[i] : 0.0f;
 
     if (threadIdx.x == 0) {
@@ -299,22 +298,24 @@ gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
                 const int next = tile + (int)gridDim.x;
                 if (next < p.num_tiles)
                     for (int kb = 0; kb < KB; ++kb) tma_prefetch_2d(&map_a, kb * BK, next * BM);
-                for (int kb = 0; kb < KB; ++kb, ++it) {
-                    const int s = it % kStages;
-                    const uint32_t ph = (it / kStages) & 1u;
-                    if (!mbar_wait(bar_empty(s), ph ^ 1u, abort_flag, p.status, kErrWaitEmpty)) {
-                        ok = false;
-                        break;
+                for (int h = 0; h < passes && ok; ++h) {  // the second pass finds the row panel in L2
+                    for (int kb = 0; kb < KB; ++kb, ++it) {
+                        const int s = it % kStages;
+                        const uint32_t ph = (it / kStages) & 1u;
+                        if (!mbar_wait(bar_empty(s), ph ^ 1u, abort_flag, p.status, kErrWaitEmpty)) {
+                            ok = false;
+                            break;
+                        }
+                        const uint32_t sa = smem_u32(stage_base + s * STAGE_BYTES);
+                        mbar_arrive_expect_tx(bar_full(s), (uint32_t)A_TILE_BYTES + 2u * b_bytes);
+                        tma_load_2d(sa, &map_a, bar_full(s), kb * BK, m0);
+                        tma_load_2d(sa + 2 * A_TILE_BYTES, &map_bhi, bar_full(s), kb * BK, h * BN);
+                        tma_load_2d(sa + 2 * A_TILE_BYTES + B_TILE_BYTES, &map_blo, bar_full(s), kb * BK, h * BN);
                     }
-                    const uint32_t sa = smem_u32(stage_base + s * STAGE_BYTES);
-                    mbar_arrive_expect_tx(bar_full(s), (uint32_t)A_TILE_BYTES + 2u * b_bytes);
-                    tma_load_2d(sa, &map_a, bar_full(s), kb * BK, m0);
-                    tma_load_2d(sa + 2 * A_TILE_BYTES, &map_bhi, bar_full(s), kb * BK, 0);
-                    tma_load_2d(sa + 2 * A_TILE_BYTES + B_TILE_BYTES, &map_blo, bar_full(s), kb * BK, 0);
                 }
             }
             if (!ok) {
-                // copies of the last two k-blocks issued may still be landing: wait for them, bounded
+                // copies of the last k-blocks issued may still be landing: wait for them, bounded
                 for (uint32_t back = 1; back <= (uint32_t)kStages && back <= it; ++back) {
                     const uint32_t j = it - back;
                     const unsigned long long t0 = globaltimer_ns();
@@ -330,50 +331,58 @@ gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
     } else if (warp == 1) {
         // ---------------- MMA issuer ----------------
         if (lane == 0) {
-            const uint32_t idesc = make_instr_desc(p.n_pad);
             uint32_t it = 0, t = 0;
             bool ok = true;
-            for (int tile = blockIdx.x; tile < p.num_tiles && ok; tile += gridDim.x, ++t) {
-                const int b = t & 1;
-                if (!mbar_wait(bar_acc_empty(b), ((t >> 1) & 1u) ^ 1u, abort_flag, p.status, kErrWaitAccFree)) {
-                    ok = false;
-                    break;
-                }
-                tc_fence_after();
-                const uint32_t d_tmem = tmem_base + (uint32_t)(b * kAccStride);
-                for (int kb = 0; kb < KB; ++kb, ++it) {
-                    const int s = it % kStages;
-                    const uint32_t ph = (it / kStages) & 1u;
-                    if (!mbar_wait(bar_full(s), ph, abort_flag, p.status, kErrWaitFull)) {
+            for (int tile = blockIdx.x; tile < p.num_tiles && ok; tile += gridDim.x) {
+                for (int h = 0; h < passes && ok; ++h, ++t) {
+                    const int b = t & 1;
+                    const int n_cols = min(BN, p.n_pad - h * BN);  // multiple of 16
+                    const uint32_t idesc = make_instr_desc(n_cols);
+                    if (!mbar_wait(bar_acc_empty(b), ((t >> 1) & 1u) ^ 1u, abort_flag, p.status, kErrWaitAccFree)) {
                         ok = false;
                         break;
                     }
                     tc_fence_after();
-                    const uint32_t sa = smem_u32(stage_base + s * STAGE_BYTES);
-                    const uint64_t a_hi = make_smem_desc(sa);  // the panel as loaded
-                    const uint64_t a_lo = make_smem_desc(sa + A_TILE_BYTES);
-                    const uint64_t b_hi = make_smem_desc(sa + 2 * A_TILE_BYTES);
-                    const uint64_t b_lo = make_smem_desc(sa + 2 * A_TILE_BYTES + B_TILE_BYTES);
-                    // the two products of the loaded panel start at once; k advances 32 bytes inside the swizzled row
+                    // the main product and the two small ones have accumulators of their own: the accumulator
+                    // rounds toward zero once per MMA, and the small terms would otherwise triple the number of
+                    // roundings at full magnitude
+                    const uint32_t d_main = tmem_base + (uint32_t)(b * kAccStride);
+                    const uint32_t d_small = d_main + (uint32_t)kSmallOffset;
+                    for (int kb = 0; kb < KB; ++kb, ++it) {
+                        const int s = it % kStages;
+                        const uint32_t ph = (it / kStages) & 1u;
+                        if (!mbar_wait(bar_full(s), ph, abort_flag, p.status, kErrWaitFull)) {
+                            ok = false;
+                            break;
+                        }
+                        tc_fence_after();
+                        const uint32_t sa = smem_u32(stage_base + s * STAGE_BYTES);
+                        const uint64_t a_hi = make_smem_desc(sa);  // the panel as loaded
+                        const uint64_t a_lo = make_smem_desc(sa + A_TILE_BYTES);
+                        const uint64_t b_hi = make_smem_desc(sa + 2 * A_TILE_BYTES);
+                        const uint64_t b_lo = make_smem_desc(sa + 2 * A_TILE_BYTES + B_TILE_BYTES);
+                        // the two products of the loaded panel start at once; k advances 32 bytes inside the swizzled row
 #pragma unroll
-                    for (int k = 0; k < BK / UMMA_K; ++k)
-                        tc_mma_tf32(d_tmem, a_hi + (uint64_t)(2 * k), b_lo + (uint64_t)(2 * k), idesc,
-                                    (kb > 0 || k > 0) ? 1u : 0u);
+                        for (int k = 0; k < BK / UMMA_K; ++k)
+                            tc_mma_tf32(d_small, a_hi + (uint64_t)(2 * k), b_lo + (uint64_t)(2 * k), idesc,
+                                        (kb > 0 || k > 0) ? 1u : 0u);
 #pragma unroll
-                    for (int k = 0; k < BK / UMMA_K; ++k)
-                        tc_mma_tf32(d_tmem, a_hi + (uint64_t)(2 * k), b_hi + (uint64_t)(2 * k), idesc, 1u);
-                    // the remainder panel is ready a little later
-                    if (!mbar_wait(bar_split(s), ph, abort_flag, p.status, kErrWaitSplit)) {
-                        ok = false;
-                        break;
+                        for (int k = 0; k < BK / UMMA_K; ++k)
+                            tc_mma_tf32(d_main, a_hi + (uint64_t)(2 * k), b_hi + (uint64_t)(2 * k), idesc,
+                                        (kb > 0 || k > 0) ? 1u : 0u);
+                        // the remainder panel is ready a little later
+                        if (!mbar_wait(bar_split(s), ph, abort_flag, p.status, kErrWaitSplit)) {
+                            ok = false;
+                            break;
+                        }
+                        tc_fence_after();
+#pragma unroll
+                        for (int k = 0; k < BK / UMMA_K; ++k)
+                            tc_mma_tf32(d_small, a_lo + (uint64_t)(2 * k), b_hi + (uint64_t)(2 * k), idesc, 1u);
+                        tc_commit(bar_empty(s));  // the stage is free once these MMAs have read it
                     }
-                    tc_fence_after();
-#pragma unroll
-                    for (int k = 0; k < BK / UMMA_K; ++k)
-                        tc_mma_tf32(d_tmem, a_lo + (uint64_t)(2 * k), b_hi + (uint64_t)(2 * k), idesc, 1u);
-                    tc_commit(bar_empty(s));  // the stage is free once these MMAs have read it
+                    if (ok) tc_commit(bar_acc_full(b));
                 }
-                if (ok) tc_commit(bar_acc_full(b));
             }
             if (!ok) {
                 // MMAs already issued still read shared memory and write tensor memory: drain, bounded
@@ -393,7 +402,7 @@ gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
         uint32_t it = 0;
         bool ok = true;
         for (int tile = blockIdx.x; tile < p.num_tiles && ok; tile += gridDim.x) {
-            for (int kb = 0; kb < KB; ++kb, ++it) {
+            for (int kb = 0; kb < passes * KB; ++kb, ++it) {
                 const int s = it % kStages;
                 const uint32_t ph = (it / kStages) & 1u;
                 if (!mbar_wait(bar_full(s), ph, abort_flag, p.status, kErrWaitFull)) {
@@ -424,68 +433,78 @@ gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
         float *tr = reinterpret_cast<float *>(my_epi);
         uint32_t t = 0, nstore = 0;
         bool ok = true;
-        for (int tile = blockIdx.x; tile < p.num_tiles && ok; tile += gridDim.x, ++t) {
-            const int b = t & 1;
-            // warp-uniform outcome: the tensor-memory loads below are warp-collective
-            if (!__all_sync(kFullMask, mbar_wait(bar_acc_full(b), (t >> 1) & 1u, abort_flag, p.status, kErrWaitAccFull))) {
-                ok = false;
-                break;
-            }
-            tc_fence_after();
+        for (int tile = blockIdx.x; tile < p.num_tiles && ok; tile += gridDim.x) {
             const int64_t row0 = (int64_t)tile * BM + q * 32;
-            for (int c0 = 0; c0 < p.N; c0 += 32) {
-                uint32_t r[32];
-                tc_ld_32x32(tmem_base + (uint32_t)(b * kAccStride + c0) + ((uint32_t)(q * 32) << 16), r);
-                if (p.tma_store) {
-                    // this thread's row of the 32 x 32 block goes to shared memory in the 128-byte-swizzled
-                    // layout of the output tensor map (16-byte chunk j of row r sits at chunk j ^ (r & 7)),
-                    // then one lane hands the block to TMA: plain store, or add for accumulate
-                    uint8_t *buf = my_epi + (nstore & 1u) * kEpiTile;
-                    if (lane == 0) tma_store_wait_read<1>();  // the store that last read this buffer is done with it
-                    __syncwarp();
-#pragma unroll
-                    for (int j = 0; j < 8; ++j) {
-                        float4 v;
-                        v.x = __uint_as_float(r[4 * j + 0]) + bias_s[c0 + 4 * j + 0];
-                        v.y = __uint_as_float(r[4 * j + 1]) + bias_s[c0 + 4 * j + 1];
-                        v.z = __uint_as_float(r[4 * j + 2]) + bias_s[c0 + 4 * j + 2];
-                        v.w = __uint_as_float(r[4 * j + 3]) + bias_s[c0 + 4 * j + 3];
-                        *reinterpret_cast<float4 *>(buf + lane * 128 + ((j ^ (lane & 7)) << 4)) = v;
-                    }
-                    fence_generic_to_async_smem();
-                    __syncwarp();
-                    if (lane == 0) {
-                        if (p.accumulate)
-                            tma_reduce_add_2d(&map_c, smem_u32(buf), c0, (int)row0);
-                        else
-                            tma_store_2d(&map_c, smem_u32(buf), c0, (int)row0);
-                        tma_store_commit();
-                    }
-                    ++nstore;
-                    continue;
+            for (int h = 0; h < passes && ok; ++h, ++t) {
+                const int b = t & 1;
+                // warp-uniform outcome: the tensor-memory loads below are warp-collective
+                if (!__all_sync(kFullMask,
+                                mbar_wait(bar_acc_full(b), (t >> 1) & 1u, abort_flag, p.status, kErrWaitAccFull))) {
+                    ok = false;
+                    break;
                 }
-                // output rows that TMA cannot address (stride not a multiple of 16 bytes): transpose the block
-                // through shared memory and store row segments with plain coalesced stores
+                tc_fence_after();
+                const int col_base = h * BN;
+                const int n_valid = min(BN, p.N - col_base);
+                const uint32_t t_main = tmem_base + (uint32_t)(b * kAccStride) + ((uint32_t)(q * 32) << 16);
+                for (int c0 = 0; c0 < n_valid; c0 += 32) {
+                    uint32_t r[32], rs[32];
+                    tc_ld_32x32(t_main + (uint32_t)c0, r);
+                    tc_ld_32x32(t_main + (uint32_t)(kSmallOffset + c0), rs);
+                    float v[32];
 #pragma unroll
-                for (int j = 0; j < 32; ++j) tr[lane * kEpiPad + j] = __uint_as_float(r[j]);
-                __syncwarp();
-                const int col = c0 + lane;
-                if (col < p.N) {
-                    const float bv = bias_s[col];
+                    for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]) + __uint_as_float(rs[j]);
+                    if (p.tma_store) {
+                        // this thread's row of the 32 x 32 block goes to shared memory in the 128-byte-swizzled
+                        // layout of the output tensor map (16-byte chunk j of row r sits at chunk j ^ (r & 7)),
+                        // then one lane hands the block to TMA: plain store, or add for accumulate
+                        uint8_t *buf = my_epi + (nstore & 1u) * kEpiTile;
+                        if (lane == 0) tma_store_wait_read<1>();  // the store that last read this buffer is done
+                        __syncwarp();
+#pragma unroll
+                        for (int j = 0; j < 8; ++j) {
+                            float4 o;
+                            o.x = v[4 * j + 0] + bias_s[col_base + c0 + 4 * j + 0];
+                            o.y = v[4 * j + 1] + bias_s[col_base + c0 + 4 * j + 1];
+                            o.z = v[4 * j + 2] + bias_s[col_base + c0 + 4 * j + 2];
+                            o.w = v[4 * j + 3] + bias_s[col_base + c0 + 4 * j + 3];
+                            *reinterpret_cast<float4 *>(buf + lane * 128 + ((j ^ (lane & 7)) << 4)) = o;
+                        }
+                        fence_generic_to_async_smem();
+                        __syncwarp();
+                        if (lane == 0) {
+                            if (p.accumulate)
+                                tma_reduce_add_2d(&map_c, smem_u32(buf), col_base + c0, (int)row0);
+                            else
+                                tma_store_2d(&map_c, smem_u32(buf), col_base + c0, (int)row0);
+                            tma_store_commit();
+                        }
+                        ++nstore;
+                        continue;
+                    }
+                    // output rows that TMA cannot address (stride not a multiple of 16 bytes): transpose the
+                    // block through shared memory and store row segments with plain coalesced stores
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) tr[lane * kEpiPad + j] = v[j];
+                    __syncwarp();
+                    const int col = col_base + c0 + lane;
+                    if (col < p.N) {
+                        const float bv = bias_s[col];
 #pragma unroll 4
-                    for (int rr = 0; rr < 32; ++rr) {
-                        const int64_t row = row0 + rr;
-                        if (row >= p.M) break;
-                        float v = tr[rr * kEpiPad + lane] + bv;
-                        float *dst = p.C + row * p.ldc + col;
-                        if (p.accumulate) v += *dst;
-                        *dst = v;
+                        for (int rr = 0; rr < 32; ++rr) {
+                            const int64_t row = row0 + rr;
+                            if (row >= p.M) break;
+                            float o = tr[rr * kEpiPad + lane] + bv;
+                            float *dst = p.C + row * p.ldc + col;
+                            if (p.accumulate) o += *dst;
+                            *dst = o;
+                        }
                     }
+                    __syncwarp();
                 }
-                __syncwarp();
+                tc_fence_before();
+                mbar_arrive(bar_acc_empty(b));
             }
-            tc_fence_before();
-            mbar_arrive(bar_acc_empty(b));
         }
         if (p.tma_store && lane == 0) tma_store_wait_all();  // shared memory stays valid until TMA has read it
     }
@@ -886,8 +905,9 @@ extern "C" int gnnagg_dense_tf32x3_f32(const float *A, int64_t lda, const float 
     const bool tma_store = aligned16(C) && (ldc % 4) == 0;
     CUtensorMap map_a, map_bhi, map_blo, map_c;
     int rc = make_map(&map_a, A, M, K, lda, BK, BM);
-    if (rc == GNNAGG_OK) rc = make_map(&map_bhi, w_hi, N, K, ldw, BK, n_pad);
-    if (rc == GNNAGG_OK) rc = make_map(&map_blo, w_lo, N, K, ldw, BK, n_pad);
+    const int b_box_rows = n_pad < BN ? n_pad : BN;  // weight rows per pass (rows past N read as zero)
+    if (rc == GNNAGG_OK) rc = make_map(&map_bhi, w_hi, N, K, ldw, BK, b_box_rows);
+    if (rc == GNNAGG_OK) rc = make_map(&map_blo, w_lo, N, K, ldw, BK, b_box_rows);
     if (rc == GNNAGG_OK) {
         if (tma_store)
             rc = make_map(&map_c, C, M, N, ldc, 32, 32);
@@ -916,6 +936,7 @@ extern "C" int gnnagg_dense_tf32x3_f32(const float *A, int64_t lda, const float 
     p.accumulate = accumulate;
     p.num_tiles = (int)((M + BM - 1) / BM);
     p.tma_store = tma_store ? 1 : 0;
+    p.b_box_rows = b_box_rows;
     const int grid = p.num_tiles < kNumSMs ? p.num_tiles : kNumSMs;
     gemm_tf32x3_kernel<<<grid, kThreads, SMEM_BYTES, st>>>(map_a, map_bhi, map_blo, map_c, p);
     return check_launch("gemm_tf32x3_kernel");

@@ -20,7 +20,7 @@ from . import _lib
 
 MAX_N = 256
 # "tf32x3": use the tensor-core kernel wherever `supported()`; "cublas": plain torch fp32 matmul.
-MODE = os.environ.get("GNNAGG_DENSE", "cublas")
+MODE = os.environ.get("GNNAGG_DENSE", "tf32x3")
 
 _workspaces = {}
 

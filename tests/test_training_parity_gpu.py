@@ -174,7 +174,7 @@ def test_loss_curve_against_reference_run(cuda_lib, tmp_path, path, dense_mode, 
     import torch.multiprocessing as mp
 
     monkeypatch.setenv("GNNAGG_DENSE", dense_mode)  # read by the spawned ranks at import
-    tol = 1e-4 if dense_mode == "cublas" else 1e-3
+    tol = 1e-4
     g = np.load(path)
     P = sum(1 for k in g.files if k.endswith("_losses"))
     port = 29700 + (os.getpid() % 200)
