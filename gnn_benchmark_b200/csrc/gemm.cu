@@ -33,18 +33,20 @@ namespace gnnagg {
 namespace {
 
 constexpr int BM = 128;                 // rows of A per tile = UMMA M = TMEM lanes
-constexpr int BN = 128;                 // output columns per pass over a row panel (N <= 256: one or two passes)
+constexpr int BN = 128;                 // output columns per accumulator pair (N <= 256: one or two column halves)
 constexpr int BK = 32;                  // fp32 per k-block: 128 bytes = one 128-byte swizzle row
 constexpr int kRowBytes = BK * 4;
 constexpr int UMMA_K = 8;               // tf32 elements per tcgen05.mma
-constexpr int kStages = 3;
+constexpr int kStages = 2;
 constexpr int kMaxN = 256;
-constexpr int kTmemCols = 512;          // two buffers of (main, small) accumulators, 128 columns each
-constexpr int kAccStride = 256;         // column offset of the second buffer
+constexpr int kTmemCols = 512;          // (main, small) accumulator pairs of 128 columns each: two column halves of
+                                        // one row panel, or two row panels in flight when N <= 128
+constexpr int kAccStride = 256;         // column offset of the second pair
 constexpr int kSmallOffset = 128;       // column offset of a buffer's small-terms accumulator
 constexpr int A_TILE_BYTES = BM * kRowBytes;     // 16 KB
-constexpr int B_TILE_BYTES = BN * kRowBytes;     // 16 KB per piece
-constexpr int STAGE_BYTES = 2 * A_TILE_BYTES + 2 * B_TILE_BYTES;  // a (loaded), a_lo, b_hi, b_lo: 64 KB
+constexpr int B_TILE_BYTES = kMaxN * kRowBytes;  // 32 KB per piece (all N rows of the weight)
+constexpr int B_HALF_BYTES = BN * kRowBytes;     // the rows of one column half
+constexpr int STAGE_BYTES = 2 * A_TILE_BYTES + 2 * B_TILE_BYTES;  // a (loaded), a_lo, b_hi, b_lo: 96 KB
 constexpr int kEpiPad = 33;
 constexpr int kEpiTile = 32 * 32 * 4;   // one 32 x 32 fp32 output block
 constexpr int EPI_BYTES = 4 * 2 * kEpiTile;  // per epilogue warp: two blocks (TMA store double buffer)
@@ -259,7 +261,8 @@ gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int KB = (p.K + BK - 1) / BK;
-    const int passes = (p.n_pad + BN - 1) / BN;  // column passes over a row panel: 1 or 2
+    const int halves = (p.n_pad + BN - 1) / BN;  // column halves of a row panel: 1 or 2
+    const int nbuf = halves == 1 ? 2 : 1;         // row panels whose accumulators fit in tensor memory at once
     const uint32_t b_bytes = (uint32_t)p.b_box_rows * kRowBytes;
     for (int i = threadIdx.x; i < kMaxN; i += kThreads) bias_s[i] = (p.bias != nullptr && i < p.N) ? p.bias[i] : 0.0f;
 
@@ -298,20 +301,18 @@ gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
                 const int next = tile + (int)gridDim.x;
                 if (next < p.num_tiles)
                     for (int kb = 0; kb < KB; ++kb) tma_prefetch_2d(&map_a, kb * BK, next * BM);
-                for (int h = 0; h < passes && ok; ++h) {  // the second pass finds the row panel in L2
-                    for (int kb = 0; kb < KB; ++kb, ++it) {
-                        const int s = it % kStages;
-                        const uint32_t ph = (it / kStages) & 1u;
-                        if (!mbar_wait(bar_empty(s), ph ^ 1u, abort_flag, p.status, kErrWaitEmpty)) {
-                            ok = false;
-                            break;
-                        }
-                        const uint32_t sa = smem_u32(stage_base + s * STAGE_BYTES);
-                        mbar_arrive_expect_tx(bar_full(s), (uint32_t)A_TILE_BYTES + 2u * b_bytes);
-                        tma_load_2d(sa, &map_a, bar_full(s), kb * BK, m0);
-                        tma_load_2d(sa + 2 * A_TILE_BYTES, &map_bhi, bar_full(s), kb * BK, h * BN);
-                        tma_load_2d(sa + 2 * A_TILE_BYTES + B_TILE_BYTES, &map_blo, bar_full(s), kb * BK, h * BN);
+                for (int kb = 0; kb < KB; ++kb, ++it) {
+                    const int s = it % kStages;
+                    const uint32_t ph = (it / kStages) & 1u;
+                    if (!mbar_wait(bar_empty(s), ph ^ 1u, abort_flag, p.status, kErrWaitEmpty)) {
+                        ok = false;
+                        break;
                     }
+                    const uint32_t sa = smem_u32(stage_base + s * STAGE_BYTES);
+                    mbar_arrive_expect_tx(bar_full(s), (uint32_t)A_TILE_BYTES + 2u * b_bytes);
+                    tma_load_2d(sa, &map_a, bar_full(s), kb * BK, m0);
+                    tma_load_2d(sa + 2 * A_TILE_BYTES, &map_bhi, bar_full(s), kb * BK, 0);
+                    tma_load_2d(sa + 2 * A_TILE_BYTES + B_TILE_BYTES, &map_blo, bar_full(s), kb * BK, 0);
                 }
             }
             if (!ok) {
@@ -333,56 +334,62 @@ gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
         if (lane == 0) {
             uint32_t it = 0, t = 0;
             bool ok = true;
-            for (int tile = blockIdx.x; tile < p.num_tiles && ok; tile += gridDim.x) {
-                for (int h = 0; h < passes && ok; ++h, ++t) {
-                    const int b = t & 1;
-                    const int n_cols = min(BN, p.n_pad - h * BN);  // multiple of 16
-                    const uint32_t idesc = make_instr_desc(n_cols);
-                    if (!mbar_wait(bar_acc_empty(b), ((t >> 1) & 1u) ^ 1u, abort_flag, p.status, kErrWaitAccFree)) {
+            uint32_t idesc[2];
+            for (int h = 0; h < 2; ++h) idesc[h] = make_instr_desc(max(16, min(BN, p.n_pad - h * BN)));
+            for (int tile = blockIdx.x; tile < p.num_tiles && ok; tile += gridDim.x, ++t) {
+                const int b = (int)(t % (uint32_t)nbuf);
+                if (!mbar_wait(bar_acc_empty(b), ((t / (uint32_t)nbuf) & 1u) ^ 1u, abort_flag, p.status,
+                               kErrWaitAccFree)) {
+                    ok = false;
+                    break;
+                }
+                tc_fence_after();
+                // the main product and the two small ones have accumulators of their own: the accumulator
+                // rounds toward zero once per MMA, and the small terms would otherwise triple the number of
+                // roundings at full magnitude.  Column half h of row-panel buffer b sits at pair (b + h).
+                for (int kb = 0; kb < KB; ++kb, ++it) {
+                    const int s = it % kStages;
+                    const uint32_t ph = (it / kStages) & 1u;
+                    if (!mbar_wait(bar_full(s), ph, abort_flag, p.status, kErrWaitFull)) {
                         ok = false;
                         break;
                     }
                     tc_fence_after();
-                    // the main product and the two small ones have accumulators of their own: the accumulator
-                    // rounds toward zero once per MMA, and the small terms would otherwise triple the number of
-                    // roundings at full magnitude
-                    const uint32_t d_main = tmem_base + (uint32_t)(b * kAccStride);
-                    const uint32_t d_small = d_main + (uint32_t)kSmallOffset;
-                    for (int kb = 0; kb < KB; ++kb, ++it) {
-                        const int s = it % kStages;
-                        const uint32_t ph = (it / kStages) & 1u;
-                        if (!mbar_wait(bar_full(s), ph, abort_flag, p.status, kErrWaitFull)) {
-                            ok = false;
-                            break;
-                        }
-                        tc_fence_after();
-                        const uint32_t sa = smem_u32(stage_base + s * STAGE_BYTES);
-                        const uint64_t a_hi = make_smem_desc(sa);  // the panel as loaded
-                        const uint64_t a_lo = make_smem_desc(sa + A_TILE_BYTES);
-                        const uint64_t b_hi = make_smem_desc(sa + 2 * A_TILE_BYTES);
-                        const uint64_t b_lo = make_smem_desc(sa + 2 * A_TILE_BYTES + B_TILE_BYTES);
-                        // the two products of the loaded panel start at once; k advances 32 bytes inside the swizzled row
+                    const uint32_t sa = smem_u32(stage_base + s * STAGE_BYTES);
+                    const uint64_t a_hi = make_smem_desc(sa);  // the panel as loaded
+                    const uint64_t a_lo = make_smem_desc(sa + A_TILE_BYTES);
+                    const uint32_t first = (kb > 0) ? 1u : 0u;
+                    // the two products of the loaded panel start at once; k advances 32 bytes inside the swizzled row
+                    for (int h = 0; h < halves; ++h) {
+                        const uint32_t d_main = tmem_base + (uint32_t)((b + h) * kAccStride);
+                        const uint32_t d_small = d_main + (uint32_t)kSmallOffset;
+                        const uint64_t b_hi = make_smem_desc(sa + 2 * A_TILE_BYTES + h * B_HALF_BYTES);
+                        const uint64_t b_lo = make_smem_desc(sa + 2 * A_TILE_BYTES + B_TILE_BYTES + h * B_HALF_BYTES);
 #pragma unroll
                         for (int k = 0; k < BK / UMMA_K; ++k)
-                            tc_mma_tf32(d_small, a_hi + (uint64_t)(2 * k), b_lo + (uint64_t)(2 * k), idesc,
-                                        (kb > 0 || k > 0) ? 1u : 0u);
+                            tc_mma_tf32(d_small, a_hi + (uint64_t)(2 * k), b_lo + (uint64_t)(2 * k), idesc[h],
+                                        k > 0 ? 1u : first);
 #pragma unroll
                         for (int k = 0; k < BK / UMMA_K; ++k)
-                            tc_mma_tf32(d_main, a_hi + (uint64_t)(2 * k), b_hi + (uint64_t)(2 * k), idesc,
-                                        (kb > 0 || k > 0) ? 1u : 0u);
-                        // the remainder panel is ready a little later
-                        if (!mbar_wait(bar_split(s), ph, abort_flag, p.status, kErrWaitSplit)) {
-                            ok = false;
-                            break;
-                        }
-                        tc_fence_after();
-#pragma unroll
-                        for (int k = 0; k < BK / UMMA_K; ++k)
-                            tc_mma_tf32(d_small, a_lo + (uint64_t)(2 * k), b_hi + (uint64_t)(2 * k), idesc, 1u);
-                        tc_commit(bar_empty(s));  // the stage is free once these MMAs have read it
+                            tc_mma_tf32(d_main, a_hi + (uint64_t)(2 * k), b_hi + (uint64_t)(2 * k), idesc[h],
+                                        k > 0 ? 1u : first);
                     }
-                    if (ok) tc_commit(bar_acc_full(b));
+                    // the remainder panel is ready a little later
+                    if (!mbar_wait(bar_split(s), ph, abort_flag, p.status, kErrWaitSplit)) {
+                        ok = false;
+                        break;
+                    }
+                    tc_fence_after();
+                    for (int h = 0; h < halves; ++h) {
+                        const uint32_t d_small = tmem_base + (uint32_t)((b + h) * kAccStride + kSmallOffset);
+                        const uint64_t b_hi = make_smem_desc(sa + 2 * A_TILE_BYTES + h * B_HALF_BYTES);
+#pragma unroll
+                        for (int k = 0; k < BK / UMMA_K; ++k)
+                            tc_mma_tf32(d_small, a_lo + (uint64_t)(2 * k), b_hi + (uint64_t)(2 * k), idesc[h], 1u);
+                    }
+                    tc_commit(bar_empty(s));  // the stage is free once these MMAs have read it
                 }
+                if (ok) tc_commit(bar_acc_full(b));
             }
             if (!ok) {
                 // MMAs already issued still read shared memory and write tensor memory: drain, bounded
@@ -402,7 +409,7 @@ gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
         uint32_t it = 0;
         bool ok = true;
         for (int tile = blockIdx.x; tile < p.num_tiles && ok; tile += gridDim.x) {
-            for (int kb = 0; kb < passes * KB; ++kb, ++it) {
+            for (int kb = 0; kb < KB; ++kb, ++it) {
                 const int s = it % kStages;
                 const uint32_t ph = (it / kStages) & 1u;
                 if (!mbar_wait(bar_full(s), ph, abort_flag, p.status, kErrWaitFull)) {
@@ -433,20 +440,20 @@ gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
         float *tr = reinterpret_cast<float *>(my_epi);
         uint32_t t = 0, nstore = 0;
         bool ok = true;
-        for (int tile = blockIdx.x; tile < p.num_tiles && ok; tile += gridDim.x) {
+        for (int tile = blockIdx.x; tile < p.num_tiles && ok; tile += gridDim.x, ++t) {
             const int64_t row0 = (int64_t)tile * BM + q * 32;
-            for (int h = 0; h < passes && ok; ++h, ++t) {
-                const int b = t & 1;
-                // warp-uniform outcome: the tensor-memory loads below are warp-collective
-                if (!__all_sync(kFullMask,
-                                mbar_wait(bar_acc_full(b), (t >> 1) & 1u, abort_flag, p.status, kErrWaitAccFull))) {
-                    ok = false;
-                    break;
-                }
-                tc_fence_after();
+            const int b = (int)(t % (uint32_t)nbuf);
+            // warp-uniform outcome: the tensor-memory loads below are warp-collective
+            if (!__all_sync(kFullMask, mbar_wait(bar_acc_full(b), (t / (uint32_t)nbuf) & 1u, abort_flag, p.status,
+                                                 kErrWaitAccFull))) {
+                ok = false;
+                break;
+            }
+            tc_fence_after();
+            for (int h = 0; h < halves; ++h) {
                 const int col_base = h * BN;
                 const int n_valid = min(BN, p.N - col_base);
-                const uint32_t t_main = tmem_base + (uint32_t)(b * kAccStride) + ((uint32_t)(q * 32) << 16);
+                const uint32_t t_main = tmem_base + (uint32_t)((b + h) * kAccStride) + ((uint32_t)(q * 32) << 16);
                 for (int c0 = 0; c0 < n_valid; c0 += 32) {
                     uint32_t r[32], rs[32];
                     tc_ld_32x32(t_main + (uint32_t)c0, r);
@@ -502,9 +509,9 @@ gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
                     }
                     __syncwarp();
                 }
-                tc_fence_before();
-                mbar_arrive(bar_acc_empty(b));
             }
+            tc_fence_before();
+            mbar_arrive(bar_acc_empty(b));
         }
         if (p.tma_store && lane == 0) tma_store_wait_all();  // shared memory stays valid until TMA has read it
     }
@@ -905,7 +912,7 @@ extern "C" int gnnagg_dense_tf32x3_f32(const float *A, int64_t lda, const float 
     const bool tma_store = aligned16(C) && (ldc % 4) == 0;
     CUtensorMap map_a, map_bhi, map_blo, map_c;
     int rc = make_map(&map_a, A, M, K, lda, BK, BM);
-    const int b_box_rows = n_pad < BN ? n_pad : BN;  // weight rows per pass (rows past N read as zero)
+    const int b_box_rows = n_pad;  // all weight rows of a k-block in one box (rows past N read as zero)
     if (rc == GNNAGG_OK) rc = make_map(&map_bhi, w_hi, N, K, ldw, BK, b_box_rows);
     if (rc == GNNAGG_OK) rc = make_map(&map_blo, w_lo, N, K, ldw, BK, b_box_rows);
     if (rc == GNNAGG_OK) {
