@@ -8,19 +8,23 @@
 // kernel into a caller-provided workspace (hi = tf32_rna(w), lo = tf32_rna(w - hi)).  The activation
 // panel is used as loaded for its "hi" products (the tensor core reads the upper 19 bits of an fp32
 // word, i.e. hi = x truncated); its remainder panel lo = tf32_rna(x - hi) is computed inside the GEMM,
-// in shared memory, while those products already run.  What limits the accuracy is the accumulator,
-// which rounds toward zero once per MMA: about 1e-6 of sum |a||b| at K = 256 (an fp32 FMA chain: 3e-7).
+// in shared memory, while those products already run.  The tensor-memory accumulator rounds toward
+// zero once per MMA, so the main product and the two small ones are kept in separate accumulators
+// (the small ones' rounding errors are 2^-11 of the main one's) and added in the epilogue: measured
+// error 3.7e-7 of sum |a||b| at K = 256 (an fp32 FMA chain: 3e-7; one shared accumulator: 1.3e-6).
 //
 // One persistent CTA per SM, 10 warps:
-//   warp 0      lane 0 issues the TMA loads (A raw, B_hi, B_lo per 32-wide k-block; two stages) and
+//   warp 0      lane 0 issues the TMA loads (A as stored, B_hi, B_lo per 32-wide k-block; two stages) and
 //               prefetches the next row panel of A into L2;
-//   warp 1      allocates tensor memory; lane 0 issues tcgen05.mma (128 x N x 8 per instruction) and
-//               the commits that free a stage / publish an accumulator;
+//   warp 1      allocates tensor memory; lane 0 issues tcgen05.mma (128 x 128 x 8 per instruction, one
+//               accumulator pair per 128 output columns) and the commits that free a stage / publish
+//               the accumulators of a row panel;
 //   warps 2-5   compute the remainder (lo) panel of a stage's A tile into a second buffer;
-//   warps 6-9   epilogue: tcgen05.ld of a finished accumulator (two of them in tensor memory, so the
-//               epilogue of one row panel runs under the MMAs of the next), bias add, 32 x 32 blocks
-//               through swizzled shared memory to TMA stores (TMA reduce-add for accumulate); output
-//               rows that TMA cannot address go through a shared-memory transpose and plain stores.
+//   warps 6-9   epilogue: tcgen05.ld of the finished accumulators, main + small, bias add, 32 x 32
+//               blocks through swizzled shared memory to TMA stores (TMA reduce-add for accumulate);
+//               output rows that TMA cannot address go through a shared-memory transpose and plain
+//               stores.  For N <= 128 two row panels fit in tensor memory and the epilogue of one runs
+//               under the MMAs of the next.
 // Every wait is bounded (about a second); on a time-out the kernel records a code in the status
 // word of the workspace, drains its own copies and MMAs, frees tensor memory and returns.
 #include <cuda.h>

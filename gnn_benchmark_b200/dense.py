@@ -19,7 +19,7 @@ import torch
 from . import _lib
 
 MAX_N = 256
-# "tf32x3": use the tensor-core kernel wherever `supported()`; "cublas": plain torch fp32 matmul.
+# "tf32x3" (default): the tensor-core kernels wherever `supported()`; "cublas": plain torch fp32 matmul.
 MODE = os.environ.get("GNNAGG_DENSE", "tf32x3")
 
 _workspaces = {}

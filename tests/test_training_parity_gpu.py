@@ -166,11 +166,9 @@ def test_gcn_configuration_1_against_reference_aggregator_run(cuda_lib, tmp_path
 @pytest.mark.parametrize("path", sorted(glob.glob(os.path.join(GOLD, "train_sage_*.npz"))),
                          ids=lambda p: os.path.basename(p)[6:-4])
 def test_loss_curve_against_reference_run(cuda_lib, tmp_path, path, dense_mode, monkeypatch):
-    """dense_mode "cublas": the layer's fp32 transforms on cuBLAS SIMT kernels (bar 1e-4);
-    "tf32x3": on the tensor-core kernels, whose accumulator rounds once per instruction and is a few
-    times less accurate than an fp32 FMA chain (about 1e-6 instead of 3e-7 of sum |a||b|): the first
-    ten epochs still agree to 1e-5, then the steeply falling curve amplifies the difference; bar 1e-3
-    (largest deviation measured: 3.3e-4, at epoch 17)."""
+    """dense_mode "tf32x3" (default): the layer's fp32 transforms and weight gradients on the tensor-core
+    kernels (three TF32 products per fp32 product, separate accumulators for the main and the small
+    products); "cublas": on torch's fp32 matmul.  Same bar for both: 1e-4 on every epoch."""
     import torch.multiprocessing as mp
 
     monkeypatch.setenv("GNNAGG_DENSE", dense_mode)  # read by the spawned ranks at import
