@@ -23,10 +23,8 @@ same line with "impl": "reference".
 import argparse
 import json
 import os
-import statistics
 import subprocess
 import sys
-import tempfile
 import time
 
 import torch

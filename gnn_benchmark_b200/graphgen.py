@@ -7,7 +7,7 @@ configurations copy; every generator takes an explicit seed and is pure torch, s
 gives the same graph on every rank.
 """
 import math
-from typing import List, Tuple
+from typing import Tuple
 
 import torch
 
