@@ -1,4 +1,4 @@
-"""Pieces shared by the benchmark drivers (bench.py at the repository root, bench_multi, bench_epoch):
+"""Pieces shared by the benchmark drivers beside this file (bench.py, bench_multi.py, bench_epoch.py):
 workload constants, roofline arithmetic, the nvidia-smi clock sampler and the three-stream host pipeline."""
 import json
 import os
@@ -9,17 +9,15 @@ import time
 
 import torch
 
-ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+ROOT = os.path.dirname(os.path.abspath(__file__))
 
-# the benchmark's widths; GNNAGG_BENCH_WIDTHS narrows them for a profiler capture of one kernel
-WIDTHS = tuple(int(w) for w in os.environ.get("GNNAGG_BENCH_WIDTHS", "32,128,256").split(","))
+# the benchmark workload; bench.py --scale / --widths choose a smaller case for a profiler capture and
+# are echoed into the line's `config`
+WIDTHS = (32, 128, 256)
 SEED = 20261127
-SCALE = int(os.environ.get("GNNAGG_BENCH_SCALE", "22"))  # 22 is the benchmark; smaller only for dry runs
+SCALE = 22
 EDGE_FACTOR = 16
 FALLBACK_HBM_GBS = 6650.0
-# dram__bytes_read.sum + dram__bytes_write.sum of ONE spmm_chunk_kernel launch on the default workload
-# (scale 22), from a one-pass ncu capture at full size (profiles/spmm_dram_traffic_rmat22.md); keyed by F
-NCU_DRAM_BYTES_PER_LAUNCH = {256: 76.16e9, 128: 31.27e9, 32: 4.73e9}
 
 
 def measured_peak_gbs():

@@ -9,8 +9,7 @@ import os
 import torch
 
 _PKG_DIR = os.path.dirname(os.path.abspath(__file__))
-# GNNAGG_LIB points at an alternative build of the same library (kernel tuning experiments)
-LIB_PATH = os.environ.get("GNNAGG_LIB") or os.path.join(_PKG_DIR, "libgnnagg.so")
+LIB_PATH = os.path.join(_PKG_DIR, "libgnnagg.so")
 
 _lib = None
 

@@ -35,18 +35,17 @@ def _stale() -> bool:
     return any(os.path.getmtime(d) > t for d in deps)
 
 
-def build(force: bool = False, verbose: bool = False, extra_flags=(), out_path: str = LIB_PATH) -> str:
-    """Compile every .cu under csrc/ into libgnnagg.so; returns its path.
-    extra_flags / out_path: tuning builds (e.g. -DGNNAGG_SPMM_MINBLOCKS=6) next to the default one."""
-    if not force and out_path == LIB_PATH and not _stale():
+def build(force: bool = False, verbose: bool = False) -> str:
+    """Compile every .cu under csrc/ into libgnnagg.so; returns its path."""
+    if not force and not _stale():
         return LIB_PATH
     nvcc = os.environ.get("NVCC", "/usr/local/cuda/bin/nvcc")
-    cmd = [nvcc] + NVCC_FLAGS + ["-I", os.path.join(REPO_ROOT, "include"), "-I", CSRC] + list(extra_flags)
+    cmd = [nvcc] + NVCC_FLAGS + ["-I", os.path.join(REPO_ROOT, "include"), "-I", CSRC]
     if verbose:
         cmd += ["-Xptxas", "-v"]
-    cmd += sources() + ["-o", out_path]
+    cmd += sources() + ["-o", LIB_PATH]
     subprocess.run(cmd, check=True)
-    return out_path
+    return LIB_PATH
 
 
 if __name__ == "__main__":

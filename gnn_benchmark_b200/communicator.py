@@ -9,8 +9,9 @@ caller's stream (not the host) wait for them -- which is how the exchange overla
 SpMM launched in between.  The blocking barrier the reference puts before every exchange
 (communicator.py:98,292) is not needed for correctness and is off by default.
 
-With CPU tensors and the gloo backend the same code runs as host-side plumbing (used by the
-world_size-2 CPU tests); the quantised mode needs the CUDA codec and therefore CUDA tensors.
+With CPU tensors and the gloo backend the fp32 exchange runs as host-side plumbing (used by the
+world_size-2 CPU tests); the bf16 and quantised modes need the CUDA kernels and therefore CUDA
+tensors.
 """
 import os
 
@@ -208,11 +209,8 @@ class Communicator(object):
 
 
 def _cast(src: torch.Tensor, dst: torch.Tensor) -> None:
-    """fp32 <-> bf16 buffer copy (communicator.py:128,137) through the C ABI on CUDA tensors;
-    torch's copy_ for the CPU plumbing tests."""
-    if not src.is_cuda:
-        dst.copy_(src)
-        return
+    """fp32 <-> bf16 buffer copy (communicator.py:128,137) through the C ABI; CUDA tensors only."""
+    _lib.require_cuda(src, dst)
     n = src.numel()
     if n == 0:
         return

@@ -26,6 +26,25 @@ __host__ __device__ inline int64_t div_up(int64_t a, int64_t b) { return (a + b 
 
 inline bool aligned16(const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
+// A set-up step that has to run once per device of the process (function attributes are per
+// device): run(f) calls f() the first time it is reached with a given device current and returns
+// f's result, cudaSuccess afterwards.  A failed f is retried by the next call.
+struct PerDeviceOnce {
+    static constexpr int kMaxDevices = 64;
+    int done[kMaxDevices] = {0};
+    template <typename Fn>
+    cudaError_t run(Fn f) {
+        int dev = -1;
+        cudaError_t e = cudaGetDevice(&dev);
+        if (e != cudaSuccess) return e;
+        if (dev < 0 || dev >= kMaxDevices) return cudaErrorInvalidDevice;
+        if (__atomic_load_n(&done[dev], __ATOMIC_ACQUIRE)) return cudaSuccess;
+        e = f();  // idempotent: two threads racing here set the same attribute
+        if (e == cudaSuccess) __atomic_store_n(&done[dev], 1, __ATOMIC_RELEASE);
+        return e;
+    }
+};
+
 // Gathered feature rows: read-only path, default L2 policy so that hub rows stay resident.
 __device__ __forceinline__ float4 ld_nc_v4(const float *p) { return __ldg(reinterpret_cast<const float4 *>(p)); }
 __device__ __forceinline__ float ld_nc(const float *p) { return __ldg(p); }

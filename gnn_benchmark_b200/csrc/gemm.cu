@@ -903,10 +903,9 @@ extern "C" int gnnagg_dense_tf32x3_f32(const float *A, int64_t lda, const float 
     float *w_hi = reinterpret_cast<float *>(ws + kStatusBytes);
     float *w_lo = reinterpret_cast<float *>(ws + kStatusBytes + piece_bytes(N, K));
 
-    static std::once_flag attr_once;
-    static cudaError_t attr_err = cudaSuccess;
-    std::call_once(attr_once, [] {
-        attr_err = cudaFuncSetAttribute(gemm_tf32x3_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
+    static PerDeviceOnce attr_done;
+    const cudaError_t attr_err = attr_done.run([] {
+        return cudaFuncSetAttribute(gemm_tf32x3_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
     });
     if (attr_err != cudaSuccess)
         return fail(GNNAGG_ERR_CUDA, "dense: cannot reserve %d bytes of shared memory: %s", SMEM_BYTES,
@@ -986,10 +985,9 @@ extern "C" int gnnagg_dense_wgrad_tf32x3_f32(const float *G, int64_t ldg, const 
         return GNNAGG_OK;
     }
 
-    static std::once_flag attr_once;
-    static cudaError_t attr_err = cudaSuccess;
-    std::call_once(attr_once, [] {
-        attr_err = cudaFuncSetAttribute(wgrad_tf32x3_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, WG_SMEM_BYTES);
+    static PerDeviceOnce attr_done;
+    const cudaError_t attr_err = attr_done.run([] {
+        return cudaFuncSetAttribute(wgrad_tf32x3_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, WG_SMEM_BYTES);
     });
     if (attr_err != cudaSuccess)
         return fail(GNNAGG_ERR_CUDA, "dense_wgrad: cannot reserve %d bytes of shared memory: %s", WG_SMEM_BYTES,

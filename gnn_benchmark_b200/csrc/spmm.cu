@@ -25,7 +25,6 @@
 // (less what L2 catches) + (M+1)*8 rowptr + M*F*4 output (+ the same again when
 // accumulating).
 #include <limits.h>
-#include <stdlib.h>
 
 #include "common.cuh"
 
@@ -59,19 +58,7 @@ struct PlanHeader {
 };
 static_assert(sizeof(PlanHeader) == 64, "plan header is 64 bytes");
 
-static int chunk_items() {
-    static int cached = 0;
-    if (cached == 0) {
-        int v = kDefaultItems;
-        const char *s = getenv("GNNAGG_SPMM_CHUNK_ITEMS");  // tuning knob
-        if (s != nullptr) {
-            const int t = atoi(s);
-            if (t >= 32 && t <= (1 << 20)) v = t;
-        }
-        cached = v;
-    }
-    return cached;
-}
+static int chunk_items() { return kDefaultItems; }
 
 static int64_t num_chunks(int64_t M, int64_t nnz, int items) {
     const int64_t n = div_up(M + nnz, items);

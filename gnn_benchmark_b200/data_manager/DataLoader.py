@@ -76,6 +76,39 @@ def _scatter_matrix(idx: torch.Tensor, num_local_nodes: int) -> SparseTensor:
     return SparseTensor(row=idx.to(torch.int64), col=cols, sparse_sizes=(num_local_nodes, idx.numel()))
 
 
+def _check_graph(graph) -> None:
+    """Refuse a malformed graph before any kernel runs on it: the gather, SpMM and codec kernels index
+    device memory with these arrays and do no bounds checks of their own.  Every matrix goes through
+    the device-side CSR check (row pointers monotone, columns in range); the send index must address
+    local rows; the halo matrices must have exactly one column (row) per exchanged row.  CUDA graphs
+    only: the check is a kernel of the library."""
+    n = graph.local_adj_t.sparse_size(0)
+    if not graph.local_adj_t.device.type == "cuda":
+        return
+    n_recv, n_send = sum(graph.comm_splits.recv_splits), sum(graph.comm_splits.send_splits)
+    graph.local_adj_t.validate()
+    if hasattr(graph, "remote_adj_t"):
+        graph.remote_adj_t.validate()
+        if graph.remote_adj_t.sparse_size(1) != n_recv or graph.remote_adj_t.sparse_size(0) != n:
+            raise RuntimeError("remote_adj_t does not match the receive splits")
+        idx = graph.idx_nodes_send_to_others
+        if idx.numel() != n_send:
+            raise RuntimeError("idx_nodes_send_to_others does not match the send splits")
+        if idx.numel() and (int(idx.min()) < 0 or int(idx.max()) >= n):
+            raise RuntimeError("idx_nodes_send_to_others addresses rows outside this partition")
+        graph.scatter_adj_t.validate()
+    else:
+        graph.adj_t_pre_post_aggr_from.validate()
+        graph.adj_t_pre_post_aggr_to.validate()
+        if graph.adj_t_pre_post_aggr_from.sparse_sizes() != (n, n_recv) or \
+                graph.adj_t_pre_post_aggr_to.sparse_sizes() != (n_send, n):
+            raise RuntimeError("pre/post aggregation matrices do not match the exchange splits")
+    q = graph.comm_buf_for_quantization
+    if q is not None:
+        if int(q.quantized_work_range_per_proc[-1]) != n_send or int(q.dequantized_work_range_per_proc[-1]) != n_recv:
+            raise RuntimeError("per-peer row prefixes of the packed halo do not match the exchange splits")
+
+
 def get_distributed_graph(local_edges_list, remote_edges_list, local_nodes_list, nodes_range_on_each_subgraph,
                           num_local_nodes: int, max_feat_len: int, world_size: int, bits: int, device=None,
                           lean_halo: bool = False):
@@ -120,6 +153,7 @@ def get_distributed_graph(local_edges_list, remote_edges_list, local_nodes_list,
     )
     graph.idx_nodes_send_to_others_i32 = graph.idx_nodes_send_to_others.to(torch.int32)
     graph.scatter_adj_t = _scatter_matrix(graph.idx_nodes_send_to_others, num_local_nodes)
+    _check_graph(graph)
     return graph
 
 
@@ -154,7 +188,7 @@ def get_distributed_graph_for_pre_aggressive(local_edges_list, remote_edges_list
     comm_buf_for_quantization = None
     if bits in (2, 4, 8):
         comm_buf_for_quantization = CommBufferForQuantization(comm_splits, max_feat_len, bits, device)
-    return DistributedGraphForPre(
+    graph = DistributedGraphForPre(
         local_adj_t.to(device),
         adj_t_pre_post_aggr_from.to(device),
         adj_t_pre_post_aggr_to.to(device),
@@ -165,6 +199,8 @@ def get_distributed_graph_for_pre_aggressive(local_edges_list, remote_edges_list
         comm_buf,
         comm_buf_for_quantization,
     )
+    _check_graph(graph)
+    return graph
 
 
 def build_graph(local_edges_list, remote_edges_list, nodes_range_on_each_subgraph, rank, world_size, max_feat_len,

@@ -1,11 +1,16 @@
 """Communication-plan construction for one rank, with the reference's class and method names.
 
-The reference builds these plans with per-edge Python loops and `.item()` calls
-(self_benchmark/a64fx/data_manager/DataProcessor.py:39-53, 238-246, 438-444).  Here every
-step is a sort / unique / searchsorted / cumsum over whole tensors, so it runs on whatever
-device the edge lists live on (CPU or GPU) and scales to billions of edges, while producing
-the same arrays: halo slot numbering, per-peer split counts, send index, and the three
-sparse matrices of the pre/post-aggregation scheme.
+The reference builds these plans with per-edge Python loops and `.item()` calls, and the pre/post
+plan additionally peer by peer, masking the whole edge list once per peer and growing its result
+lists with `torch.cat` (self_benchmark/a64fx/data_manager/DataProcessor.py:39-53, 133-326,
+429-445).  Here a plan is ONE pass over the rank's remote edges for all peers at once: the owner of
+every source comes from a `searchsorted` on the partition starts, one stable sort groups the edges
+by owner, multiplicities and the pre/post decision are segment operations on composite
+(owner, id) keys, and the per-peer pieces the reference returns are cut out of the grouped arrays
+by their counts.  It runs on whatever device the edge lists live on (CPU or GPU) and produces the
+same arrays: halo slot numbering, per-peer split counts, send index, and the three sparse matrices
+of the pre/post-aggregation scheme.  The stage functions the reference's unit tests call keep their
+names and signatures and are thin adapters over the same pass.
 """
 import torch
 import torch.distributed as dist
@@ -30,6 +35,13 @@ def _exchange_counts(counts: torch.Tensor, world_size: int) -> torch.Tensor:
     return out
 
 
+def _prefix(counts: torch.Tensor) -> torch.Tensor:
+    """[0, cumsum(counts)] as a CPU int64 tensor (the reference keeps its edge offsets on the host)."""
+    out = torch.zeros(counts.numel() + 1, dtype=torch.int64)
+    out[1:] = torch.cumsum(counts.to(torch.int64).cpu(), 0)
+    return out
+
+
 class DataProcessor(object):
     def __init__(self) -> None:
         pass
@@ -37,22 +49,16 @@ class DataProcessor(object):
     @staticmethod
     def get_in_degrees(local_edges_list, remote_edges_list, num_local_nodes):
         """In-degree of every local node over local and remote in-edges, clamped to >= 1, (n,1)
-        fp32 (DataProcessor.py:11-18)."""
-        dev = local_edges_list[1].device
-        local_degs = torch.zeros((num_local_nodes), dtype=torch.float32, device=dev)
-        source = torch.ones((local_edges_list[1].shape[0]), dtype=torch.float32, device=dev)
-        local_degs.index_add_(dim=0, index=local_edges_list[1], source=source)
-        source = torch.ones((remote_edges_list[1].shape[0]), dtype=torch.float32, device=dev)
-        local_degs.index_add_(dim=0, index=remote_edges_list[1], source=source)
-        return local_degs.clamp(min=1).unsqueeze(-1)
+        fp32 (DataProcessor.py:11-18): one histogram of all destination ids."""
+        dst = torch.cat((local_edges_list[1].reshape(-1), remote_edges_list[1].reshape(-1)))
+        degs = torch.bincount(dst, minlength=num_local_nodes)[:num_local_nodes]
+        return degs.clamp_(min=1).to(torch.float32).unsqueeze(-1)
 
     @staticmethod
     def sort_remote_edges_list_based_on_remote_nodes(remote_edges_list):
         """Sort remote edges by (global) source id, in place (DataProcessor.py:20-26)."""
-        remote_edges_row, remote_edges_col = remote_edges_list[0], remote_edges_list[1]
-        sort_index = torch.sort(remote_edges_row, stable=True)[1]
-        remote_edges_list[0] = remote_edges_row[sort_index]
-        remote_edges_list[1] = remote_edges_col[sort_index]
+        sort_index = torch.sort(remote_edges_list[0], stable=True)[1]
+        remote_edges_list[0], remote_edges_list[1] = remote_edges_list[0][sort_index], remote_edges_list[1][sort_index]
         return remote_edges_list
 
     @staticmethod
@@ -109,18 +115,94 @@ class DataProcessor(object):
         return local_adj_t, remote_adj_t
 
 
-def _multiplicity(x: torch.Tensor) -> torch.Tensor:
-    """For every element, how many times its value occurs in x."""
-    if x.numel() == 0:
-        return torch.zeros(0, dtype=torch.int64, device=x.device)
-    _, inverse, counts = torch.unique(x, return_inverse=True, return_counts=True)
+# ---- the one-pass engine of the pre/post plan --------------------------------------------------------
+def _multiplicity(key: torch.Tensor) -> torch.Tensor:
+    """For every element, how many times its value occurs in `key`."""
+    if key.numel() == 0:
+        return torch.zeros(0, dtype=torch.int64, device=key.device)
+    _, inverse, counts = torch.unique(key, return_inverse=True, return_counts=True)
     return counts[inverse]
 
 
-def _sort_pairs(first: torch.Tensor, second: torch.Tensor, by_second: bool):
-    key = second if by_second else first
-    idx = torch.sort(key, stable=True)[1]
-    return first[idx], second[idx]
+def _mask_of(idx: torch.Tensor, n: int) -> torch.Tensor:
+    """Boolean mask of length n from either a boolean mask or a list of positions."""
+    if idx.dtype == torch.bool:
+        return idx
+    m = torch.zeros(n, dtype=torch.bool, device=idx.device)
+    m[idx.to(torch.int64)] = True
+    return m
+
+
+class _Grouped(object):
+    """Pairs (first, second) of all peers, grouped by peer: `counts[p]` pairs belong to peer p."""
+
+    def __init__(self, first, second, counts, distinct):
+        self.first, self.second, self.counts, self.distinct = first, second, counts, distinct
+
+    def per_peer(self):
+        sizes = [int(c) for c in self.counts.tolist()]
+        return list(zip(torch.split(self.first, sizes), torch.split(self.second, sizes)))
+
+
+def _group_pairs(first, second, owner, sort_by_second: bool, span: int, world_size: int) -> _Grouped:
+    """Order pairs by (owner, key) with key = second or first; pairs with equal (owner, key) keep their
+    input order.  `distinct[p]` = number of different keys inside peer p = rows on the wire."""
+    key = owner * span + (second if sort_by_second else first)
+    key, perm = torch.sort(key, stable=True)
+    counts = torch.bincount(owner, minlength=world_size)[:world_size] if owner.numel() else \
+        torch.zeros(world_size, dtype=torch.int64, device=first.device)
+    if key.numel():
+        distinct = torch.bincount(torch.unique_consecutive(key) // span, minlength=world_size)[:world_size]
+    else:
+        distinct = torch.zeros(world_size, dtype=torch.int64, device=first.device)
+    return _Grouped(first[perm], second[perm], counts, distinct)
+
+
+def _ship_and_aggregate(src, dst, owner, post, span: int, world_size: int):
+    """From the classified remote edges of all peers build, grouped by peer,
+      * what each owner must learn (DataProcessor.py:250-279): the pre edges (s, d) plus (s, s) for
+        every distinct post source, ordered by the second key;
+      * what is aggregated here after the exchange (DataProcessor.py:281-326): the post edges (s, d)
+        plus (d, d) for every distinct pre destination, ordered by the first key."""
+    pre = ~post
+    # distinct post sources / pre destinations of every peer, with their owners, from composite keys
+    k_post = torch.unique(owner[post] * span + src[post])
+    post_src, post_src_owner = k_post % span, k_post // span
+    k_pre = torch.unique(owner[pre] * span + dst[pre])
+    pre_dst, pre_dst_owner = k_pre % span, k_pre // span
+    shipped = _group_pairs(torch.cat((src[pre], post_src)), torch.cat((dst[pre], post_src)),
+                           torch.cat((owner[pre], post_src_owner)), True, span, world_size)
+    aggregated = _group_pairs(torch.cat((src[post], pre_dst)), torch.cat((dst[post], pre_dst)),
+                              torch.cat((owner[post], pre_dst_owner)), False, span, world_size)
+    return shipped, aggregated
+
+
+def _span(*tensors) -> int:
+    m = 0
+    for t in tensors:
+        if t.numel():
+            m = max(m, int(t.max()))
+    return m + 1
+
+
+def _classify(src, dst, owner, span: int) -> torch.Tensor:
+    """post[e] = outdeg(src[e]) > indeg(dst[e]), both counted inside the edge's own peer subset
+    (DataProcessor.py:227-248)."""
+    return _multiplicity(owner * span + src) > _multiplicity(owner * span + dst)
+
+
+def _plan_all_peers(begin_node_on_each_subgraph, src, dst, world_size: int):
+    dev = src.device
+    begin = torch.as_tensor(begin_node_on_each_subgraph, dtype=torch.int64, device=dev)
+    owner = torch.searchsorted(begin, src, right=True) - 1
+    inside = (owner >= 0) & (owner < world_size)  # sources outside every range belong to no peer
+    if not bool(inside.all()):
+        src, dst, owner = src[inside], dst[inside], owner[inside]
+    owner, order = torch.sort(owner, stable=True)  # peers in order, edge order kept inside a peer
+    src, dst = src[order], dst[order]
+    span = _span(src, dst)
+    post = _classify(src, dst, owner, span)
+    return _ship_and_aggregate(src, dst, owner, post, span, world_size)
 
 
 class DataProcessorForPreAggresive(object):
@@ -129,125 +211,87 @@ class DataProcessorForPreAggresive(object):
 
     @staticmethod
     def get_degrees(nodes_list):
-        """{node id: multiplicity} (DataProcessor.py:125-131); kept for small inputs and tests,
-        the plan builder itself uses the tensor form `_multiplicity`."""
+        """{node id: multiplicity} (DataProcessor.py:125-131); for small inputs and tests, the plan
+        itself counts with `_multiplicity`."""
         unique_nodes_list, counts = torch.unique(nodes_list, return_counts=True)
         return dict(zip(unique_nodes_list.tolist(), counts.tolist()))
 
     @staticmethod
     def decide_pre_or_post_aggr(src_in_remote_edges, dst_in_remote_edges, is_pre, is_post):
-        """Edge (s, d) is post-aggregated iff outdeg(s) > indeg(d) inside this peer's edge
-        subset, else pre-aggregated (DataProcessor.py:227-248)."""
-        out_deg = _multiplicity(src_in_remote_edges)
-        in_deg = _multiplicity(dst_in_remote_edges)
-        flags = torch.full((src_in_remote_edges.shape[0],), is_pre, dtype=torch.int64,
-                           device=src_in_remote_edges.device)
-        flags[out_deg > in_deg] = is_post
-        return flags
+        """Flags of one peer's edge subset: is_post where outdeg(s) > indeg(d), else is_pre."""
+        n = src_in_remote_edges.shape[0]
+        owner = torch.zeros(n, dtype=torch.int64, device=src_in_remote_edges.device)
+        post = _classify(src_in_remote_edges, dst_in_remote_edges, owner, _span(src_in_remote_edges, dst_in_remote_edges))
+        return torch.where(post, int(is_post), int(is_pre)).to(torch.int64)
+
+    @staticmethod
+    def _one_peer(src, dst, pre_aggr_edge_idx, post_aggr_edge_idx):
+        n = src.shape[0]
+        post = _mask_of(post_aggr_edge_idx, n)
+        keep = post | _mask_of(pre_aggr_edge_idx, n)  # the caller's two selections, whatever made them
+        src, dst, post = src[keep], dst[keep], post[keep]
+        owner = torch.zeros(src.shape[0], dtype=torch.int64, device=src.device)
+        return _ship_and_aggregate(src, dst, owner, post, _span(src, dst), 1)
 
     @staticmethod
     def collect_edges_sent_to_other_subgraphs(src_in_remote_edges, dst_in_remote_edges, pre_aggr_edge_idx,
                                               post_aggr_edge_idx, remote_edges_sent_for_graph_exchange):
-        """What the owner of the sources must learn (DataProcessor.py:250-279): the pre edges
-        (s, d) plus (s, s) for every unique post source, sorted by the second key, appended as
-        one tensor [firsts..., seconds...]."""
-        src_in_pre = src_in_remote_edges[pre_aggr_edge_idx]
-        dst_in_pre = dst_in_remote_edges[pre_aggr_edge_idx]
-        src_in_post = torch.unique(src_in_remote_edges[post_aggr_edge_idx], sorted=True)
-        src_to_send = torch.cat((src_in_pre, src_in_post), dim=0)
-        dst_to_send = torch.cat((dst_in_pre, src_in_post), dim=0)
-        src_to_send, dst_to_send = _sort_pairs(src_to_send, dst_to_send, by_second=True)
-        remote_edges_sent_for_graph_exchange.append(torch.cat((src_to_send, dst_to_send), dim=0))
+        """Append one peer's shipped list [firsts..., seconds...] (DataProcessor.py:250-279)."""
+        shipped, _ = DataProcessorForPreAggresive._one_peer(src_in_remote_edges, dst_in_remote_edges,
+                                                            pre_aggr_edge_idx, post_aggr_edge_idx)
+        remote_edges_sent_for_graph_exchange.append(torch.cat((shipped.first, shipped.second)))
 
     @staticmethod
     def collect_edges_for_aggregation(src_in_remote_edges, dst_in_remote_edges, pre_aggr_edge_idx, post_aggr_edge_idx,
                                       remote_edges_for_aggr_on_recv, recv_splits_for_data_exchange,
                                       begin_edge_on_each_partition_from, cur_rank):
-        """Receiver-side aggregation list of one peer (DataProcessor.py:281-326): the post edges
-        (s, d) plus (d, d) for every unique pre destination, sorted by the first key; the number
-        of distinct first keys is this peer's receive split."""
-        src_in_post = src_in_remote_edges[post_aggr_edge_idx]
-        dst_in_post = dst_in_remote_edges[post_aggr_edge_idx]
-        dst_in_pre = dst_in_remote_edges[pre_aggr_edge_idx]
-        dst_from_recv = torch.unique(dst_in_pre, sorted=True)
-        src_from_recv = torch.cat((src_in_post, dst_from_recv), dim=0)
-        dst_from_recv = torch.cat((dst_in_post, dst_from_recv), dim=0)
-        src_from_recv, dst_from_recv = _sort_pairs(src_from_recv, dst_from_recv, by_second=False)
-        recv_splits_for_data_exchange.append(int(torch.unique(src_from_recv).shape[0]))
-        remote_edges_for_aggr_on_recv[0] = torch.cat((remote_edges_for_aggr_on_recv[0], src_from_recv), dim=0)
-        remote_edges_for_aggr_on_recv[1] = torch.cat((remote_edges_for_aggr_on_recv[1], dst_from_recv), dim=0)
-        begin_edge_on_each_partition_from[cur_rank + 1] = (
-            begin_edge_on_each_partition_from[cur_rank] + src_from_recv.shape[0]
-        )
+        """Append one peer's receiver-side aggregation list, its receive split and its edge offset
+        (DataProcessor.py:281-326)."""
+        _, aggregated = DataProcessorForPreAggresive._one_peer(src_in_remote_edges, dst_in_remote_edges,
+                                                               pre_aggr_edge_idx, post_aggr_edge_idx)
+        recv_splits_for_data_exchange.append(int(aggregated.distinct[0]))
+        remote_edges_for_aggr_on_recv[0] = torch.cat((remote_edges_for_aggr_on_recv[0], aggregated.first))
+        remote_edges_for_aggr_on_recv[1] = torch.cat((remote_edges_for_aggr_on_recv[1], aggregated.second))
+        begin_edge_on_each_partition_from[cur_rank + 1] = (begin_edge_on_each_partition_from[cur_rank]
+                                                           + aggregated.first.shape[0])
 
     @staticmethod
     def split_remote_edges_for_aggr_and_graph_exchange(begin_node_on_each_subgraph, remote_edges_list, world_size):
-        """Per peer: classify its remote edges, build what is shipped to it and what is aggregated
-        here (DataProcessor.py:133-199)."""
-        dev = remote_edges_list[0].device
-        remote_edges_sent_for_graph_exchange = []
-        recv_splits_for_data_exchange = []
-        begin_edge_on_each_partition_from = torch.zeros(world_size + 1, dtype=torch.int64)
-        remote_edges_for_aggr_on_recv = [
-            torch.empty((0), dtype=torch.int64, device=dev),
-            torch.empty((0), dtype=torch.int64, device=dev),
-        ]
-        is_pre, is_post = 1, 0
-        all_src, all_dst = remote_edges_list[0], remote_edges_list[1]
-        for i in range(world_size):
-            begin_idx = int(begin_node_on_each_subgraph[i])
-            end_idx = int(begin_node_on_each_subgraph[i + 1])
-            edge_idx = (all_src >= begin_idx) & (all_src < end_idx)
-            src = all_src[edge_idx]
-            dst = all_dst[edge_idx]
-            flags = DataProcessorForPreAggresive.decide_pre_or_post_aggr(src, dst, is_pre, is_post)
-            pre_aggr_edge_idx = flags == is_pre
-            post_aggr_edge_idx = flags == is_post
-            DataProcessorForPreAggresive.collect_edges_sent_to_other_subgraphs(
-                src, dst, pre_aggr_edge_idx, post_aggr_edge_idx, remote_edges_sent_for_graph_exchange)
-            DataProcessorForPreAggresive.collect_edges_for_aggregation(
-                src, dst, pre_aggr_edge_idx, post_aggr_edge_idx, remote_edges_for_aggr_on_recv,
-                recv_splits_for_data_exchange, begin_edge_on_each_partition_from, i)
-        begin_edge_on_each_partition_from[world_size] = remote_edges_for_aggr_on_recv[0].shape[0]
-        return (
-            remote_edges_sent_for_graph_exchange,
-            remote_edges_for_aggr_on_recv,
-            begin_edge_on_each_partition_from,
-            recv_splits_for_data_exchange,
-        )
+        """All peers at once (DataProcessor.py:133-199): the shipped list of every peer, the
+        receiver-side aggregation list (peers concatenated), its per-peer edge offsets and the receive
+        splits."""
+        shipped, aggregated = _plan_all_peers(begin_node_on_each_subgraph, remote_edges_list[0], remote_edges_list[1],
+                                              world_size)
+        sent = [torch.cat(pair) for pair in shipped.per_peer()]
+        return (sent, [aggregated.first, aggregated.second], _prefix(aggregated.counts),
+                [int(x) for x in aggregated.distinct.tolist()])
 
     @staticmethod
     def split_remote_edges_recv_from_graph_exchange(remote_edges_recv_from_graph_exchange, world_size):
-        """Sender side: unpack what each peer shipped ([firsts..., seconds...]) and count the
-        distinct second keys = rows this rank sends to that peer (DataProcessor.py:201-225)."""
-        dev = remote_edges_recv_from_graph_exchange[0].device if len(remote_edges_recv_from_graph_exchange) else None
-        remote_edges_for_aggr_for_send = [
-            torch.empty((0), dtype=torch.int64, device=dev),
-            torch.empty((0), dtype=torch.int64, device=dev),
-        ]
-        begin_edge_on_each_partition_to = torch.zeros(world_size + 1, dtype=torch.int64)
-        send_splits_for_data_exchange = []
-        for i in range(world_size):
-            num_remote_edges = int(remote_edges_recv_from_graph_exchange[i].shape[0] / 2)
-            src = remote_edges_recv_from_graph_exchange[i][:num_remote_edges]
-            dst = remote_edges_recv_from_graph_exchange[i][num_remote_edges:]
-            send_splits_for_data_exchange.append(int(torch.unique(dst).shape[0]))
-            remote_edges_for_aggr_for_send[0] = torch.cat((remote_edges_for_aggr_for_send[0], src), dim=0)
-            remote_edges_for_aggr_for_send[1] = torch.cat((remote_edges_for_aggr_for_send[1], dst), dim=0)
-            begin_edge_on_each_partition_to[i + 1] = begin_edge_on_each_partition_to[i] + dst.shape[0]
-        begin_edge_on_each_partition_to[world_size] = remote_edges_for_aggr_for_send[0].shape[0]
-        return remote_edges_for_aggr_for_send, begin_edge_on_each_partition_to, send_splits_for_data_exchange
+        """Sender side (DataProcessor.py:201-225): every peer's message is [firsts..., seconds...];
+        the rows this rank sends to that peer are its distinct second keys."""
+        msgs = list(remote_edges_recv_from_graph_exchange)[:world_size]
+        halves = [int(m.shape[0]) // 2 for m in msgs]
+        dev = msgs[0].device if msgs else None
+        empty = torch.empty(0, dtype=torch.int64, device=dev)
+        first = torch.cat([m[:h] for m, h in zip(msgs, halves)]) if msgs else empty
+        second = torch.cat([m[h:2 * h] for m, h in zip(msgs, halves)]) if msgs else empty
+        counts = torch.tensor(halves, dtype=torch.int64)
+        peer = torch.repeat_interleave(torch.arange(len(msgs), device=dev), counts.to(dev)) if msgs else empty
+        if second.numel():
+            span = _span(second)
+            distinct = torch.bincount(torch.unique(peer * span + second) // span, minlength=world_size)[:world_size]
+            send_splits = [int(x) for x in distinct.tolist()]
+        else:
+            send_splits = [0] * world_size
+        return [first, second], _prefix(counts), send_splits
 
     @staticmethod
     def communicate_to_get_num_remote_edges(remote_edges_sent_for_graph_exchange, world_size):
         """Exchange the lengths of the shipped lists (DataProcessor.py:328-350)."""
         dev = remote_edges_sent_for_graph_exchange[0].device
-        num_remote_edges_send = torch.tensor([t.shape[0] for t in remote_edges_sent_for_graph_exchange],
-                                             dtype=torch.int64, device=dev)
-        num_remote_edges_recv = torch.zeros(world_size, dtype=torch.int64, device=dev)
-        if world_size != 1:
-            dist.all_to_all_single(num_remote_edges_recv, num_remote_edges_send, [1] * world_size, [1] * world_size)
-        return num_remote_edges_send, num_remote_edges_recv
+        lengths = torch.tensor([t.shape[0] for t in remote_edges_sent_for_graph_exchange], dtype=torch.int64, device=dev)
+        return lengths, (_exchange_counts(lengths, world_size) if world_size != 1 else torch.zeros_like(lengths))
 
     @staticmethod
     def communicate_to_get_remote_edges(remote_edges_sent_for_graph_exchange, send_splits_for_graph_exchange,
@@ -255,44 +299,24 @@ class DataProcessorForPreAggresive(object):
         """Exchange the shipped lists themselves (DataProcessor.py:352-382)."""
         send_splits = [int(x) for x in send_splits_for_graph_exchange.tolist()]
         recv_splits = [int(x) for x in recv_splits_for_graph_exchange.tolist()]
-        send = torch.cat(remote_edges_sent_for_graph_exchange, dim=0)
-        recv = torch.empty(sum(recv_splits), dtype=torch.int64, device=send.device)
+        send = torch.cat(remote_edges_sent_for_graph_exchange)
         if world_size != 1:
-            dist.all_to_all_single(recv, send, recv_splits, send_splits)
-        return torch.split(recv, recv_splits, dim=0)
+            recv = _all_to_all_v(send, send_splits, recv_splits)
+        else:
+            recv = torch.empty(sum(recv_splits), dtype=torch.int64, device=send.device)
+        return torch.split(recv, recv_splits)
 
     @staticmethod
     def divide_remote_edges_list(begin_node_on_each_subgraph, remote_edges_list, world_size):
-        """DataProcessor.py:384-427."""
-        (
-            remote_edges_sent_for_graph_exchange,
-            remote_edges_for_aggr_on_recv,
-            begin_edge_on_each_partition_from,
-            recv_splits_for_data_exchange,
-        ) = DataProcessorForPreAggresive.split_remote_edges_for_aggr_and_graph_exchange(
-            begin_node_on_each_subgraph, remote_edges_list, world_size
-        )
-        send_splits, recv_splits = DataProcessorForPreAggresive.communicate_to_get_num_remote_edges(
-            remote_edges_sent_for_graph_exchange, world_size
-        )
-        remote_edges_recv_from_graph_exchange = DataProcessorForPreAggresive.communicate_to_get_remote_edges(
-            remote_edges_sent_for_graph_exchange, send_splits, recv_splits, world_size
-        )
-        (
-            remote_edges_for_aggr_for_send,
-            begin_edge_on_each_partition_to,
-            send_splits_for_data_exchange,
-        ) = DataProcessorForPreAggresive.split_remote_edges_recv_from_graph_exchange(
-            remote_edges_recv_from_graph_exchange, world_size
-        )
-        return (
-            remote_edges_for_aggr_on_recv,
-            remote_edges_for_aggr_for_send,
-            begin_edge_on_each_partition_from,
-            begin_edge_on_each_partition_to,
-            recv_splits_for_data_exchange,
-            send_splits_for_data_exchange,
-        )
+        """Both sides of the pre/post plan of this rank (DataProcessor.py:384-427): classify and group
+        locally, ship to the owners, regroup what the others shipped."""
+        cls = DataProcessorForPreAggresive
+        sent, for_recv, begin_from, recv_splits = cls.split_remote_edges_for_aggr_and_graph_exchange(
+            begin_node_on_each_subgraph, remote_edges_list, world_size)
+        n_send, n_recv = cls.communicate_to_get_num_remote_edges(sent, world_size)
+        got = cls.communicate_to_get_remote_edges(sent, n_send, n_recv, world_size)
+        for_send, begin_to, send_splits = cls.split_remote_edges_recv_from_graph_exchange(got, world_size)
+        return for_recv, for_send, begin_from, begin_to, recv_splits, send_splits
 
     @staticmethod
     def remap_remote_nodes_id(remote_nodes_list, begin_edge_on_each_partition):
@@ -322,22 +346,15 @@ class DataProcessorForPreAggresive(object):
         local_adj_t (n x n); adj_t_pre_post_aggr_from (n x recv slots): row = local destination,
         col = wire slot; adj_t_pre_post_aggr_to (send slots x n): row = wire slot, col = local
         source."""
-        local_adj_t = SparseTensor(row=local_edges_list[1], col=local_edges_list[0],
-                                   sparse_sizes=(num_local_nodes, num_local_nodes))
-        remote_edges_list_pre_post_aggr_from[1] -= local_node_begin_idx
-        num_remote_nodes_from = DataProcessorForPreAggresive.remap_remote_nodes_id(
-            remote_edges_list_pre_post_aggr_from[0], begin_edge_on_each_partition_from
-        )
-        adj_t_pre_post_aggr_from = SparseTensor(
-            row=remote_edges_list_pre_post_aggr_from[1], col=remote_edges_list_pre_post_aggr_from[0],
-            sparse_sizes=(num_local_nodes, num_remote_nodes_from),
-        )
-        remote_edges_list_pre_post_aggr_to[0] -= local_node_begin_idx
-        num_remote_nodes_to = DataProcessorForPreAggresive.remap_remote_nodes_id(
-            remote_edges_list_pre_post_aggr_to[1], begin_edge_on_each_partition_to
-        )
-        adj_t_pre_post_aggr_to = SparseTensor(
-            row=remote_edges_list_pre_post_aggr_to[1], col=remote_edges_list_pre_post_aggr_to[0],
-            sparse_sizes=(num_remote_nodes_to, num_local_nodes),
-        )
+        remap = DataProcessorForPreAggresive.remap_remote_nodes_id
+        n = num_local_nodes
+        local_adj_t = SparseTensor(row=local_edges_list[1], col=local_edges_list[0], sparse_sizes=(n, n))
+        slot_from, dst_local = remote_edges_list_pre_post_aggr_from
+        dst_local -= local_node_begin_idx
+        num_slots_from = remap(slot_from, begin_edge_on_each_partition_from)  # keys -> slot ids, in place
+        adj_t_pre_post_aggr_from = SparseTensor(row=dst_local, col=slot_from, sparse_sizes=(n, num_slots_from))
+        src_local, slot_to = remote_edges_list_pre_post_aggr_to
+        src_local -= local_node_begin_idx
+        num_slots_to = remap(slot_to, begin_edge_on_each_partition_to)
+        adj_t_pre_post_aggr_to = SparseTensor(row=slot_to, col=src_local, sparse_sizes=(num_slots_to, n))
         return local_adj_t, adj_t_pre_post_aggr_from, adj_t_pre_post_aggr_to

@@ -12,21 +12,34 @@ into a small matrix) on the same tensor-core scheme.  Shapes the kernels do not 
 output columns, operand rows not 16-byte aligned) go to cuBLAS: `supported()` / `wgrad_supported()`
 say which.
 """
-import os
+import warnings
 
 import torch
 
 from . import _lib
 
 MAX_N = 256
-# "tf32x3" (default): the tensor-core kernels wherever `supported()`; "cublas": plain torch fp32 matmul.
-MODE = os.environ.get("GNNAGG_DENSE", "tf32x3")
+# "tf32x3": the tensor-core kernels wherever `supported()`.  Tests and the epoch benchmark set
+# "cublas" (torch's fp32 matmul) to have the library call the kernels replace measured beside them.
+MODE = "tf32x3"
 
 _workspaces = {}
 
 
 def enabled() -> bool:
     return MODE == "tf32x3"
+
+
+_warned = set()
+
+
+def _library_path(what: str, shape) -> None:
+    """Say once per shape that a product went to cuBLAS because the tensor-core kernel does not take it."""
+    key = (what, tuple(shape))
+    if enabled() and key not in _warned:
+        _warned.add(key)
+        warnings.warn(f"dense.{what}: shape {tuple(shape)} is outside the tensor-core kernel's range "
+                      f"(at most {MAX_N} output columns, 16-byte aligned operand rows); using torch.matmul for it")
 
 
 def supported(a: torch.Tensor, n_out: int) -> bool:
@@ -113,6 +126,7 @@ def _matmul_tn(g: torch.Tensor, x: torch.Tensor) -> torch.Tensor:
     """g.T @ x, tensor-core kernel when it takes the shapes, cuBLAS otherwise."""
     if enabled() and wgrad_supported(g, x):
         return wgrad(g, x)
+    _library_path("wgrad", (g.size(1), x.size(1)))
     return g.t() @ x
 
 
@@ -168,6 +182,7 @@ def _matmul_nt(a: torch.Tensor, w: torch.Tensor, bias=None, out=None, accumulate
     """a @ w.T (+bias), tensor-core kernel when it takes the shape, cuBLAS otherwise."""
     if enabled() and supported(a, w.size(0)):
         return linear(a, w, bias, out, accumulate)
+    _library_path("linear", (w.size(0), a.size(1)))
     r = a @ w.t()
     if bias is not None:
         r += bias

@@ -7,14 +7,14 @@ self_benchmark/a64fx/model/DistSAGE.py:49-54).
 mask comes from a counter-based generator inside the kernel, keyed by a 64-bit seed drawn from
 torch's CPU generator (so `torch.manual_seed` makes runs repeatable); it is not torch's mask.
 """
-import os
+import warnings
 
 import torch
 import torch.nn.functional as F
 
 from . import _lib
 
-MODE = os.environ.get("GNNAGG_NORM", "fused")  # "fused" | "torch"
+MODE = "fused"  # tests set "torch" to compare against the three separate ops
 
 _partials = {}
 
@@ -22,6 +22,18 @@ _partials = {}
 def supported(x: torch.Tensor) -> bool:
     return (MODE == "fused" and x.is_cuda and x.dtype == torch.float32 and x.dim() == 2 and x.stride(1) == 1
             and x.size(1) % 4 == 0 and 0 < x.size(1) <= 1024 and x.stride(0) % 4 == 0 and x.data_ptr() % 16 == 0)
+
+
+_warned = set()
+
+
+def _torch_path(what: str, x: torch.Tensor) -> None:
+    """Say once per width that a call went to the separate torch ops because the fused kernel does not
+    take it (F not a multiple of 4 or above 1024, rows not 16-byte aligned)."""
+    if MODE == "fused" and (what, x.size(-1)) not in _warned:
+        _warned.add((what, x.size(-1)))
+        warnings.warn(f"norm.{what}: width {x.size(-1)} / this row alignment is outside the fused kernel's range; "
+                      "using the separate torch ops for it")
 
 
 def _partial(device, f: int) -> torch.Tensor:
@@ -77,6 +89,7 @@ def dropout_ln_relu(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor, p
     _lib.require_cuda(x, weight, bias)
     if supported(x) and weight is not None and bias is not None:
         return _DropoutLayerNormReLU.apply(x, weight, bias, p, training, eps)
+    _torch_path("dropout_ln_relu", x)
     x = F.dropout(x, p=p, training=training)
     return F.relu(F.layer_norm(x, (x.size(-1),), weight, bias, eps))
 
@@ -117,5 +130,6 @@ def relu_dropout_(x: torch.Tensor, p: float, training: bool) -> torch.Tensor:
     _lib.require_cuda(x)
     if supported(x):
         return _ReluDropout_.apply(x, p, training)
+    _torch_path("relu_dropout_", x)
     x = F.relu(x, inplace=True)
     return F.dropout(x, p=p, training=training) if p > 0 else x

@@ -10,6 +10,7 @@ import torch
 import torch.distributed as dist
 import torch.nn.functional as F
 
+from . import dense
 from .communicator import Communicator
 from .data_manager import load_data
 from .model import create_model_and_optimizer, set_random_seed
@@ -60,6 +61,7 @@ def train(model, data, optimizer, num_epochs, num_bits, eval_every_epoch=True, l
         optimizer.step()
         torch.cuda.synchronize()
         update_weight_end = time.perf_counter()
+        dense.check_status()  # a tensor-core kernel that gave up on a bounded wait left its output partly written
         losses.append(float(loss.detach()))
         times.append(update_weight_end - forward_start)
         train_acc = val_acc = test_acc = float("nan")
@@ -96,9 +98,6 @@ def main():
     data = load_data(config)
     TimeRecorder(config["num_layers"], config["num_epochs"], enabled=bool(config.get("record_phases", False)))
     train(model, data, optimizer, config["num_epochs"], config["num_bits"])
-    from . import dense
-
-    dense.check_status()  # raises if a tensor-core kernel gave up on one of its bounded waits
     TimeRecorder.ctx.print_total_time()
 
 

@@ -64,5 +64,8 @@ def build(ref_root: str, force: bool = False) -> str:
 
 
 if __name__ == "__main__":
-    root = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+    roots = [a for a in sys.argv[1:] if not a.startswith("--")]
+    root = roots[0] if roots else os.environ.get("GNNAGG_REFERENCE_ROOT")
+    if not root:
+        raise SystemExit("usage: python oracle/build_ref.py <reference_root> [--force]  (or set GNNAGG_REFERENCE_ROOT)")
     print(build(root, force="--force" in sys.argv))

@@ -145,7 +145,9 @@ def save_parts(out, begin, parts):
 
 
 def main():
-    ref_root = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+    ref_root = sys.argv[1] if len(sys.argv) > 1 else os.environ.get("GNNAGG_REFERENCE_ROOT")
+    if not ref_root:
+        raise SystemExit("usage: python tests/golden/make_golden.py <reference_root>  (or set GNNAGG_REFERENCE_ROOT)")
     ref = install_shims(ref_root)
     from data_manager.DataProcessor import DataProcessor, DataProcessorForPreAggresive
 

@@ -16,7 +16,7 @@ pytestmark = pytest.mark.gpu
 GOLD = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden")
 
 
-def _worker(rank, P, port, path, out_dir):
+def _worker(rank, P, port, path, out_dir, dense_mode="tf32x3"):
     import torch.distributed as dist
 
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
@@ -46,7 +46,9 @@ def _worker(rank, P, port, path, out_dir):
     from gnn_benchmark_b200.data_manager.DataLoader import build_graph
     from gnn_benchmark_b200.model import create_model_and_optimizer, set_random_seed
     from gnn_benchmark_b200.train import train
+    from gnn_benchmark_b200 import dense
 
+    dense.MODE = dense_mode
     g = np.load(path)
     cfg = {k: float(v) for k, v in zip(g["cfg_keys"], g["cfg_vals"])}
     for k in ("in_channels", "hidden_channels", "out_channels", "num_layers", "num_epochs", "random_seed", "num_bits"):
@@ -165,18 +167,17 @@ def test_gcn_configuration_1_against_reference_aggregator_run(cuda_lib, tmp_path
 @pytest.mark.parametrize("dense_mode", ["cublas", "tf32x3"])
 @pytest.mark.parametrize("path", sorted(glob.glob(os.path.join(GOLD, "train_sage_*.npz"))),
                          ids=lambda p: os.path.basename(p)[6:-4])
-def test_loss_curve_against_reference_run(cuda_lib, tmp_path, path, dense_mode, monkeypatch):
+def test_loss_curve_against_reference_run(cuda_lib, tmp_path, path, dense_mode):
     """dense_mode "tf32x3" (default): the layer's fp32 transforms and weight gradients on the tensor-core
     kernels (three TF32 products per fp32 product, separate accumulators for the main and the small
     products); "cublas": on torch's fp32 matmul.  Same bar for both: 1e-4 on every epoch."""
     import torch.multiprocessing as mp
 
-    monkeypatch.setenv("GNNAGG_DENSE", dense_mode)  # read by the spawned ranks at import
     tol = 1e-4
     g = np.load(path)
     P = sum(1 for k in g.files if k.endswith("_losses"))
     port = 29700 + (os.getpid() % 200)
-    mp.spawn(_worker, args=(P, port, path, str(tmp_path)), nprocs=P, join=True)
+    mp.spawn(_worker, args=(P, port, path, str(tmp_path), dense_mode), nprocs=P, join=True)
     for r in range(P):
         got = np.load(os.path.join(str(tmp_path), f"r{r}.npz"))
         assert bool(got["same_init"]), "seeded initial weights differ from the reference's"
