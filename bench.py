@@ -33,8 +33,10 @@ ROOT = os.path.dirname(os.path.abspath(__file__))
 if ROOT not in sys.path:
     sys.path.insert(0, ROOT)
 
-from gnn_benchmark_b200.benchlib import (EDGE_FACTOR, NCU_DRAM_BYTES_PER_LAUNCH, SCALE, SEED, WIDTHS, ClockSampler,  # noqa: E402
-                                         HostPipeline, measured_peak_gbs, spmm_algorithmic_bytes, workload_config)
+from benchlib import (EDGE_FACTOR, SCALE, SEED, WIDTHS, ClockSampler, HostPipeline, measured_peak_gbs,  # noqa: E402
+                      spmm_algorithmic_bytes, workload_config)
+
+NCU_DRAM_BYTES_PER_LAUNCH = {}
 
 # ------------------------------------------------------------------------------------------------
 def build_single_gpu_graph(device):
@@ -241,7 +243,7 @@ def run_epoch_leg():
     """The other half of the metric: full-batch epoch time of the products-shaped 3-layer GraphSAGE
     (2.45 M nodes, 61.9 M undirected Chung-Lu edges, 100 -> 256 -> 256 -> 47) on this GPU, measured by
     `gnn_benchmark_b200.bench_epoch` in a process of its own after this one has released its buffers."""
-    cmd = [sys.executable, "-m", "gnn_benchmark_b200.bench_epoch", "--model", "sage", "--nodes", "2450000",
+    cmd = [sys.executable, os.path.join(ROOT, "bench_epoch.py"), "--model", "sage", "--nodes", "2450000",
            "--edges", "61900000", "--in-channels", "100", "--hidden", "256", "--out-channels", "47",
            "--train-frac", "0.08", "--bits", "32", "--epochs", "5"]
     env = {k: v for k, v in os.environ.items() if k not in ("RANK", "LOCAL_RANK", "WORLD_SIZE")}
@@ -330,7 +332,7 @@ def main():
         raise SystemExit("bench.py needs a CUDA device: the aggregation path has no CPU fallback")
     world = int(os.environ.get("WORLD_SIZE", "1"))
     if world > 1 or args.gpus > 1:
-        from gnn_benchmark_b200.bench_multi import run_multi_gpu
+        from bench_multi import run_multi_gpu
 
         run_multi_gpu(args)
     else:

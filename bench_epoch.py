@@ -1,6 +1,6 @@
 """Full-batch epoch time of a GNN over the aggregation path, on synthetic power-law graphs.
 
-    torchrun --nproc-per-node N -m gnn_benchmark_b200.bench_epoch --model gcn --nodes 111000000 \\
+    torchrun --nproc-per-node N bench_epoch.py --model gcn --nodes 111000000 \\
         --edges 1600000000 --in-channels 128 --hidden 256 --out-channels 172 --layers 3 --bits 2
 
 Shapes: `--model sage --nodes 2450000 --edges 61900000 --in-channels 100 --hidden 256 --out-channels 47
@@ -16,16 +16,23 @@ import argparse
 import json
 import time
 
+import os
+import sys
+
 import torch
 import torch.distributed as dist
 
-from . import dense, graphgen
-from .communicator import Communicator
-from .data_manager.DataLoader import build_graph
-from .model import create_model_and_optimizer, set_random_seed
-from .quantizer import Quantizer_for_all_procs
-from .time_recorder import TimeRecorder
-from .train import train
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+from gnn_benchmark_b200 import dense, graphgen  # noqa: E402
+from gnn_benchmark_b200.communicator import Communicator  # noqa: E402
+from gnn_benchmark_b200.data_manager.DataLoader import build_graph  # noqa: E402
+from gnn_benchmark_b200.model import create_model_and_optimizer, set_random_seed  # noqa: E402
+from gnn_benchmark_b200.quantizer import Quantizer_for_all_procs  # noqa: E402
+from gnn_benchmark_b200.time_recorder import TimeRecorder  # noqa: E402
+from gnn_benchmark_b200.train import train  # noqa: E402
 
 
 def aggregation_passes(model_name: str, dims) -> int:
@@ -65,7 +72,7 @@ def main():
 
     dense.MODE = args.dense
     comm = Communicator(args.bits, is_async=True)
-    if "RANK" in __import__("os").environ:
+    if "RANK" in os.environ:
         rank, world = comm.init_dist_group("nccl")
     else:
         rank, world = 0, 1

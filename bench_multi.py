@@ -24,7 +24,7 @@ def _gcn_values(graph, comm, world):
     through one fp32 halo exchange of a single column."""
     import torch
 
-    from .aggregator import gather_rows
+    from gnn_benchmark_b200.aggregator import gather_rows
 
     n = graph.local_adj_t.sparse_size(0)
     dev = graph.local_adj_t.device
@@ -54,8 +54,8 @@ def _run_e2e(args, graph, widths, num_bits, is_pre, n, nnz_total, device):
     """The same step through Aggregator with this rank's features and output gradients in pinned
     HOST memory: per call copy the operand host->device, run, copy the result device->host, pipelined
     over three streams (bench.HostPipeline)."""
-    from . import benchlib as bench
-    from .aggregator import Aggregator
+    import benchlib as bench
+    from gnn_benchmark_b200.aggregator import Aggregator
 
     Fmax = max(widths)
     host_in = torch.empty(n, Fmax, pin_memory=True).normal_(generator=torch.Generator().manual_seed(1))
@@ -98,10 +98,10 @@ def _run_e2e(args, graph, widths, num_bits, is_pre, n, nnz_total, device):
 
 
 def run_multi_gpu(args):
-    from . import benchlib as bench
-    from . import Communicator, Quantizer_for_all_procs, TimeRecorder, graphgen
-    from .aggregator import Aggregator
-    from .data_manager.DataLoader import build_graph
+    import benchlib as bench
+    from gnn_benchmark_b200 import Communicator, Quantizer_for_all_procs, TimeRecorder, graphgen
+    from gnn_benchmark_b200.aggregator import Aggregator
+    from gnn_benchmark_b200.data_manager.DataLoader import build_graph
 
     num_bits = int(os.environ.get("GNNAGG_BENCH_BITS", "32"))  # halo format of the headline number
     is_pre = os.environ.get("GNNAGG_BENCH_PRE", "0") == "1"

@@ -49,25 +49,35 @@ def erdos_renyi_edges(n: int, m: int, seed: int = 0, device="cpu") -> Tuple[torc
     return src, dst
 
 
-def chung_lu_edges(n: int, m: int, gamma: float = 2.1, seed: int = 0, device="cpu",
-                   chunk: int = 1 << 26) -> Tuple[torch.Tensor, torch.Tensor]:
-    """m edges whose endpoints are drawn independently with probability proportional to the
-    expected degrees w_i ~ (i + i0)^(-1/(gamma-1)), w_max capped at sqrt(sum w)."""
-    g = _gen(seed, device)
+def _power_law_cdf(n: int, m: int, gamma: float, device) -> torch.Tensor:
+    """Integer cumulative weights of the Chung-Lu endpoint distribution: expected degrees
+    w_i ~ (i + 1)^(-1/(gamma-1)), scaled to sum 2m and capped at sqrt(2m), then put on a fixed-point
+    grid of about 2^52 units in total.  The running sum is taken over INTEGERS, so it is exact and the
+    same whatever order a parallel scan adds in: a floating-point prefix sum on the GPU differs in
+    the last bit from run to run, which at 10^8 vertices and 10^9 draws moves a dozen edges."""
     i = torch.arange(n, dtype=torch.float64, device=device)
     w = (i + 1.0).pow(-1.0 / (gamma - 1.0))
     w = w * (2.0 * m / w.sum())
     w = torch.clamp(w, max=math.sqrt(2.0 * m))
-    cdf = torch.cumsum(w, 0)
-    cdf = cdf / cdf[-1]
+    units = (w * (float(1 << 52) / float(w.sum()))).floor().to(torch.int64).clamp_(min=1)
+    return torch.cumsum(units, 0)
+
+
+def _draw_endpoints(cdf: torch.Tensor, k: int, g: torch.Generator) -> torch.Tensor:
+    """k vertex ids with probability proportional to the weights behind the integer `cdf`."""
+    u = torch.randint(0, int(cdf[-1]), (k,), generator=g, device=cdf.device, dtype=torch.int64)
+    return torch.searchsorted(cdf, u, right=True).clamp_(max=cdf.numel() - 1)
+
+
+def chung_lu_edges(n: int, m: int, gamma: float = 2.1, seed: int = 0, device="cpu",
+                   chunk: int = 1 << 26) -> Tuple[torch.Tensor, torch.Tensor]:
+    """m edges whose endpoints are drawn independently with probability proportional to the
+    expected degrees w_i ~ (i + 1)^(-1/(gamma-1)), w_max capped at sqrt(sum w)."""
+    g = _gen(seed, device)
+    cdf = _power_law_cdf(n, m, gamma, device)
     out = []
     for _ in range(2):
-        parts = []
-        for start in range(0, m, chunk):
-            k = min(chunk, m - start)
-            u = torch.rand(k, generator=g, device=device, dtype=torch.float64)
-            parts.append(torch.searchsorted(cdf, u).clamp_(max=n - 1))
-        out.append(torch.cat(parts))
+        out.append(torch.cat([_draw_endpoints(cdf, min(chunk, m - start), g) for start in range(0, m, chunk)]))
     return out[0], out[1]
 
 
@@ -172,13 +182,7 @@ def partitioned_in_edges(kind: str, n: int, n_edges: int, seed: int, rank: int, 
     g = _gen(seed, device)
     cdf = None
     if kind == "chung_lu":
-        i = torch.arange(n, dtype=torch.float64, device=device)
-        w = (i + 1.0).pow(-1.0 / (gamma - 1.0))
-        w = w * (2.0 * n_edges / w.sum())
-        w = torch.clamp(w, max=math.sqrt(2.0 * n_edges))
-        cdf = torch.cumsum(w, 0)
-        cdf = (cdf / cdf[-1]).to(torch.float64)
-        del i, w
+        cdf = _power_law_cdf(n, n_edges, gamma, device)
     keys = []
     for start in range(0, n_edges, chunk):
         m = min(chunk, n_edges - start)
@@ -191,8 +195,8 @@ def partitioned_in_edges(kind: str, n: int, n_edges: int, seed: int, rank: int, 
                 src = (src << 1) | (r >= (a + b)).to(torch.int64)
                 dst = (dst << 1) | (((r >= a) & (r < a + b)) | (r >= a + b + c)).to(torch.int64)
         elif kind == "chung_lu":
-            src = torch.searchsorted(cdf, torch.rand(m, generator=g, device=device, dtype=torch.float64)).clamp_(max=n - 1)
-            dst = torch.searchsorted(cdf, torch.rand(m, generator=g, device=device, dtype=torch.float64)).clamp_(max=n - 1)
+            src = _draw_endpoints(cdf, m, g)
+            dst = _draw_endpoints(cdf, m, g)
         else:
             raise ValueError(kind)
         keep = src != dst

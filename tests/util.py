@@ -67,3 +67,22 @@ def dropout_keep_bits(rows, chunks, seed, p):
     for i, d in enumerate(draws):
         bits |= ((d >= thresh).astype(np.uint8) << i)
     return bits
+
+
+def synthetic_problem(cfg, device="cpu"):
+    """Graph, features, labels and train mask of a scaled BASELINE configuration, from the seeds in
+    `cfg` (nodes, edges, P, dims, graph_seed, self_loops, train_frac).  Used by the script that runs the
+    reference (tests/golden/make_config_golden.py) and by the tests that replay its runs, so that both
+    sides see exactly the same inputs."""
+    from gnn_benchmark_b200 import graphgen
+
+    n, P = cfg["nodes"], cfg["P"]
+    src, dst = graphgen.chung_lu_edges(n, cfg["edges"], gamma=2.1, seed=cfg["graph_seed"], device=device)
+    src, dst = graphgen.relabel(src, dst, n, cfg["graph_seed"] + 7)
+    src, dst = graphgen.symmetrize(src, dst, n, self_loops=bool(cfg["self_loops"]))
+    begin = graphgen.contiguous_partitions(n, P)
+    g = torch.Generator().manual_seed(cfg["graph_seed"] + 1)
+    X = torch.randn(n, cfg["dims"][0], generator=g)
+    labels = torch.randint(0, cfg["dims"][-1], (n,), generator=g)
+    train_mask = torch.rand(n, generator=g) < cfg["train_frac"]
+    return src, dst, begin, X, labels, train_mask
