@@ -1,24 +1,26 @@
 """Benchmark of the graph-aggregation hot path on B200.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference] [--scale S] [--widths 32,128,256]
 
 N = 1  workload "spmm_rmat22": the single-GPU SpMM microbenchmark -- R-MAT scale 22, edge factor
        16, (a,b,c,d) = (.57,.19,.19,.05), symmetrised, deduplicated, self-loops, GCN-normalised
        fp32 CSR values, int32 columns, int64 row pointers; one step = forward A.X and transposed
        A^T.G at feature widths 32, 128 and 256 (six SpMM calls).
-N > 1  workload "aggregate_rmat22_per_gpu": the same graph family with 2^22 vertices per GPU,
-       randomly relabelled and cut into N contiguous partitions; one step = Aggregator forward +
-       backward (halo exchange over NCCL overlapped with the local SpMM) at the same three widths.
+N > 1  workload "aggregate_rmat22_per_gpu" (bench_multi.py): the same graph family with 2^22 vertices
+       per GPU, randomly relabelled and cut into N contiguous partitions; one step = Aggregator forward
+       + backward (halo exchange overlapped with the SpMMs) at the same three widths.
 
 Prints ONE JSON line (rank 0).  `value` = aggregated edges per second over the whole job with
 inputs resident in HBM; `e2e` = the same metric through the public call with pinned HOST buffers,
-H2D/D2H copies inside the timed region; `roofline` = algorithmic bytes of the widest SpMM launch
-over its CUDA-event time, against the measured HBM copy bandwidth; `cpu_baseline` = the
-reference's own CPU SpMM (compiled from its sources when available, else the C port) timed on
-this box's host cores on a stated sample.
+H2D/D2H copies inside the timed region; `roofline` = the SpMM launches of the widest feature width:
+algorithmic bytes (no-reuse gather model), compulsory bytes and measured DRAM traffic, each over the
+CUDA-event time and against the measured HBM copy bandwidth; `cpu_baseline` = the reference's own
+CPU SpMM (compiled from its sources when available, else the C port) timed on this box's host cores
+on a stated sample; `epoch` = full-batch epoch time of the products-shaped GraphSAGE (bench_epoch.py).
 
---impl reference times only that CPU implementation, same metric and workload, and prints the
-same line with "impl": "reference".
+--impl reference (bench_reference.py) times only the reference's CPU implementation, same metric and
+workload family, and prints the same line with "impl": "reference".
+--scale / --widths choose a smaller case (profiler captures); they are echoed into `config`.
 """
 import argparse
 import json
@@ -33,17 +35,15 @@ ROOT = os.path.dirname(os.path.abspath(__file__))
 if ROOT not in sys.path:
     sys.path.insert(0, ROOT)
 
-from benchlib import (EDGE_FACTOR, SCALE, SEED, WIDTHS, ClockSampler, HostPipeline, measured_peak_gbs,  # noqa: E402
-                      spmm_algorithmic_bytes, workload_config)
+import benchlib  # noqa: E402
+from benchlib import EDGE_FACTOR, SEED, ClockSampler, HostPipeline, measured_peak_gbs  # noqa: E402
 
-NCU_DRAM_BYTES_PER_LAUNCH = {}
 
-# ------------------------------------------------------------------------------------------------
-def build_single_gpu_graph(device):
+def build_single_gpu_graph(device, scale):
     from gnn_benchmark_b200 import SparseTensor, graphgen
 
-    n = 1 << SCALE
-    s, d = graphgen.rmat_edges(SCALE, EDGE_FACTOR, seed=SEED, device=device)
+    n = 1 << scale
+    s, d = graphgen.rmat_edges(scale, EDGE_FACTOR, seed=SEED, device=device)
     s, d = graphgen.symmetrize(s, d, n)
     rowptr, col, val = graphgen.csr_from_edges(s, d, n, n, gcn_normalize=True)
     del s, d
@@ -54,99 +54,13 @@ def build_single_gpu_graph(device):
     return A
 
 
-def cpu_reference_spmm(rowptr, col64, val, X, out, splits, ref_mod):
-    """One accumulating SpMM on the host: the reference's compiled kernel, or the C port."""
-    import oracle
-
-    if ref_mod is not None:
-        M = rowptr.numel() - 1
-        ref_mod.spmm(rowptr, col64, val, X, out, M, splits, torch.tensor([0, X.size(1)], dtype=torch.int32))
-    else:
-        oracle.spmm(rowptr.numpy(), col64.numpy(), val.numpy(), X.numpy(), out.numpy())
-
-
-class CpuArm:
-    """The reference's CPU SpMM on this box's host cores.  Sample = forward + transposed product at
-    F = 128 on the full benchmark graph (2 of the 6 calls of a step; 520 of the step's mean 563
-    algorithmic bytes per edge)."""
-    SAMPLE_F = 128
-
-    def __init__(self, A):
-        import oracle
-
-        self.ref_mod = oracle.load_reference_module()
-        self.kind = "reference" if self.ref_mod is not None else "port"
-        self.cores = torch.get_num_threads() if self.ref_mod is not None else oracle.num_threads()
-        rowptr, col, val = A.csr()
-        self.fwd = (rowptr.cpu(), col.cpu().to(torch.int64), val.cpu())
-        self.bwd = (A.storage.colptr().cpu(), A.storage.row_T().cpu().to(torch.int64), A.storage.value_T().cpu())
-        self.nnz = A.nnz()
-        n = A.sparse_size(0)
-        g = torch.Generator().manual_seed(SEED)
-        self.X = torch.randn(n, self.SAMPLE_F, generator=g)
-        self.out = torch.zeros(n, self.SAMPLE_F)
-        ones = torch.ones(self.nnz)
-        self.splits = [torch.from_numpy(oracle.distribute_work_for_row(t[0].numpy(), ones.numpy(), self.cores))
-                       for t in (self.fwd, self.bwd)]
-        self.sample = (f"forward + transposed SpMM at F={self.SAMPLE_F} on the full R-MAT scale-{SCALE} graph "
-                       f"({2 * self.nnz} edges per step)")
-
-    def step(self):
-        for (rp, c, v), sp in zip((self.fwd, self.bwd), self.splits):
-            cpu_reference_spmm(rp, c, v, self.X, self.out, sp, self.ref_mod)
-        return 2 * self.nnz
-
-    def run(self, steps, warmup):
-        for _ in range(warmup):
-            self.step()
-        t0 = time.perf_counter()
-        edges = 0
-        for _ in range(steps):
-            edges += self.step()
-        dt = time.perf_counter() - t0
-        return edges / dt, dt / steps
-
-
-def run_reference_arm(args):
-    rank = int(os.environ.get("RANK", "0"))
-    if rank != 0:
-        return
-    device = torch.device("cuda", 0) if torch.cuda.is_available() else torch.device("cpu")
-    A = build_single_gpu_graph(device) if device.type == "cuda" else _cpu_graph()
-    arm = CpuArm(A)
-    value, sec_per_step = arm.run(args.steps, args.warmup)
-    line = {
-        "impl": "reference", "metric": "aggregated_edges_per_s", "value": value, "unit": "edges/s",
-        "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": sec_per_step * 1e3,
-        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": workload_config(args.gpus, A),
-        "cpu_baseline": {"value": value, "unit": "edges/s", "cores": arm.cores, "kind": arm.kind,
-                         "sample": arm.sample},
-        "e2e": {"value": value, "unit": "edges/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
-        "gpu_launches": 0,
-    }
-    print(json.dumps(line), flush=True)
-
-
-def _cpu_graph():
-    from gnn_benchmark_b200 import SparseTensor, graphgen
-
-    n = 1 << SCALE
-    s, d = graphgen.rmat_edges(SCALE, EDGE_FACTOR, seed=SEED, device="cpu")
-    s, d = graphgen.symmetrize(s, d, n)
-    rowptr, col, val = graphgen.csr_from_edges(s, d, n, n, gcn_normalize=True)
-    A = SparseTensor(rowptr=rowptr, col=col, value=val, sparse_sizes=(n, n))
-    A.storage.colptr()
-    return A
-
-
-# ------------------------------------------------------------------------------------------------
 def run_single_gpu(args):
     from gnn_benchmark_b200 import SPMM_backward, SPMM_forward
 
+    WIDTHS = args.widths
     device = torch.device("cuda", 0)
     torch.cuda.set_device(device)
-    A = build_single_gpu_graph(device)
+    A = build_single_gpu_graph(device, args.scale)
     n, nnz = A.sparse_size(0), A.nnz()
     g = torch.Generator(device=device).manual_seed(SEED)
     X = {F: torch.randn(n, F, device=device, generator=g) for F in WIDTHS}
@@ -159,7 +73,8 @@ def run_single_gpu(args):
             SPMM_backward(A, G[F], Y[F], accumulate=False)
 
     launches_per_step = 2 * 2 * len(WIDTHS)  # chunk kernel + fix-up kernel per call
-    for _ in range(max(args.warmup, 3)):
+    warmup = max(args.warmup, 3)
+    for _ in range(warmup):
         step()
     torch.cuda.synchronize()
 
@@ -182,7 +97,8 @@ def run_single_gpu(args):
     value = 2 * len(WIDTHS) * nnz / t_step
 
     # ---- per-launch timing of every width (roofline) ----
-    per_width = {}
+    peak, peak_kind = measured_peak_gbs()
+    by_width = {}
     for F in WIDTHS:
         times = []
         for fn, src in ((SPMM_forward, X), (SPMM_backward, G)):
@@ -193,45 +109,59 @@ def run_single_gpu(args):
                 b.record()
                 torch.cuda.synchronize()
                 times.append(a.elapsed_time(b) / 1e3)
-        avg = sum(times) / len(times)
-        by = spmm_algorithmic_bytes(n, nnz, F)
-        per_width[F] = {"ms": avg * 1e3, "algorithmic_bytes": by, "gbs": by / avg / 1e9,
-                        "edges_per_s": nnz / avg}
-    peak, peak_kind = measured_peak_gbs()
-    top = max(WIDTHS, key=lambda F: per_width[F]["ms"])
+        t = sum(times) / len(times)
+        alg = benchlib.spmm_algorithmic_bytes(n, nnz, F)
+        b_min = benchlib.spmm_compulsory_bytes(n, n, nnz, F)
+        traffic = benchlib.spmm_dram_traffic(args.scale, F)
+        by_width[F] = {
+            "ms": round(t * 1e3, 4), "edges_per_s": nnz / t,
+            "algorithmic": alg, "b_min": b_min, "traffic": traffic,
+            "algorithmic_gbs": round(alg / t / 1e9, 1), "frac_algorithmic": round(alg / t / 1e9 / peak, 4),
+            "frac_b_min": round(b_min / t / 1e9 / peak, 4),
+            "traffic_gbs": None if traffic is None else round(traffic / t / 1e9, 1),
+            "frac_traffic": None if traffic is None else round(traffic / t / 1e9 / peak, 4),
+        }
+    top = max(WIDTHS, key=lambda F: by_width[F]["ms"])
+    w = by_width[top]
     roofline = {
         "bound": "hbm", "kernel": f"spmm_chunk_kernel (F={top}, forward and transposed launches averaged)",
-        "achieved": per_width[top]["gbs"], "peak": peak, "unit": "GB/s", "frac": per_width[top]["gbs"] / peak,
-        "peak_kind": peak_kind + " copy bandwidth, burst",
-        "traffic": NCU_DRAM_BYTES_PER_LAUNCH.get(top) if SCALE == 22 else None,
-        "traffic_gbs": (NCU_DRAM_BYTES_PER_LAUNCH[top] / (per_width[top]["ms"] / 1e3) / 1e9
-                        if SCALE == 22 and top in NCU_DRAM_BYTES_PER_LAUNCH else None),
-        "by_width": {str(F): {"ms": round(per_width[F]["ms"], 4), "gbs": round(per_width[F]["gbs"], 1),
-                              "frac": round(per_width[F]["gbs"] / peak, 4)} for F in WIDTHS},
+        "achieved": w["algorithmic"] / (w["ms"] / 1e3) / 1e9, "peak": peak, "unit": "GB/s",
+        # the physical fraction: DRAM bytes the launch moved (ncu) over its CUDA-event time; the algorithmic
+        # figure counts a gathered row per nonzero and exceeds the peak where L2 serves the hub rows
+        "frac": w["frac_traffic"] if w["frac_traffic"] is not None else w["frac_algorithmic"],
+        "frac_is": ("dram traffic / event time / peak" if w["frac_traffic"] is not None
+                    else "algorithmic bytes / event time / peak (no DRAM capture for this kernel source)"),
+        "frac_algorithmic": w["frac_algorithmic"], "frac_b_min": w["frac_b_min"],
+        "peak_kind": peak_kind + " copy bandwidth, burst", "traffic": w["traffic"], "b_min": w["b_min"],
+        "traffic_source": ("ncu dram__bytes_read.sum + dram__bytes_write.sum of one launch on this workload, kernel "
+                           "source " + str(benchlib.SPMM_DRAM_TRAFFIC["kernel_source"])),
+        "by_width": {str(F): by_width[F] for F in WIDTHS},
     }
 
     # ---- end to end through the public call with pinned host buffers ----
     e2e = None if args.no_e2e else run_e2e_single(A, args, device)
+    if e2e is not None:
+        e2e["note"] = ("bound by the host link: every call moves its dense operand in and its result out over PCIe "
+                       "(bytes above), the kernels are a sixth of the step")
 
     # ---- CPU baseline on the host cores ----
     del X, G, Y
+    config = benchlib.workload_config(1, args.scale, WIDTHS, A)
+    del A
     torch.cuda.empty_cache()
     cpu = None
     if not args.no_cpu_baseline:
-        arm = CpuArm(A)
-        v, _ = arm.run(steps=2, warmup=1)
-        cpu = {"value": v, "unit": "edges/s", "cores": arm.cores, "kind": arm.kind, "sample": arm.sample}
+        import bench_reference
 
-    config = workload_config(1, A)
-    epoch = None
-    if not args.no_epoch:
-        del A
-        torch.cuda.empty_cache()
-        epoch = run_epoch_leg()
+        arm = bench_reference.SpmmArm(args.scale, bench_reference.host_threads())
+        v, _ = bench_reference._timed(arm.step, 2, 1)
+        cpu = {"value": v, "unit": "edges/s", "cores": arm.threads, "kind": arm.kind, "sample": arm.sample}
+        del arm
 
+    epoch = None if args.no_epoch else run_epoch_leg()
     line = {
         "metric": "aggregated_edges_per_s", "value": value, "unit": "edges/s", "n_gpus": 1, "steps": args.steps,
-        "warmup": max(args.warmup, 3), "ms_per_step": t_step * 1e3, "higher_is_better": True, "scaling": "weak",
+        "warmup": warmup, "ms_per_step": t_step * 1e3, "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "f32", "data": "synthetic", "config": config,
         "clocks": clocks, "e2e": e2e, "gpu_launches": launches_per_step * args.steps, "roofline": roofline,
         "cpu_baseline": cpu, "epoch": epoch,
@@ -268,6 +198,7 @@ def run_e2e_single(A, args, device):
     matrix (the graph) stays resident, as it does in the reference, which caches it on the SparseTensor."""
     from gnn_benchmark_b200 import SPMM_backward, SPMM_forward
 
+    WIDTHS = args.widths
     n, nnz = A.sparse_size(0), A.nnz()
     Fmax = max(WIDTHS)
     host_in = torch.empty(n, Fmax, pin_memory=True)
@@ -310,19 +241,34 @@ def run_e2e_single(A, args, device):
     return out
 
 
+def _widths(text):
+    return tuple(int(w) for w in text.split(","))
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=10)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", type=str, default="ours", choices=["ours", "reference"])
+    ap.add_argument("--scale", type=int, default=benchlib.SCALE,
+                    help="log2 of the vertices per GPU (22 is the benchmark; smaller only for profiler captures)")
+    ap.add_argument("--widths", type=_widths, default=benchlib.WIDTHS, help="feature widths of a step, comma-separated")
+    ap.add_argument("--bits", type=int, default=32, choices=[32, 16, 8, 4, 2],
+                    help="N > 1: halo format of the headline value (the 2-bit value is always reported beside it)")
+    ap.add_argument("--pre", action="store_true", help="N > 1: pre/post-aggregation plan instead of the plain halo")
+    ap.add_argument("--exchange", default="pipelined", choices=["pipelined", "all_to_all"],
+                    help="N > 1: peer-by-peer exchange with each peer's rows aggregated on arrival, or one all-to-all")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer leg (profiler captures)")
-    ap.add_argument("--no-epoch", action="store_true", help="skip the full-batch epoch leg (N = 1 only)")
+    ap.add_argument("--no-epoch", action="store_true", help="skip the full-batch epoch legs")
+    ap.add_argument("--no-check", action="store_true", help="N > 1: skip the correctness check of the exchange path")
     args = ap.parse_args()
 
     if args.impl == "reference":
-        run_reference_arm(args)
+        import bench_reference
+
+        bench_reference.run(args)
         return
     from gnn_benchmark_b200 import _lib, build
 

@@ -1,5 +1,6 @@
 """Pieces shared by the benchmark drivers beside this file (bench.py, bench_multi.py, bench_epoch.py):
 workload constants, roofline arithmetic, the nvidia-smi clock sampler and the three-stream host pipeline."""
+import hashlib
 import json
 import os
 import statistics
@@ -30,8 +31,38 @@ def measured_peak_gbs():
 
 
 def spmm_algorithmic_bytes(M, nnz, F, accumulate=False, rowptr_bytes=8):
-    """nnz*(4 col + 4 val + 4F gathered row) + (M+1)*rowptr + M*F*4 written (+ read when accumulating)."""
+    """nnz*(4 col + 4 val + 4F gathered row) + (M+1)*rowptr + M*F*4 written (+ read when accumulating):
+    the no-reuse gather model (every nonzero fetches its feature row from memory)."""
     return nnz * (8 + 4 * F) + (M + 1) * rowptr_bytes + M * F * 4 * (2 if accumulate else 1)
+
+
+def spmm_compulsory_bytes(M, K, nnz, F, accumulate=False, rowptr_bytes=8):
+    """Lower bound: the index and value streams, every feature row of the operand once, the output once."""
+    return nnz * 8 + (M + 1) * rowptr_bytes + K * F * 4 + M * F * 4 * (2 if accumulate else 1)
+
+
+def spmm_kernel_source_hash():
+    """Identifies the SpMM kernel a DRAM-traffic capture belongs to: sha256 over its two source files."""
+    h = hashlib.sha256()
+    for name in ("spmm.cu", "common.cuh"):
+        with open(os.path.join(ROOT, "gnn_benchmark_b200", "csrc", name), "rb") as f:
+            h.update(f.read())
+    return h.hexdigest()[:16]
+
+
+# dram__bytes_read.sum + dram__bytes_write.sum of ONE spmm_chunk_kernel launch (ncu), keyed by R-MAT scale
+# and feature width, with the hash of the kernel source the capture was taken on.  A bench run on other
+# kernel source reports `traffic: null` instead of a stale figure.
+SPMM_DRAM_TRAFFIC = {
+    "kernel_source": None,
+    "bytes_per_launch": {},
+}
+
+
+def spmm_dram_traffic(scale, F):
+    if SPMM_DRAM_TRAFFIC["kernel_source"] != spmm_kernel_source_hash():
+        return None
+    return SPMM_DRAM_TRAFFIC["bytes_per_launch"].get((scale, F))
 
 
 class ClockSampler:
@@ -96,12 +127,12 @@ class ClockSampler:
         return out
 
 
-def workload_config(n_gpus, A=None):
+def workload_config(n_gpus, scale=SCALE, widths=WIDTHS, A=None):
     cfg = {
-        "workload": "spmm_rmat22" if n_gpus == 1 else "aggregate_rmat22_per_gpu",
-        "graph": f"R-MAT scale {SCALE}{'' if n_gpus == 1 else ' per GPU'}, edge factor {EDGE_FACTOR}, "
+        "workload": f"spmm_rmat{scale}" if n_gpus == 1 else f"aggregate_rmat{scale}_per_gpu",
+        "graph": f"R-MAT scale {scale}{'' if n_gpus == 1 else ' per GPU'}, edge factor {EDGE_FACTOR}, "
                  "(a,b,c,d)=(0.57,0.19,0.19,0.05), symmetrised, deduplicated, self-loops, GCN-normalised",
-        "widths": list(WIDTHS),
+        "widths": list(widths),
         "calls_per_step": "forward A.X + transposed A^T.G per width",
         "index_types": "int64 rowptr, int32 col, fp32 val",
         "l2_policy": "inputs_larger_than_L2 (X is 0.5-4.3 GB, CSR 1.1 GB; nothing flushed between steps)",

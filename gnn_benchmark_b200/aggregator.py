@@ -7,8 +7,9 @@ forward  out = A_local @ x  +  A_remote @ halo(x)          (aggregator.py:17-119
 backward grad = A_local^T @ g + scatter(halo^T(A_remote^T @ g))   (aggregator.py:121-208)
 
 Per call, on the current (compute) stream unless noted:
-  1. fill the send side: pre-aggregation SpMM (pre/post path), row gather, or -- quantised
-     plain path -- gather fused into the quantise+pack kernel (no fp32 send buffer is written);
+  1. fill the send side: pre-aggregation SpMM (pre/post path) or row gather; with a packed halo the
+     quantise + pack step is the epilogue of that SpMM / fused with that gather, so no fp32 send
+     buffer is written (backward: the transposed receive-side SpMM packs its rows the same way);
   2. start the exchange (Communicator; runs on the NCCL stream);
   3. local SpMM, overlapping the exchange;
   4. make the compute stream wait for the exchange, unpack + dequantise if it was packed;
@@ -22,7 +23,8 @@ import torch.distributed as dist
 from . import _lib
 from .communicator import Communicator
 from .quantizer import Quantizer_for_all_procs
-from .spmm_kernel import SPMM_backward, SPMM_backward_packed, SPMM_forward, SPMM_forward_packed
+from .spmm_kernel import (SPMM_backward, SPMM_backward_packed, SPMM_backward_quant_pack, SPMM_forward,
+                          SPMM_forward_packed, SPMM_forward_quant_pack, quant_pack_fusable)
 from .time_recorder import TimeRecorder
 
 
@@ -30,6 +32,10 @@ from .time_recorder import TimeRecorder
 # into the fp32 halo buffer first (same result bit for bit; the fp32 buffer is then left untouched).
 # Set to False to get the reference's two-step sequence, e.g. to inspect comm_buf.recv_buf.
 FUSE_UNPACK = True
+# Packed halo modes: quantise + pack as the epilogue of the SpMM that produces the rows to send (forward:
+# pre-aggregation; backward: transposed receive-side matrix), so comm_buf.send_buf / recv_buf are not
+# written.  Set to False for the reference's two-step sequence.
+FUSE_PACK = True
 
 
 def _world_size() -> int:
@@ -94,38 +100,9 @@ def _remote_parts(graph, world_size):
     return parts
 
 
-# Packed halo, backward: transposed remote SpMM and packing done peer by peer (always on when the
-# graph's CommBuffer is lean).
-PACK_PER_PEER = False
-
-
-def _pack_halo_gradients_per_peer(graph, g, world_size) -> None:
-    from .quantizer import _quant_pack
-
-    q = graph.comm_buf_for_quantization
-    bits = Quantizer_for_all_procs.ctx._bits()
-    epb = 8 // bits
-    parts = _remote_parts(graph, world_size)
-    offs = _prefix(graph.comm_splits.recv_splits)
-    poffs = _prefix(graph.comm_splits.recv_splits_int2)
-    feat_len = g.size(-1)
-    biggest = max(graph.comm_splits.recv_splits) if graph.comm_splits.recv_splits else 0
-    if biggest == 0:
-        return
-    scratch = torch.empty((biggest, feat_len), dtype=torch.float32, device=g.device)
-    segs = getattr(graph, "_one_peer_segs", None)
-    if segs is None:
-        segs = [torch.tensor([0, n], dtype=torch.int32, device=g.device) for n in graph.comm_splits.recv_splits]
-        graph._one_peer_segs = segs
-    for p in range(world_size):
-        n_p = offs[p + 1] - offs[p]
-        if n_p == 0:
-            continue
-        block = scratch[:n_p]
-        SPMM_backward(parts[p], g, block, accumulate=False)
-        _quant_pack(block, q.quantized_recv_data_buf[poffs[p]:poffs[p + 1]],
-                    q.quantized_recv_params_buf_fp32[offs[p]:offs[p + 1]], segs[p], 1, bits,
-                    params_bf16=q.quantized_recv_params_buf_bf16[offs[p]:offs[p + 1]])
+def _push_transport(graph) -> bool:
+    comm = Communicator.ctx
+    return comm is not None and comm.transport == "push" and getattr(graph, "push_plan", None) is not None
 
 
 def _pipelined(num_bits, is_pre_delay, is_training, world_size) -> bool:
@@ -156,6 +133,14 @@ class Aggregator(torch.autograd.Function):
 
         comm_handle = None
         rounds = None
+        if world_size > 1 and _push_transport(graph):
+            from . import aggregator_push
+
+            out = aggregator_push.forward(graph, x, feat_len, num_bits, is_pre_delay, packed, world_size, rec)
+            if rec:
+                rec.record_total_convolution_time(t_total)
+                rec.next_layer()
+            return out
         if _pipelined(num_bits, is_pre_delay, is_training, world_size):
             # peer-by-peer exchange: every peer's rows are aggregated as soon as they are in
             t = rec.start() if rec else None
@@ -171,7 +156,13 @@ class Aggregator(torch.autograd.Function):
             send_buf = graph.comm_buf.send_buf
             q = graph.comm_buf_for_quantization
             fused_pack = False
-            if is_pre_delay:  # pre-aggregation: partial sums for remote destinations, raw rows for post sources
+            if is_pre_delay and packed and FUSE_PACK and quant_pack_fusable(x):
+                # pre-aggregation with the quantise + pack step as its epilogue
+                SPMM_forward_quant_pack(graph.adj_t_pre_post_aggr_to, x, q.quantized_send_data_buf,
+                                        q.quantized_send_params_buf_fp32, q.quantized_send_params_buf_bf16,
+                                        q.quantized_work_range_per_proc, world_size, Quantizer_for_all_procs.ctx._bits())
+                fused_pack = True
+            elif is_pre_delay:  # pre-aggregation: partial sums for remote destinations, raw rows for post sources
                 SPMM_forward(graph.adj_t_pre_post_aggr_to, x, send_buf, accumulate=False)
             elif packed:      # gather fused into quantise + pack
                 Quantizer_for_all_procs.ctx.quantize_fp32_to_intX(
@@ -183,7 +174,8 @@ class Aggregator(torch.autograd.Function):
             if rec:
                 rec.record_prepare_comm_time(t)
             if lean and not fused_pack:
-                raise RuntimeError("lean halo buffers need the plain (not pre/post) path with a packed halo")
+                raise RuntimeError("lean halo buffers need a packed halo and feature rows the fused pack kernels take "
+                                   "(F a multiple of 4, at most 512, 16-byte aligned rows)")
             if fused_pack:
                 comm_handle = Communicator.ctx.comm_with_int2_quantization_for_all_procs(
                     graph.comm_splits, graph.comm_buf, q, "forward", already_quantized=True)
@@ -260,6 +252,14 @@ class Aggregator(torch.autograd.Function):
 
         comm_handle = None
         rounds = None
+        if world_size > 1 and _push_transport(graph):
+            from . import aggregator_push
+
+            grad = aggregator_push.backward(graph, g, feat_len, num_bits, is_pre_delay, packed, world_size, rec)
+            if rec:
+                rec.record_total_convolution_time(t_total)
+                rec.next_layer()
+            return None, grad, None, None, None, None
         if _pipelined(num_bits, is_pre_delay, True, world_size):
             # the block of halo gradients that goes back to a peer is computed right before its round
             _resize(graph, feat_len, num_bits)
@@ -276,19 +276,26 @@ class Aggregator(torch.autograd.Function):
                                                        before_send=make_block)
             if rec:
                 rec.record_pre_aggregate_time(t)
-        elif world_size > 1 and packed and FUSE_UNPACK and not is_pre_delay and feat_len % 4 == 0 \
-                and (getattr(graph.comm_buf, "lean", False) or PACK_PER_PEER):
-            # halo gradients are produced and packed one peer at a time through a peer-sized scratch, so
-            # the full fp32 halo buffer is never needed (same codes: packing groups restart per peer)
+        elif world_size > 1 and packed and FUSE_PACK and quant_pack_fusable(g):
+            # halo gradients: the transposed receive-side SpMM packs its rows in its epilogue, so the fp32
+            # halo buffer is never needed (the receive-side buffers are the ones sent: the roles swap)
             _resize(graph, feat_len, num_bits)
             t = rec.start() if rec else None
-            _pack_halo_gradients_per_peer(graph, g, world_size)
+            q = graph.comm_buf_for_quantization
+            adj = graph.adj_t_pre_post_aggr_from if is_pre_delay else graph.remote_adj_t
+            if sum(graph.comm_splits.recv_splits) != 0:
+                SPMM_backward_quant_pack(adj, g, q.quantized_recv_data_buf, q.quantized_recv_params_buf_fp32,
+                                         q.quantized_recv_params_buf_bf16, q.dequantized_work_range_per_proc,
+                                         world_size, Quantizer_for_all_procs.ctx._bits())
             if rec:
                 rec.record_pre_aggregate_time(t)
             comm_handle = Communicator.ctx.comm_with_int2_quantization_for_all_procs(
                 graph.comm_splits, graph.comm_buf, graph.comm_buf_for_quantization, "backward",
                 already_quantized=True)
         elif world_size > 1:
+            if getattr(graph.comm_buf, "lean", False):
+                raise RuntimeError("lean halo buffers need a packed halo and gradient rows the fused pack kernel takes "
+                                   "(F a multiple of 4, at most 512, 16-byte aligned rows)")
             _resize(graph, feat_len, num_bits)
             # the two buffers swap roles: recv_buf is sent, send_buf receives
             remote_nodes_grad_buf = graph.comm_buf.recv_buf

@@ -38,10 +38,23 @@ class _Handles(object):
 class Communicator(object):
     ctx = None
 
-    def __init__(self, num_bits=32, is_async=True, use_barrier=False, pipeline_peers=False) -> None:
+    def __init__(self, num_bits=32, is_async=True, use_barrier=False, pipeline_peers=False, transport="all_to_all",
+                 push_groups=3) -> None:
+        """transport (an addition): "all_to_all" -- the reference's exchange, one collective per aggregation
+        (NCCL here); "push" -- rows are stored straight into the receivers' buffers over NVLink by the
+        kernel that gathers / produces them (peer.py, aggregator_push.py; one node, NCCL process group).
+        push_groups: with the fp32 halo on the plain path the peers are served in this many groups, the
+        receive-side SpMM of one group overlapping the stores of the next; 1 keeps the ascending-peer
+        summation order of the all-to-all path."""
+        if transport not in ("all_to_all", "push"):
+            raise ValueError("transport must be 'all_to_all' or 'push'")
         self.num_bits = num_bits
         self.is_async = is_async
         self.use_barrier = use_barrier
+        self.transport = transport
+        self.push_groups = int(push_groups)
+        self._peers = None
+        self._push_streams = {}
         # fp32 halo only: exchange peer by peer and aggregate each peer's rows as they arrive (see
         # exchange_by_peer).  Off by default because the peers' contributions are then added in arrival
         # order, not in the reference's ascending-peer order (same terms, fp32 re-association).
@@ -69,6 +82,26 @@ class Communicator(object):
         self.world_size = dist.get_world_size()
         self.rank = dist.get_rank()
         return (self.rank, self.world_size)
+
+    def peers(self):
+        """The peer-memory service of the push transport (created on first use; tests install their own)."""
+        if self._peers is None:
+            from .peer import NcclPeers
+
+            self._peers = NcclPeers(torch.device("cuda", torch.cuda.current_device()))
+        return self._peers
+
+    def push_stream(self, device):
+        """Side stream of the push transport's stores (high priority: they must get onto the SMs while the
+        local SpMM keeps them busy); one per device and host thread."""
+        import threading
+
+        key = (torch.device(device).index, threading.get_ident())
+        s = self._push_streams.get(key)
+        if s is None:
+            s = torch.cuda.Stream(device=device, priority=-1)
+            self._push_streams[key] = s
+        return s
 
     # ---------------------------------------------------------------------------------------
     def comm(self, comm_splits, comm_buf, comm_buf_for_quantization, layer, is_training, direction):
@@ -199,13 +232,37 @@ class Communicator(object):
                 rec.record_quantization_time(t)
         self._barrier()
         t = rec.start() if rec else None
-        h_params = dist.all_to_all_single(recv_params_bf16, send_params_bf16, recv_splits, send_splits,
-                                          async_op=self.is_async)
-        h_data = dist.all_to_all_single(quantized_recv_data_buf, quantized_send_data_buf, recv_splits_int2,
-                                        send_splits_int2, async_op=self.is_async)
+        handle = self._exchange_together([
+            (recv_params_bf16, send_params_bf16, recv_splits, send_splits),
+            (quantized_recv_data_buf, quantized_send_data_buf, recv_splits_int2, send_splits_int2)])
         if rec:
             rec.record_communication_time(t)
-        return _Handles([h_params, h_data])
+        return handle
+
+    def _exchange_together(self, parts):
+        """Several all-to-alls with row splits -- parts = [(recv, send, recv_splits, send_splits), ...] --
+        as ONE exchange.  The reference sends the parameters and the codes of a packed halo as two
+        messages per peer (communicator.py:297-311).  On NCCL both travel in one grouped launch of
+        point-to-point operations (every rank lists its sends and receives per peer in the same part
+        order, so they pair up); other backends (the gloo plumbing tests) run one all_to_all_single per
+        part."""
+        if dist.get_backend() != "nccl":
+            return _Handles([dist.all_to_all_single(r, s, rs, ss, async_op=self.is_async) for r, s, rs, ss in parts])
+        ops = []
+        for recv, send, recv_splits, send_splits in parts:
+            ro = so = 0
+            for p, (nr, ns) in enumerate(zip(recv_splits, send_splits)):
+                if ns:
+                    ops.append(dist.P2POp(dist.isend, send[so:so + ns], p))
+                if nr:
+                    ops.append(dist.P2POp(dist.irecv, recv[ro:ro + nr], p))
+                ro, so = ro + nr, so + ns
+        works = dist.batch_isend_irecv(ops) if ops else []
+        if not self.is_async:
+            for w in works:
+                w.wait()
+            return None
+        return _Handles(works)
 
 
 def _cast(src: torch.Tensor, dst: torch.Tensor) -> None:

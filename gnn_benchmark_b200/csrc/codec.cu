@@ -115,6 +115,119 @@ __device__ __forceinline__ void quant_exact_rows(const float4 (&xv)[8 / BITS][NV
     }
 }
 
+// Quantise + pack one packed row whose <= EPB input rows are held in registers (xv[t][k] = float4 number
+// gl + GQ*k of input row i0 + t), by the GQ lanes of one group: per-row min / max, parameters, codes,
+// stores.  Shared by the stand-alone pack kernel (rows loaded from memory) and by the SpMM whose
+// epilogue packs the rows it has just summed.
+template <int BITS, int NV, int GQ>
+__device__ __forceinline__ void quant_pack_group(const float4 (&xv)[8 / BITS][NV], int cnt, int i0, int64_t R, int gl,
+                                                 unsigned gmask, int lead, int FV, int F, int params_given,
+                                                 float *__restrict__ params, uint32_t *__restrict__ params_bf16,
+                                                 uint8_t *__restrict__ codes) {
+    constexpr int EPB = 8 / BITS;
+    constexpr float LEVELS = (float)((1 << BITS) - 1);
+    float zp[EPB], rinv[EPB], sc[EPB];
+    bool fast[EPB];
+#pragma unroll
+    for (int t = 0; t < EPB; ++t) {
+        zp[t] = 0.f, sc[t] = 1.f;
+        if (t < cnt) {
+            if (!params_given) {
+                float mn = __int_as_float(0x7f800000), mx = __int_as_float(0xff800000);  // +inf, -inf
+#pragma unroll
+                for (int k = 0; k < NV; ++k)
+                    if (gl + GQ * k < FV) {
+                        mn = fminf(fminf(mn, xv[t][k].x), fminf(xv[t][k].y, fminf(xv[t][k].z, xv[t][k].w)));
+                        mx = fmaxf(fmaxf(mx, xv[t][k].x), fmaxf(xv[t][k].y, fmaxf(xv[t][k].z, xv[t][k].w)));
+                    }
+                // lanes past the row's end hold +inf / -inf and drop out of the reduction
+                mn = ordered_to_float(__reduce_min_sync(gmask, float_to_ordered(mn)));
+                mx = ordered_to_float(__reduce_max_sync(gmask, float_to_ordered(mx)));
+                const float x0 = __shfl_sync(gmask, xv[t][0].x, lead);
+                if (x0 != x0) {  // a NaN in column 0 is never replaced by the reference's scan
+                    mn = mx = x0;
+                } else if (mn == 0.0f || mx == 0.0f) {
+                    // of several zeros of either sign the reference keeps the first one met:
+                    // find the first zero column of the row and take its sign
+                    int zkey = INT_MAX;
+#pragma unroll
+                    for (int k = NV - 1; k >= 0; --k) {
+                        const int vi = gl + GQ * k;
+                        if (vi < FV) {
+                            const float e[4] = {xv[t][k].x, xv[t][k].y, xv[t][k].z, xv[t][k].w};
+#pragma unroll
+                            for (int i = 3; i >= 0; --i)
+                                if (e[i] == 0.0f) zkey = ((vi * 4 + i) << 1) | (int)(__float_as_uint(e[i]) >> 31);
+                        }
+                    }
+                    zkey = __reduce_min_sync(gmask, zkey);
+                    const float z = (zkey & 1) ? -0.0f : 0.0f;
+                    if (mn == 0.0f) mn = z;
+                    if (mx == 0.0f) mx = z;
+                }
+                float s = __fdiv_rn(__fsub_rn(mx, mn), LEVELS);
+                if (s == 0.0f) s = 1.0f;
+                zp[t] = mn, sc[t] = s;
+                if (gl == 0) {
+                    *reinterpret_cast<float2 *>(params + (int64_t)(i0 + t) * 2) = make_float2(mn, s);
+                    if (params_bf16) params_bf16[i0 + t] = bf16_bits(mn) | (bf16_bits(s) << 16);
+                }
+            } else {
+                zp[t] = params[(int64_t)(i0 + t) * 2];
+                sc[t] = params[(int64_t)(i0 + t) * 2 + 1];
+                if (gl == 0 && params_bf16) params_bf16[i0 + t] = bf16_bits(zp[t]) | (bf16_bits(sc[t]) << 16);
+            }
+        }
+        const float a = fabsf(sc[t]);
+        fast[t] = (a >= 7.888609e-31f) && (a <= 1.2676506e30f);  // 1/scale is a full-precision normal
+        rinv[t] = fast[t] ? __frcp_rn(sc[t]) : 0.f;
+    }
+
+    // code = round-half-even(fl((x - zp) / scale)), IEEE division.  The quotient is estimated as
+    // (x - zp) * fl(1/scale) -- within 2 ulp of the true quotient -- which rounds to the same integer
+    // as the exact quotient unless it lies within 8 ulp of a rounding boundary k + 0.5 (or out of the
+    // code range, or is not finite).  The whole packed row is encoded from the estimate first; only if
+    // some element of the group was that close to a boundary (about one packed row in a hundred for
+    // 2-bit codes) is the row encoded again with true divisions, so the hot loop holds no division.
+    constexpr float kBound = LEVELS + 1.0f;
+    constexpr float kThr = 0.5f - kBound * 9.5367431640625e-07f;  // 0.5 - 2^-20 * bound
+    bool unsure = false;
+    auto enc_fast = [&](float x, int t) -> uint32_t {
+        const float q = __fmul_rn(__fsub_rn(x, zp[t]), rinv[t]);
+        const float k = rintf(q);
+        unsure = unsure || !((fabsf(__fsub_rn(q, k)) < kThr) && (fabsf(q) <= kBound));
+        return params_given ? (uint32_t)__float2int_rn(k) : __float2uint_rn(k);
+    };
+    uint32_t words[NV];
+#pragma unroll
+    for (int t = 0; t < EPB; ++t) unsure = unsure || (t < cnt && !fast[t]);
+#pragma unroll
+    for (int k = 0; k < NV; ++k) {
+        uint32_t b0 = 0, b1 = 0, b2 = 0, b3 = 0;
+        if (gl + GQ * k < FV) {
+#pragma unroll
+            for (int t = 0; t < EPB; ++t) {
+                if (t < cnt) {
+                    const int sh = (EPB - 1 - t) * BITS;
+                    b0 |= enc_fast(xv[t][k].x, t) << sh;
+                    b1 |= enc_fast(xv[t][k].y, t) << sh;
+                    b2 |= enc_fast(xv[t][k].z, t) << sh;
+                    b3 |= enc_fast(xv[t][k].w, t) << sh;
+                }
+            }
+        }
+        words[k] = (b0 & 255u) | ((b1 & 255u) << 8) | ((b2 & 255u) << 16) | ((b3 & 255u) << 24);
+    }
+    if (__any_sync(gmask, unsure)) {
+        quant_exact_rows<BITS, NV, GQ>(xv, zp, sc, cnt, gl, FV, params_given != 0, words);
+    }
+    uint32_t *out = reinterpret_cast<uint32_t *>(codes + R * (int64_t)F);
+#pragma unroll
+    for (int k = 0; k < NV; ++k)
+        if (gl + GQ * k < FV) __stcs(out + gl + GQ * k, words[k]);
+
+}
+
 // ---- fast path: F % 4 == 0, F <= 512, 16-byte aligned rows ------------------------------
 // GQ lanes own one packed row (GQ = 8, 16 or 32 by width), so a warp works on 32/GQ packed rows at a
 // time and narrow rows do not leave lanes idle; NV float4 per lane and input row (NV > 1 only with
@@ -126,7 +239,6 @@ __global__ void __launch_bounds__(kCodecWarps * 32, (NV == 1 ? 8 : (NV == 2 ? 5 
                           uint32_t *__restrict__ params_bf16, uint8_t *__restrict__ codes) {
     constexpr int EPB = 8 / BITS;
     constexpr int NG = 32 / GQ;
-    constexpr float LEVELS = (float)((1 << BITS) - 1);
     __shared__ int pbase[kMaxSeg + 1];
     __shared__ int sseg[kMaxSeg + 1];
     build_packed_prefix(seg, P, EPB, pbase, sseg);
@@ -158,106 +270,90 @@ __global__ void __launch_bounds__(kCodecWarps * 32, (NV == 1 ? 8 : (NV == 2 ? 5 
                 if (t < cnt && vi < FV) xv[t][k] = __ldcs(reinterpret_cast<const float4 *>(xp[t]) + vi);
             }
 
-        float zp[EPB], rinv[EPB], sc[EPB];
-        bool fast[EPB];
-#pragma unroll
-        for (int t = 0; t < EPB; ++t) {
-            zp[t] = 0.f, sc[t] = 1.f;
-            if (t < cnt) {
-                if (!params_given) {
-                    float mn = __int_as_float(0x7f800000), mx = __int_as_float(0xff800000);  // +inf, -inf
-#pragma unroll
-                    for (int k = 0; k < NV; ++k)
-                        if (gl + GQ * k < FV) {
-                            mn = fminf(fminf(mn, xv[t][k].x), fminf(xv[t][k].y, fminf(xv[t][k].z, xv[t][k].w)));
-                            mx = fmaxf(fmaxf(mx, xv[t][k].x), fmaxf(xv[t][k].y, fmaxf(xv[t][k].z, xv[t][k].w)));
-                        }
-                    // lanes past the row's end hold +inf / -inf and drop out of the reduction
-                    mn = ordered_to_float(__reduce_min_sync(gmask, float_to_ordered(mn)));
-                    mx = ordered_to_float(__reduce_max_sync(gmask, float_to_ordered(mx)));
-                    const float x0 = __shfl_sync(gmask, xv[t][0].x, lead);
-                    if (x0 != x0) {  // a NaN in column 0 is never replaced by the reference's scan
-                        mn = mx = x0;
-                    } else if (mn == 0.0f || mx == 0.0f) {
-                        // of several zeros of either sign the reference keeps the first one met:
-                        // find the first zero column of the row and take its sign
-                        int zkey = INT_MAX;
-#pragma unroll
-                        for (int k = NV - 1; k >= 0; --k) {
-                            const int vi = gl + GQ * k;
-                            if (vi < FV) {
-                                const float e[4] = {xv[t][k].x, xv[t][k].y, xv[t][k].z, xv[t][k].w};
-#pragma unroll
-                                for (int i = 3; i >= 0; --i)
-                                    if (e[i] == 0.0f) zkey = ((vi * 4 + i) << 1) | (int)(__float_as_uint(e[i]) >> 31);
-                            }
-                        }
-                        zkey = __reduce_min_sync(gmask, zkey);
-                        const float z = (zkey & 1) ? -0.0f : 0.0f;
-                        if (mn == 0.0f) mn = z;
-                        if (mx == 0.0f) mx = z;
-                    }
-                    float s = __fdiv_rn(__fsub_rn(mx, mn), LEVELS);
-                    if (s == 0.0f) s = 1.0f;
-                    zp[t] = mn, sc[t] = s;
-                    if (gl == 0) {
-                        *reinterpret_cast<float2 *>(params + (int64_t)(i0 + t) * 2) = make_float2(mn, s);
-                        if (params_bf16) params_bf16[i0 + t] = bf16_bits(mn) | (bf16_bits(s) << 16);
-                    }
-                } else {
-                    zp[t] = params[(int64_t)(i0 + t) * 2];
-                    sc[t] = params[(int64_t)(i0 + t) * 2 + 1];
-                    if (gl == 0 && params_bf16) params_bf16[i0 + t] = bf16_bits(zp[t]) | (bf16_bits(sc[t]) << 16);
-                }
-            }
-            const float a = fabsf(sc[t]);
-            fast[t] = (a >= 7.888609e-31f) && (a <= 1.2676506e30f);  // 1/scale is a full-precision normal
-            rinv[t] = fast[t] ? __frcp_rn(sc[t]) : 0.f;
-        }
-
-        // code = round-half-even(fl((x - zp) / scale)), IEEE division.  The quotient is estimated as
-        // (x - zp) * fl(1/scale) -- within 2 ulp of the true quotient -- which rounds to the same integer
-        // as the exact quotient unless it lies within 8 ulp of a rounding boundary k + 0.5 (or out of the
-        // code range, or is not finite).  The whole packed row is encoded from the estimate first; only if
-        // some element of the group was that close to a boundary (about one packed row in a hundred for
-        // 2-bit codes) is the row encoded again with true divisions, so the hot loop holds no division.
-        constexpr float kBound = LEVELS + 1.0f;
-        constexpr float kThr = 0.5f - kBound * 9.5367431640625e-07f;  // 0.5 - 2^-20 * bound
-        bool unsure = false;
-        auto enc_fast = [&](float x, int t) -> uint32_t {
-            const float q = __fmul_rn(__fsub_rn(x, zp[t]), rinv[t]);
-            const float k = rintf(q);
-            unsure = unsure || !((fabsf(__fsub_rn(q, k)) < kThr) && (fabsf(q) <= kBound));
-            return params_given ? (uint32_t)__float2int_rn(k) : __float2uint_rn(k);
-        };
-        uint32_t words[NV];
-#pragma unroll
-        for (int t = 0; t < EPB; ++t) unsure = unsure || (t < cnt && !fast[t]);
-#pragma unroll
-        for (int k = 0; k < NV; ++k) {
-            uint32_t b0 = 0, b1 = 0, b2 = 0, b3 = 0;
-            if (gl + GQ * k < FV) {
-#pragma unroll
-                for (int t = 0; t < EPB; ++t) {
-                    if (t < cnt) {
-                        const int sh = (EPB - 1 - t) * BITS;
-                        b0 |= enc_fast(xv[t][k].x, t) << sh;
-                        b1 |= enc_fast(xv[t][k].y, t) << sh;
-                        b2 |= enc_fast(xv[t][k].z, t) << sh;
-                        b3 |= enc_fast(xv[t][k].w, t) << sh;
-                    }
-                }
-            }
-            words[k] = (b0 & 255u) | ((b1 & 255u) << 8) | ((b2 & 255u) << 16) | ((b3 & 255u) << 24);
-        }
-        if (__any_sync(gmask, unsure)) {
-            quant_exact_rows<BITS, NV, GQ>(xv, zp, sc, cnt, gl, FV, params_given != 0, words);
-        }
-        uint32_t *out = reinterpret_cast<uint32_t *>(codes + R * (int64_t)F);
-#pragma unroll
-        for (int k = 0; k < NV; ++k)
-            if (gl + GQ * k < FV) __stcs(out + gl + GQ * k, words[k]);
+        quant_pack_group<BITS, NV, GQ>(xv, cnt, i0, R, gl, gmask, lead, FV, F, params_given, params, params_bf16,
+                                       codes);
     }
+}
+
+// ---- K2 + K3a fused: SpMM whose epilogue quantises + packs -------------------------------
+// Row i of the sparse matrix is wire slot i (the send side of the pre/post scheme,
+// adj_t_pre_post_aggr_to, or the transposed receive-side matrix in backward).  The GQ lanes that
+// own a packed row sum its <= EPB slot rows one after the other -- one fused multiply-add per
+// nonzero in CSR order, starting from zero: the reference's chain (model/ops/src/spmm.cpp:97-126)
+// -- keep the sums in registers and hand them to quant_pack_group, so the fp32 send buffer is never
+// written to or read from HBM.  Column indices / values are read GQ at a time (coalesced) and
+// broadcast inside the group; U gathers are in flight per lane.
+template <int BITS, int NV, int GQ, int U>
+__global__ void __launch_bounds__(kCodecWarps * 32)
+    spmm_quant_pack_kernel(const int64_t *__restrict__ rowptr, const int32_t *__restrict__ col,
+                           const float *__restrict__ val, const float *__restrict__ X, int64_t ldx, int F,
+                           const int32_t *__restrict__ seg, int P, float *__restrict__ params,
+                           uint32_t *__restrict__ params_bf16, uint8_t *__restrict__ codes) {
+    constexpr int EPB = 8 / BITS;
+    constexpr int NG = 32 / GQ;
+    __shared__ int pbase[kMaxSeg + 1];
+    __shared__ int sseg[kMaxSeg + 1];
+    build_packed_prefix(seg, P, EPB, pbase, sseg);
+    const int lane = threadIdx.x & 31;
+    const int gl = lane % GQ, grp = lane / GQ;
+    const unsigned gmask = GQ == 32 ? kFullMask : (((1u << GQ) - 1u) << (grp * GQ));
+    const int lead = grp * GQ;
+    const int FV = F >> 2;
+    const int64_t R = ((int64_t)blockIdx.x * kCodecWarps + (threadIdx.x >> 5)) * NG + grp;
+    if (R >= pbase[P]) return;  // whole groups leave together: every later shuffle names the group's lanes only
+    const int p = find_segment(pbase, P, (int)R);
+    const int i0 = sseg[p] + ((int)R - pbase[p]) * EPB;
+    const int cnt = min(EPB, sseg[p + 1] - i0);
+
+    float4 acc[EPB][NV];
+#pragma unroll
+    for (int t = 0; t < EPB; ++t)
+#pragma unroll
+        for (int k = 0; k < NV; ++k) acc[t][k] = make_float4(0.f, 0.f, 0.f, 0.f);
+
+#pragma unroll
+    for (int t = 0; t < EPB; ++t) {
+        if (t < cnt) {
+            const int64_t e0 = rowptr[i0 + t], e1 = rowptr[i0 + t + 1];
+            for (int64_t eb = e0; eb < e1; eb += GQ) {
+                const int nb = (int)((e1 - eb) < GQ ? (e1 - eb) : GQ);
+                int my_col = 0;
+                float my_val = 0.f;
+                if (gl < nb) {
+                    my_col = ld_stream(col + eb + gl);
+                    my_val = ld_stream(val + eb + gl);
+                }
+                for (int j0 = 0; j0 < nb; j0 += U) {
+                    float4 xr[U][NV];
+                    float av[U];
+#pragma unroll
+                    for (int u = 0; u < U; ++u) {
+                        const int j = j0 + u;
+                        const int c = __shfl_sync(gmask, my_col, lead + (j & (GQ - 1)));
+                        av[u] = __shfl_sync(gmask, my_val, lead + (j & (GQ - 1)));
+                        const float4 *xp = reinterpret_cast<const float4 *>(X + (int64_t)c * ldx);
+#pragma unroll
+                        for (int k = 0; k < NV; ++k)
+                            if (j < nb && gl + GQ * k < FV) xr[u][k] = __ldg(xp + gl + GQ * k);
+                    }
+#pragma unroll
+                    for (int u = 0; u < U; ++u) {
+                        if (j0 + u < nb) {
+#pragma unroll
+                            for (int k = 0; k < NV; ++k)
+                                if (gl + GQ * k < FV) {
+                                    acc[t][k].x = fmaf(av[u], xr[u][k].x, acc[t][k].x);
+                                    acc[t][k].y = fmaf(av[u], xr[u][k].y, acc[t][k].y);
+                                    acc[t][k].z = fmaf(av[u], xr[u][k].z, acc[t][k].z);
+                                    acc[t][k].w = fmaf(av[u], xr[u][k].w, acc[t][k].w);
+                                }
+                        }
+                    }
+                }
+            }
+        }
+    }
+    quant_pack_group<BITS, NV, GQ>(acc, cnt, i0, R, gl, gmask, lead, FV, F, 0, params, params_bf16, codes);
 }
 
 // ---- generic path: any F, any alignment; rows are read twice (second pass hits L1/L2) ----
@@ -513,6 +609,47 @@ extern "C" int gnnagg_quant_pack_rows(const float *X, int64_t ldx, const int32_t
     quant_pack_generic_kernel<<<blocks, kCodecWarps * 32, 0, st>>>(X, ldx, idx, F, seg, P, bits, params_given, params,
                                                                   static_cast<__nv_bfloat16 *>(params_bf16), codes);
     return check_launch("quant_pack_generic_kernel");
+}
+
+extern "C" int gnnagg_spmm_quant_pack(const int64_t *rowptr, const int32_t *col, const float *val, int64_t M, int64_t K,
+                                      int64_t nnz, const float *X, int64_t ldx, int32_t F, const int32_t *seg,
+                                      int32_t P, int32_t bits, float *params, void *params_bf16, uint8_t *codes,
+                                      void *stream) {
+    int rc = check_seg_args("spmm_quant_pack", seg, P, M, bits, F);
+    if (rc != GNNAGG_OK) return rc;
+    if (K < 0 || nnz < 0) return fail(GNNAGG_ERR_ARG, "spmm_quant_pack: negative size");
+    if (M == 0 || F == 0) return GNNAGG_OK;
+    if (rowptr == nullptr || params == nullptr || codes == nullptr || (nnz > 0 && (col == nullptr || val == nullptr || X == nullptr)))
+        return fail(GNNAGG_ERR_ARG, "spmm_quant_pack: null pointer");
+    if (ldx < F) return fail(GNNAGG_ERR_ARG, "spmm_quant_pack: ldx < F");
+    const bool ok = (F % 4 == 0) && F <= 512 && (ldx % 4 == 0) && aligned16(X) &&
+                    (reinterpret_cast<uintptr_t>(codes) % 4 == 0) && (reinterpret_cast<uintptr_t>(params) % 8 == 0) &&
+                    (params_bf16 == nullptr || reinterpret_cast<uintptr_t>(params_bf16) % 4 == 0);
+    if (!ok)
+        return fail(GNNAGG_ERR_UNSUPPORTED,
+                    "spmm_quant_pack: needs F %% 4 == 0, F <= 512 and 16-byte aligned dense rows; use gnnagg_spmm_csr_f32 "
+                    "followed by gnnagg_quant_pack_rows");
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    const int epb = 8 / bits;
+    uint32_t *pb = static_cast<uint32_t *>(params_bf16);
+    const int64_t groups = packed_rows_bound(M, P, epb);
+#define GNNAGG_SQ(B, NV, GQ, U)                                                                                        \
+    spmm_quant_pack_kernel<B, NV, GQ, U><<<(unsigned)div_up(groups, kCodecWarps * (32 / GQ)), kCodecWarps * 32, 0, st>>>( \
+        rowptr, col, val, X, ldx, F, seg, P, params, pb, codes)
+#define GNNAGG_SQ_WIDTH(B)                                       \
+    do {                                                         \
+        if (F <= 32) GNNAGG_SQ(B, 1, 8, 8);                      \
+        else if (F <= 64) GNNAGG_SQ(B, 1, 16, 8);                \
+        else if (F <= 128) GNNAGG_SQ(B, 1, 32, 8);               \
+        else if (F <= 256) GNNAGG_SQ(B, 2, 32, 4);               \
+        else GNNAGG_SQ(B, 4, 32, 2);                             \
+    } while (0)
+    if (bits == 2) GNNAGG_SQ_WIDTH(2);
+    else if (bits == 4) GNNAGG_SQ_WIDTH(4);
+    else GNNAGG_SQ_WIDTH(8);
+#undef GNNAGG_SQ_WIDTH
+#undef GNNAGG_SQ
+    return check_launch("spmm_quant_pack_kernel");
 }
 
 extern "C" int gnnagg_unpack_dequant_rows(const uint8_t *codes, int32_t F, const int32_t *seg, int32_t P, int64_t rows,

@@ -1,0 +1,91 @@
+// Halo exchange by direct stores: rows are written straight into the RECEIVING GPU's buffer over
+// NVLink (plain st.global to peer-mapped memory), optionally gathered on the way, so the send-side
+// staging buffer and the library all-to-all disappear.  One launch serves a group of peers:
+// destination peer p gets this rank's block seg[p]..seg[p+1] at dst[p], the address inside p's
+// receive buffer where this rank's rows belong.
+//
+// The kernel only stores to peer memory; it never loads from it, never waits on anything and uses no
+// multicast of any kind.  Ordering with the consumer is the caller's: the receiving rank may read
+// the rows after this kernel has completed and a collective ordered behind it (the caller uses a
+// small NCCL all-reduce) has been seen on the receiver.
+#include "common.cuh"
+
+namespace gnnagg {
+
+// UNIT bytes per lane access (16 / 4 / 1); `units` of them per row; G = 2^log2g lanes per row.
+template <typename T>
+__global__ void __launch_bounds__(256)
+    push_rows_kernel(const uint8_t *__restrict__ src, int64_t ld_src, const int32_t *__restrict__ idx, int units,
+                     int log2g, const int32_t *__restrict__ seg, int P, int first_peer, int num_peers,
+                     const uint64_t *__restrict__ dst, int64_t ld_dst) {
+    __shared__ int spre[kMaxSeg + 1];  // row prefix over the selected peers, in the order they are served
+    if (threadIdx.x == 0) {
+        int run = 0;
+        for (int j = 0; j < num_peers; ++j) {
+            int p = first_peer + j;
+            if (p >= P) p -= P;
+            spre[j] = run;
+            run += seg[p + 1] - seg[p];
+        }
+        spre[num_peers] = run;
+    }
+    __syncthreads();
+    const int total = spre[num_peers];
+    const int G = 1 << log2g;
+    const int gl = threadIdx.x & (G - 1);
+    const int64_t groups_per_block = blockDim.x >> log2g;
+    const int64_t stride = groups_per_block * gridDim.x;
+    for (int64_t v = (int64_t)blockIdx.x * groups_per_block + (threadIdx.x >> log2g); v < total; v += stride) {
+        int lo = 0, hi = num_peers - 1;  // peer slot j with spre[j] <= v < spre[j+1] (empty peers skipped)
+        while (lo < hi) {
+            const int mid = (lo + hi + 1) >> 1;
+            if (spre[mid] <= v)
+                lo = mid;
+            else
+                hi = mid - 1;
+        }
+        int p = first_peer + lo;
+        if (p >= P) p -= P;
+        const int64_t r = v - spre[lo];          // row inside this rank's block for peer p
+        const int64_t i = (int64_t)seg[p] + r;   // row of the send list
+        const int64_t s = idx ? (int64_t)idx[i] : i;
+        const T *in = reinterpret_cast<const T *>(src + s * ld_src);
+        T *out = reinterpret_cast<T *>(reinterpret_cast<uint8_t *>(dst[p]) + r * ld_dst);
+        for (int u = gl; u < units; u += G) out[u] = __ldg(in + u);
+    }
+}
+
+}  // namespace gnnagg
+
+using namespace gnnagg;
+
+extern "C" int gnnagg_push_rows(const void *src, int64_t ld_src, const int32_t *idx, int32_t row_bytes,
+                                const int32_t *seg, int32_t P, int32_t first_peer, int32_t num_peers,
+                                const uint64_t *dst, int64_t ld_dst, int64_t rows_hint, void *stream) {
+    if (row_bytes < 0 || rows_hint < 0 || P < 1 || num_peers < 0 || num_peers > P || first_peer < 0 || first_peer >= P)
+        return fail(GNNAGG_ERR_ARG, "push_rows: bad size or peer range");
+    if (P > kMaxSeg) return fail(GNNAGG_ERR_UNSUPPORTED, "push_rows: more than %d peers", kMaxSeg);
+    if (rows_hint == 0 || row_bytes == 0 || num_peers == 0) return GNNAGG_OK;
+    if (src == nullptr || seg == nullptr || dst == nullptr || ld_src < row_bytes || ld_dst < row_bytes)
+        return fail(GNNAGG_ERR_ARG, "push_rows: null pointer or leading dimension smaller than the row");
+    // widest access both sides allow; the destination bases are checked by the caller (they are device data)
+    int unit = 1;
+    if (row_bytes % 16 == 0 && ld_src % 16 == 0 && ld_dst % 16 == 0 && aligned16(src)) unit = 16;
+    else if (row_bytes % 4 == 0 && ld_src % 4 == 0 && ld_dst % 4 == 0 && (reinterpret_cast<uintptr_t>(src) & 3u) == 0) unit = 4;
+    const int units = row_bytes / unit;
+    int log2g = 0;
+    while ((1 << log2g) < units && log2g < 5) ++log2g;
+    const int64_t groups_per_block = 256 >> log2g;
+    int64_t blocks = div_up(rows_hint, groups_per_block);
+    const int64_t cap = (int64_t)kNumSMs * 16;
+    if (blocks > cap) blocks = cap;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    const uint8_t *s8 = static_cast<const uint8_t *>(src);
+#define GNNAGG_PUSH(T) \
+    push_rows_kernel<T><<<(unsigned)blocks, 256, 0, st>>>(s8, ld_src, idx, units, log2g, seg, P, first_peer, num_peers, dst, ld_dst)
+    if (unit == 16) GNNAGG_PUSH(uint4);
+    else if (unit == 4) GNNAGG_PUSH(uint32_t);
+    else GNNAGG_PUSH(uint8_t);
+#undef GNNAGG_PUSH
+    return check_launch("push_rows_kernel");
+}

@@ -13,16 +13,23 @@ class CommBuffer(object):
     """fp32 (and, for 16-bit mode, bf16) send / receive buffers of the halo exchange, allocated
     once for the widest layer and reshaped per layer (data_manager/CommBuffer.py:4-25)."""
 
-    def __init__(self, comm_splits: CommSplits, feat_len: int, bits: int, device=None, lean: bool = False) -> None:
+    def __init__(self, comm_splits: CommSplits, feat_len: int, bits: int, device=None, lean: bool = False,
+                 plan=None) -> None:
         """lean (an addition, packed halo modes only): the fp32 staging buffers get a shape but no
-        memory (meta tensors).  The fused gather+pack, per-peer pack and fused unpack paths of the
-        Aggregator never touch them; at 10^7 halo rows x 256 columns they would be tens of GB each."""
+        memory (meta tensors).  The fused pack and unpack paths of the Aggregator never touch them; at
+        10^7 halo rows x 256 columns they would be tens of GB each.
+        plan (an addition): a peer.PushPlan -- the buffers are then views into its peer-visible
+        allocation, so that other ranks can store their rows straight into them."""
         size_send_buf = (sum(comm_splits.send_splits), feat_len)
         size_recv_buf = (sum(comm_splits.recv_splits), feat_len)
         self.lean = bool(lean) and bits in (2, 4, 8)
         buf_device = "meta" if self.lean else device
-        self.send_buf = torch.zeros(size_send_buf, dtype=torch.float32, device=buf_device)
-        self.recv_buf = torch.zeros(size_recv_buf, dtype=torch.float32, device=buf_device)
+        if plan is not None and not self.lean:
+            self.send_buf = plan.region("send_buf", size_send_buf, torch.float32).zero_()
+            self.recv_buf = plan.region("recv_buf", size_recv_buf, torch.float32).zero_()
+        else:
+            self.send_buf = torch.zeros(size_send_buf, dtype=torch.float32, device=buf_device)
+            self.recv_buf = torch.zeros(size_recv_buf, dtype=torch.float32, device=buf_device)
         self.send_buf_fp16 = None
         self.recv_buf_fp16 = None
         if bits == 16:
@@ -43,17 +50,21 @@ class CommBufferForQuantization(object):
     """Packed code buffers, fp32 + bf16 parameter buffers and the per-peer row prefixes the codec
     kernels take (data_manager/CommBuffer.py:27-49; there for bits == 2 only)."""
 
-    def __init__(self, comm_splits: CommSplits, feat_len: int, bits: int, device=None) -> None:
+    def __init__(self, comm_splits: CommSplits, feat_len: int, bits: int, device=None, plan=None) -> None:
         if bits in (2, 4, 8):
             n_send, n_recv = sum(comm_splits.send_splits), sum(comm_splits.recv_splits)
-            self.quantized_send_data_buf = torch.zeros((sum(comm_splits.send_splits_int2), feat_len),
-                                                       dtype=torch.uint8, device=device)
-            self.quantized_recv_data_buf = torch.zeros((sum(comm_splits.recv_splits_int2), feat_len),
-                                                       dtype=torch.uint8, device=device)
+
+            def wire(name, shape, dtype):  # the buffers that receive rows from other ranks
+                if plan is not None:
+                    return plan.region(name, shape, dtype).zero_()
+                return torch.zeros(shape, dtype=dtype, device=device)
+
+            self.quantized_send_data_buf = wire("q_send_data", (sum(comm_splits.send_splits_int2), feat_len), torch.uint8)
+            self.quantized_recv_data_buf = wire("q_recv_data", (sum(comm_splits.recv_splits_int2), feat_len), torch.uint8)
             self.quantized_send_params_buf_fp32 = torch.zeros((n_send, 2), dtype=torch.float32, device=device)
             self.quantized_recv_params_buf_fp32 = torch.zeros((n_recv, 2), dtype=torch.float32, device=device)
-            self.quantized_send_params_buf_bf16 = torch.zeros((n_send, 2), dtype=torch.bfloat16, device=device)
-            self.quantized_recv_params_buf_bf16 = torch.zeros((n_recv, 2), dtype=torch.bfloat16, device=device)
+            self.quantized_send_params_buf_bf16 = wire("q_send_params", (n_send, 2), torch.bfloat16)
+            self.quantized_recv_params_buf_bf16 = wire("q_recv_params", (n_recv, 2), torch.bfloat16)
             self.quantized_work_range_per_proc = _prefix(comm_splits.send_splits, device)
             self.dequantized_work_range_per_proc = _prefix(comm_splits.recv_splits, device)
 

@@ -76,6 +76,19 @@ def _scatter_matrix(idx: torch.Tensor, num_local_nodes: int) -> SparseTensor:
     return SparseTensor(row=idx.to(torch.int64), col=cols, sparse_sizes=(num_local_nodes, idx.numel()))
 
 
+def _push_plan(comm_splits, max_feat_len, bits, lean_halo, world_size):
+    """The peer-visible receive buffers of this graph when the Communicator exchanges by direct stores
+    (Communicator(transport="push")); None for the all-to-all transport."""
+    from ..communicator import Communicator
+
+    comm = Communicator.ctx
+    if comm is None or world_size < 2 or getattr(comm, "transport", "all_to_all") != "push":
+        return None
+    from ..peer import PushPlan
+
+    return PushPlan(comm.peers(), comm_splits, max_feat_len, bits, bool(lean_halo) and bits in (2, 4, 8))
+
+
 def _check_graph(graph) -> None:
     """Refuse a malformed graph before any kernel runs on it: the gather, SpMM and codec kernels index
     device memory with these arrays and do no bounds checks of their own.  Every matrix goes through
@@ -136,10 +149,11 @@ def get_distributed_graph(local_edges_list, remote_edges_list, local_nodes_list,
         device = local_adj_t.device
     comm_splits = CommSplits(remote_nodes_num_from_each_subgraph.tolist(),
                              num_local_nodes_required_by_other.tolist(), world_size, bits)
-    comm_buf = CommBuffer(comm_splits, max_feat_len, bits, device, lean=lean_halo)
+    plan = _push_plan(comm_splits, max_feat_len, bits, lean_halo, world_size)
+    comm_buf = CommBuffer(comm_splits, max_feat_len, bits, device, lean=lean_halo, plan=plan)
     comm_buf_for_quantization = None
     if bits in (2, 4, 8):
-        comm_buf_for_quantization = CommBufferForQuantization(comm_splits, max_feat_len, bits, device)
+        comm_buf_for_quantization = CommBufferForQuantization(comm_splits, max_feat_len, bits, device, plan=plan)
     graph = DistributedGraph(
         local_adj_t.to(device),
         remote_adj_t.to(device),
@@ -153,12 +167,14 @@ def get_distributed_graph(local_edges_list, remote_edges_list, local_nodes_list,
     )
     graph.idx_nodes_send_to_others_i32 = graph.idx_nodes_send_to_others.to(torch.int32)
     graph.scatter_adj_t = _scatter_matrix(graph.idx_nodes_send_to_others, num_local_nodes)
+    graph.push_plan = plan
     _check_graph(graph)
     return graph
 
 
 def get_distributed_graph_for_pre_aggressive(local_edges_list, remote_edges_list, nodes_range_on_each_subgraph,
-                                             num_local_nodes, max_feat_len, rank, world_size, bits, device=None):
+                                             num_local_nodes, max_feat_len, rank, world_size, bits, device=None,
+                                             lean_halo: bool = False):
     """Pre/post-aggregation path (DataLoader.py:125-194)."""
     in_degrees = DataProcessor.get_in_degrees(local_edges_list, remote_edges_list, num_local_nodes)
     # destinations back to global ids: pre/post keys mix ids of both ranks (DataLoader.py:139)
@@ -184,10 +200,11 @@ def get_distributed_graph_for_pre_aggressive(local_edges_list, remote_edges_list
     if device is None:
         device = local_adj_t.device
     comm_splits = CommSplits(pre_post_aggr_from_splits, pre_post_aggr_to_splits, world_size, bits)
-    comm_buf = CommBuffer(comm_splits, max_feat_len, bits, device)
+    plan = _push_plan(comm_splits, max_feat_len, bits, lean_halo, world_size)
+    comm_buf = CommBuffer(comm_splits, max_feat_len, bits, device, lean=lean_halo, plan=plan)
     comm_buf_for_quantization = None
     if bits in (2, 4, 8):
-        comm_buf_for_quantization = CommBufferForQuantization(comm_splits, max_feat_len, bits, device)
+        comm_buf_for_quantization = CommBufferForQuantization(comm_splits, max_feat_len, bits, device, plan=plan)
     graph = DistributedGraphForPre(
         local_adj_t.to(device),
         adj_t_pre_post_aggr_from.to(device),
@@ -199,6 +216,7 @@ def get_distributed_graph_for_pre_aggressive(local_edges_list, remote_edges_list
         comm_buf,
         comm_buf_for_quantization,
     )
+    graph.push_plan = plan
     _check_graph(graph)
     return graph
 
@@ -213,7 +231,8 @@ def build_graph(local_edges_list, remote_edges_list, nodes_range_on_each_subgrap
     num_local_nodes = int(begin[rank + 1]) - int(begin[rank])
     if is_pre_delay:
         return get_distributed_graph_for_pre_aggressive(local_edges_list, remote_edges_list, begin, num_local_nodes,
-                                                        max_feat_len, rank, world_size, bits, device)
+                                                        max_feat_len, rank, world_size, bits, device,
+                                                        lean_halo=lean_halo)
     local_nodes_list = torch.tensor([[int(begin[rank]), 0]], dtype=torch.int64)
     return get_distributed_graph(local_edges_list, remote_edges_list, local_nodes_list, begin, num_local_nodes,
                                  max_feat_len, world_size, bits, device, lean_halo=lean_halo)

@@ -110,6 +110,50 @@ def SPMM_backward_packed(src: SparseTensor, codes, params_bf16, seg, num_segment
     return None
 
 
+def quant_pack_fusable(other: torch.Tensor) -> bool:
+    """Can the SpMM-with-packing-epilogue take `other` as its dense operand?  (F a multiple of 4, at most
+    512, rows 16-byte aligned; anything else runs SpMM and quantise + pack as two calls.)"""
+    F = other.size(1)
+    return (other.is_cuda and other.dtype == torch.float32 and other.dim() == 2 and other.stride(1) == 1
+            and F % 4 == 0 and 0 < F <= 512 and other.stride(0) % 4 == 0 and other.data_ptr() % 16 == 0)
+
+
+def spmm_quant_pack(rowptr, col, value, K: int, other: torch.Tensor, codes: torch.Tensor, params: torch.Tensor,
+                    params_bf16, seg: torch.Tensor, num_segments: int, bits: int) -> None:
+    """codes, params = quantise_pack(CSR[M,K] @ other) without the fp32 product ever reaching memory;
+    row i of the matrix is wire slot i, `seg` the per-peer slot prefix."""
+    _lib.require_cuda(rowptr, col, value, other, codes, params, params_bf16, seg)
+    if other.dtype != torch.float32 or codes.dtype != torch.uint8 or params.dtype != torch.float32:
+        raise RuntimeError("spmm_quant_pack: expected float32 operand / params and uint8 codes")
+    M, F = rowptr.numel() - 1, other.size(1)
+    if other.size(0) != K or params.size(0) != M or codes.size(-1) != F or not codes.is_contiguous() \
+            or not params.is_contiguous():
+        raise RuntimeError("spmm_quant_pack: shape mismatch")
+    if M == 0 or F == 0:
+        return
+    rc = _lib.lib().gnnagg_spmm_quant_pack(rowptr.data_ptr(), _lib.ptr(col), _lib.ptr(value), M, K, col.numel(),
+                                           other.data_ptr(), other.stride(0), F, seg.data_ptr(), num_segments, bits,
+                                           params.data_ptr(), _lib.ptr(params_bf16), codes.data_ptr(),
+                                           _lib.stream_ptr(other.device))
+    _lib.check(rc, "spmm_quant_pack")
+
+
+def SPMM_forward_quant_pack(src: SparseTensor, other, codes, params, params_bf16, seg, num_segments: int, bits: int):
+    """quantise_pack(src @ other): SPMM_forward into the send buffer followed by the quantiser
+    (model/layers/aggregator.py:48-49 + communicator.py:281-284 of the reference) as one kernel."""
+    rowptr, col, value = src.csr()
+    spmm_quant_pack(rowptr, col, value, src.sparse_size(1), other, codes, params, params_bf16, seg, num_segments, bits)
+    return None
+
+
+def SPMM_backward_quant_pack(src: SparseTensor, other, codes, params, params_bf16, seg, num_segments: int, bits: int):
+    """quantise_pack(src^T @ other) on the cached CSC arrays (the backward twin,
+    model/layers/aggregator.py:145-149 + the quantiser)."""
+    spmm_quant_pack(src.storage.colptr(), src.storage.row_T(), src.storage.value_T(), src.sparse_size(0), other, codes,
+                    params, params_bf16, seg, num_segments, bits)
+    return None
+
+
 def SPMM_forward(src: SparseTensor, other: torch.Tensor, out: torch.Tensor, accumulate: bool = True):
     """out += src @ other.  Returns None, like the reference (spmm_kernel.py:45-67).
 

@@ -126,6 +126,28 @@ int gnnagg_csr_validate(const int64_t *rowptr, const int32_t *col, int64_t M, in
 int gnnagg_gather_rows_f32(const float *X, int64_t ldx, const int32_t *idx, int64_t rows, int32_t F,
                            float *OUT, int64_t ldo, void *stream);
 
+/* Exchange by direct stores: rows of this rank's send list are written straight into the receiving
+ * GPUs' buffers (peer-mapped memory, plain stores over NVLink), gathered on the way when idx != NULL.
+ * Replaces the send-buffer fill and the all-to-all of the halo exchange for the peers it serves:
+ *   torch.index_select(x, 0, idx_nodes_send_to_others, out=send_buf)   (model/layers/aggregator.py:51)
+ *   dist.all_to_all_single(recv_buf, send_buf, recv_splits, send_splits) (communicator.py:101, :307-311)
+ *   src        rows of row_bytes bytes, leading dimension ld_src bytes (fp32 rows: 4F; packed code rows:
+ *              F; bf16 parameter pairs: 4)
+ *   idx        optional int32 gather index: send-list row i is src row idx[i]; NULL = row i
+ *   seg        device int32[P+1], prefix of the send list's per-peer row counts
+ *   first_peer, num_peers: the peers served by this launch, first_peer, first_peer+1, ... (mod P)
+ *   dst        device uint64[P]: dst[p] = address, valid on THIS device, of the place in peer p's receive
+ *              buffer where this rank's block starts; rows land there with leading dimension ld_dst
+ *              bytes.  Bases and leading dimensions must allow the access width the source allows
+ *              (16 bytes when row_bytes, ld_src, ld_dst are multiples of 16 and src is 16-byte aligned).
+ *   rows_hint  number of rows these peers get (host copy of the splits; sizes the grid)
+ * The kernel stores to peer memory only: no loads from it, no waiting, no multicast.  The receiver may
+ * read the rows once this launch has completed and it has been told so (e.g. by a collective queued
+ * behind the launch). */
+int gnnagg_push_rows(const void *src, int64_t ld_src, const int32_t *idx, int32_t row_bytes, const int32_t *seg,
+                     int32_t P, int32_t first_peer, int32_t num_peers, const uint64_t *dst, int64_t ld_dst,
+                     int64_t rows_hint, void *stream);
+
 /* Y[i,:] = X[i,:] * s[i] (divide == 0) or X[i,:] / s[i] (divide == 1, IEEE quotient), plus bias[F] when
  * bias != NULL; Y may alias X.  Replaces the broadcast `out /= graph.in_degrees` of the layer
  * (model/layers/sageconv.py:84-85) and the d^-1/2 row scalings (and bias add) of a GCN layer around
@@ -155,6 +177,27 @@ int gnnagg_scale_rows_f32(const float *X, int64_t ldx, const float *s, int64_t r
 int gnnagg_quant_pack_rows(const float *X, int64_t ldx, const int32_t *idx, int32_t F, const int32_t *seg,
                            int32_t P, int64_t rows, int32_t bits, int32_t params_given, float *params,
                            void *params_bf16, uint8_t *codes, void *stream);
+
+/* K2 + K3a fused: SpMM whose output rows are quantised + packed in its epilogue instead of stored.
+ * Row i of the CSR matrix is wire slot i; its sum over the nonzeros (one fused multiply-add each, in
+ * CSR order, starting from zero: the chain of model/ops/src/spmm.cpp:97-126) stays in registers and
+ * goes straight into the encoder of gnnagg_quant_pack_rows, so the fp32 send buffer of the exchange is
+ * never written or read.  Replaces the pair
+ *   SPMM_forward(adj_t_pre_post_aggr_to, x, send_buf)            (model/layers/aggregator.py:48-49)
+ *   quantize_tensor_for_all_procs(send_buf, ...)                 (communicator.py:281-284,
+ *                                                                 model/ops/src/quantization_arm.cpp:364-435)
+ * and, with the CSC arrays of the receive-side matrix as (rowptr, col, val), the backward pair
+ *   SPMM_backward(remote_adj_t | adj_t_pre_post_aggr_from, grad, recv_buf) + quantise
+ *                                                                (model/layers/aggregator.py:145-149).
+ *   M = number of wire slots = seg[P];  X (K,F) fp32 with leading dimension ldx;
+ *   params / params_bf16 / codes / seg / P / bits: as for gnnagg_quant_pack_rows (params computed here).
+ * Needs F % 4 == 0, F <= 512, ldx % 4 == 0 and 16-byte aligned X (GNNAGG_ERR_UNSUPPORTED otherwise: run
+ * the two calls).  Codes and parameters equal those of the two-call sequence wherever that sequence
+ * sums a row in the same order (F > 64 and no row longer than one 512-item chunk), and equal the
+ * reference's bytes for every shape (its SpMM is the sequential chain). */
+int gnnagg_spmm_quant_pack(const int64_t *rowptr, const int32_t *col, const float *val, int64_t M, int64_t K,
+                           int64_t nnz, const float *X, int64_t ldx, int32_t F, const int32_t *seg, int32_t P,
+                           int32_t bits, float *params, void *params_bf16, uint8_t *codes, void *stream);
 
 /* ------------------------------------------------------------------------------------
  * K3b  unpack + dequantise   OUT[i,k] = fma(code, scale_i, zero_point_i)

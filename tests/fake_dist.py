@@ -26,8 +26,37 @@ class _P2POp:
 _REAL_ISEND, _REAL_IRECV = dist.isend, dist.irecv
 
 
+class ThreadPeers:
+    """Stand-in for gnn_benchmark_b200.peer.NcclPeers when the ranks are threads on one GPU: every rank's
+    buffer is ordinary memory of the same device, so its address IS the peer address; a signal is a
+    stream synchronisation followed by a host barrier (nothing on the device waits for another rank)."""
+
+    def __init__(self, world: "FakeWorld", rank: int):
+        self.w, self.rank, self.world = world, rank, world.P
+        self._bufs = []
+
+    def gather_objects(self, obj):
+        self.w._objs[self.rank] = obj
+        self.w._barrier.wait()
+        out = list(self.w._objs)
+        self.w._barrier.wait()
+        return out
+
+    def share(self, nbytes: int):
+        buf = torch.zeros(nbytes, dtype=torch.uint8, device="cuda")
+        self._bufs.append(buf)
+        torch.cuda.current_stream().synchronize()
+        return buf, self.gather_objects(buf.data_ptr())
+
+    def signal(self):
+        torch.cuda.current_stream().synchronize()
+        self.w._barrier.wait()
+        return _Work()
+
+
 class FakeWorld:
     def __init__(self, world_size: int):
+        self._objs = [None] * world_size
         self.P = world_size
         self._barrier = threading.Barrier(world_size)
         self._slots = [None] * world_size
@@ -108,14 +137,19 @@ class FakeWorld:
     def patched(self):
         names = ("get_rank", "get_world_size", "is_initialized", "is_available", "get_backend", "barrier",
                  "all_to_all_single", "batch_isend_irecv")
+        from gnn_benchmark_b200.communicator import Communicator
+
         saved = {n: getattr(dist, n) for n in names}
         saved["P2POp"] = dist.P2POp
+        real_peers = Communicator.peers
         try:
             for n in names:
                 setattr(dist, n, getattr(self, n))
             dist.P2POp = _P2POp
+            Communicator.peers = lambda comm: self._local.peers  # one peer service per rank (thread)
             yield self
         finally:
+            Communicator.peers = real_peers
             for n, f in saved.items():
                 setattr(dist, n, f)
 
@@ -125,6 +159,7 @@ class FakeWorld:
 
         def target(rank):
             self._local.rank = rank
+            self._local.peers = ThreadPeers(self, rank)
             try:
                 if torch.cuda.is_available():
                     stream = torch.cuda.Stream()

@@ -273,12 +273,16 @@ def test_padded_feature_rows_give_identical_results(cuda_lib, P, bits, is_pre):
         np.testing.assert_array_equal(results[True][r][1], results[False][r][1])
 
 
-@pytest.mark.parametrize("P,F,bits", [(2, 128, 2), (4, 256, 2), (3, 64, 8)])
-def test_lean_halo_buffers_give_identical_results(cuda_lib, P, F, bits):
-    """lean_halo=True: the fp32 staging buffers of the exchange have no memory (meta tensors); forward
-    goes gather+pack -> exchange -> fused unpack SpMM, backward packs the halo gradients peer by peer
-    through a peer-sized scratch.  Outputs, gradients and the codes on the wire are bit-identical to the
-    path that stages everything in fp32."""
+@pytest.mark.parametrize("P,F,bits,is_pre", [(2, 128, 2, False), (4, 256, 2, False), (3, 96, 8, False),
+                                             (3, 128, 2, True), (4, 256, 2, True)])
+def test_lean_halo_buffers_give_identical_results(cuda_lib, monkeypatch, P, F, bits, is_pre):
+    """lean_halo=True: the fp32 staging buffers of the exchange have no memory (meta tensors).  Forward
+    goes gather+pack (plain path) or pre-aggregation SpMM with the packing epilogue (pre/post path) ->
+    exchange -> fused unpack SpMM; backward packs the halo gradients in the epilogue of the transposed
+    receive-side SpMM.  Outputs, gradients and the codes on the wire are bit-identical to the path that
+    stages everything in fp32 (SpMM into the fp32 buffer, then quantise + pack)."""
+    import gnn_benchmark_b200.aggregator as agg_mod
+
     from gnn_benchmark_b200 import Communicator, Quantizer_for_all_procs, TimeRecorder, graphgen
     from gnn_benchmark_b200.aggregator import Aggregator
     from gnn_benchmark_b200.data_manager.DataLoader import build_graph
@@ -295,13 +299,15 @@ def test_lean_halo_buffers_give_identical_results(cuda_lib, P, F, bits):
     TimeRecorder(1, 1)
     results = {}
     for lean in (False, True):
+        monkeypatch.setattr(agg_mod, "FUSE_PACK", lean)  # staged run: the reference's two-step sequence
+
         def rank_fn(rank):
             local, remote = graphgen.partition_edges(s_t, d_t, begin, rank)
-            graph = build_graph(local, remote, begin, rank, P, F, bits, False, device="cuda", lean_halo=lean)
+            graph = build_graph(local, remote, begin, rank, P, F, bits, is_pre, device="cuda", lean_halo=lean)
             assert graph.comm_buf.send_buf.is_meta == lean and graph.comm_buf.recv_buf.is_meta == lean
             b0, b1 = int(begin[rank]), int(begin[rank + 1])
             ctx = SimpleNamespace()
-            out = Aggregator.forward(ctx, graph, torch.from_numpy(X[b0:b1]).cuda(), 0, bits, False, True)
+            out = Aggregator.forward(ctx, graph, torch.from_numpy(X[b0:b1]).cuda(), 0, bits, is_pre, True)
             grad = Aggregator.backward(ctx, torch.from_numpy(G[b0:b1]).cuda())[1]
             q = graph.comm_buf_for_quantization
             return (out.cpu().numpy(), grad.cpu().numpy(), q.quantized_recv_data_buf.cpu().numpy(),
@@ -371,3 +377,55 @@ def test_config3_downscaled_codes_bit_exact(cuda_lib, monkeypatch, bits):
         np.testing.assert_array_equal(codes, wc)
         # the lossy halo keeps the aggregate within one quantisation step per remote term
         assert np.abs(out - want[b0:b1]).max() <= (2.5 if bits == 2 else 0.05) * max(1.0, scale_abs[b0:b1].max())
+
+
+@pytest.mark.parametrize("P,bits,is_pre,F,groups", [
+    (2, 32, False, 128, 1), (4, 32, False, 256, 1), (4, 32, False, 100, 3), (5, 32, False, 32, 2), (8, 32, False, 128, 3),
+    (3, 32, True, 128, 1), (2, 2, False, 128, 1), (4, 2, False, 256, 3), (3, 2, True, 128, 1), (3, 8, False, 64, 1),
+])
+def test_push_transport_matches_all_to_all(cuda_lib, P, bits, is_pre, F, groups):
+    """Communicator(transport="push"): halo rows stored straight into the receivers' buffers by
+    gnnagg_push_rows (gathered on the way), signals instead of a collective.  With one group of peers the
+    outputs, gradients and wire codes equal the all-to-all path bit for bit; with several groups (fp32 halo,
+    plain path) the peers' contributions are added in arrival order: 1e-5 of the summed magnitudes.  Two
+    forward + backward rounds, so that buffers are reused behind their "free" signals."""
+    from gnn_benchmark_b200 import Communicator, Quantizer_for_all_procs, TimeRecorder, graphgen
+    from gnn_benchmark_b200.aggregator import Aggregator
+    from gnn_benchmark_b200.data_manager.DataLoader import build_graph
+
+    begin_np, src, dst = make_graph(17 * P + F + bits, P, 400, 6)
+    N = int(begin_np[-1])
+    begin = torch.from_numpy(begin_np)
+    rng = np.random.default_rng(5)
+    X = rng.standard_normal((2, N, F)).astype(np.float32)
+    G = rng.standard_normal((2, N, F)).astype(np.float32)
+    s_t, d_t = torch.from_numpy(src).cuda(), torch.from_numpy(dst).cuda()
+    Quantizer_for_all_procs(P, bits)
+    TimeRecorder(1, 1)
+    results = {}
+    for transport in ("all_to_all", "push"):
+        Communicator(bits, is_async=True, transport=transport, push_groups=groups)
+
+        def rank_fn(rank):
+            local, remote = graphgen.partition_edges(s_t, d_t, begin, rank)
+            graph = build_graph(local, remote, begin, rank, P, F, bits, is_pre, device="cuda")
+            assert (graph.push_plan is not None) == (transport == "push")
+            b0, b1 = int(begin[rank]), int(begin[rank + 1])
+            got = []
+            for k in range(2):
+                ctx = SimpleNamespace()
+                out = Aggregator.forward(ctx, graph, torch.from_numpy(X[k, b0:b1]).cuda(), 0, bits, is_pre, True)
+                grad = Aggregator.backward(ctx, torch.from_numpy(G[k, b0:b1]).cuda())[1]
+                got += [out.cpu().numpy(), grad.cpu().numpy()]
+                if bits != 32:
+                    q = graph.comm_buf_for_quantization
+                    got += [q.quantized_recv_data_buf.cpu().numpy(), q.quantized_send_data_buf.cpu().numpy()]
+            return got
+
+        results[transport] = FakeWorld(P).run(rank_fn)
+    for r in range(P):
+        for a, b in zip(results["all_to_all"][r], results["push"][r]):
+            if groups == 1 or a.dtype == np.uint8:
+                np.testing.assert_array_equal(a, b)
+            else:
+                assert np.abs(a - b).max() <= 1e-5 * max(1.0, np.abs(a).max())

@@ -234,3 +234,78 @@ def test_bf16_casts(cuda_lib):
     back = torch.empty_like(x)
     _cast(h, back)
     assert torch.equal(back, h.float())
+
+
+# ---- SpMM whose epilogue quantises + packs (gnnagg_spmm_quant_pack) ------------------------------------
+def _slot_matrix(rng, slots, K, hub=False):
+    """CSR (slots x K): short rows (a post source is one nonzero, a pre destination a few), empty rows,
+    optionally one row far longer than an SpMM chunk."""
+    deg = rng.integers(0, 7, size=slots)
+    deg[rng.random(slots) < 0.3] = 1
+    if hub and slots:
+        deg[slots // 3] = min(K, 1500)
+    rowptr = np.concatenate([[0], np.cumsum(deg)]).astype(np.int64)
+    col = np.concatenate([np.sort(rng.choice(K, size=d, replace=False)) for d in deg] + [np.zeros(0, np.int64)])
+    val = rng.standard_normal(col.shape[0]).astype(np.float32)
+    val[rng.random(col.shape[0]) < 0.5] = 1.0  # the plans' matrices are unit-valued
+    return rowptr, col.astype(np.int64), val
+
+
+def _fused(rowptr, col, val, K, X, seg, bits):
+    from gnn_benchmark_b200.spmm_kernel import spmm_quant_pack
+
+    slots, F, epb = int(seg[-1]), X.shape[1], 8 // bits
+    prow = int(sum((int(b) - int(a) + epb - 1) // epb for a, b in zip(seg[:-1], seg[1:])))
+    codes = torch.full((prow, F), 0xAB, dtype=torch.uint8, device="cuda")
+    params = torch.full((slots, 2), float("nan"), device="cuda")
+    pb = torch.zeros((slots, 2), dtype=torch.bfloat16, device="cuda")
+    spmm_quant_pack(to_dev(rowptr), to_dev(col, torch.int32), to_dev(val), K, to_dev(X), codes, params, pb,
+                    to_dev(np.asarray(seg, dtype=np.int32)), len(seg) - 1, bits)
+    torch.cuda.synchronize()
+    return codes.cpu().numpy(), params.cpu().numpy(), pb.float().cpu().numpy()
+
+
+@pytest.mark.parametrize("F", [4, 32, 64, 100, 128, 172, 256, 512])
+@pytest.mark.parametrize("seg", [[0, 6], [0, 5, 5, 18, 19, 64, 256], [0, 0, 0, 3], [0, 1023]])
+def test_spmm_quant_pack_equals_reference_chain_then_quantise(cuda_lib, F, seg):
+    """Codes and parameters of the fused kernel against the oracle's SpMM (sequential FMA chain, the
+    reference's order) followed by its int2 quantiser: bit-exact for every width, hub row included."""
+    rng = np.random.default_rng(F + 13 * len(seg))
+    slots, K = seg[-1], 700
+    rowptr, col, val = _slot_matrix(rng, slots, K, hub=slots > 100)
+    X = rng.standard_normal((K, F)).astype(np.float32)
+    summed = oracle.spmm(rowptr, col, val, X)
+    want_codes, want_params = oracle.quantize_int2_for_all_procs(summed, seg)
+    codes, params, pb = _fused(rowptr, col, val, K, X, seg, 2)
+    np.testing.assert_array_equal(codes, want_codes)
+    bits_eq(params, want_params)
+    bits_eq(pb, oracle.bf16_round(want_params))
+
+
+@pytest.mark.parametrize("bits", [2, 4, 8])
+@pytest.mark.parametrize("F", [100, 128, 256])
+def test_spmm_quant_pack_equals_two_calls(cuda_lib, bits, F):
+    """Same bytes as SPMM_forward into an fp32 buffer followed by gnnagg_quant_pack_rows (F > 64, rows
+    shorter than a chunk: both sum in CSR order)."""
+    from gnn_benchmark_b200 import SparseTensor, SPMM_forward
+
+    rng = np.random.default_rng(bits * 100 + F)
+    seg = [0, 37, 37, 201, 333]
+    slots, K = seg[-1], 900
+    rowptr, col, val = _slot_matrix(rng, slots, K)
+    X = rng.standard_normal((K, F)).astype(np.float32)
+    A = SparseTensor(rowptr=to_dev(rowptr), col=to_dev(col), value=to_dev(val), sparse_sizes=(slots, K))
+    buf = torch.empty(slots, F, device="cuda")
+    SPMM_forward(A, to_dev(X), buf, accumulate=False)
+    want_codes, want_params, want_pb, _, _ = gpu_quant_all_procs(buf.cpu().numpy(), seg, bits=bits)
+    codes, params, pb = _fused(rowptr, col, val, K, X, seg, bits)
+    np.testing.assert_array_equal(codes, want_codes.cpu().numpy())
+    bits_eq(params, want_params.cpu().numpy())
+    bits_eq(pb, want_pb.float().cpu().numpy())
+
+
+def test_spmm_quant_pack_refuses_unsupported_width(cuda_lib):
+    rng = np.random.default_rng(0)
+    rowptr, col, val = _slot_matrix(rng, 8, 20)
+    with pytest.raises(RuntimeError, match="F %"):
+        _fused(rowptr, col, val, 20, rng.standard_normal((20, 6)).astype(np.float32), [0, 8], 2)
