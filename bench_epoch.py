@@ -45,7 +45,7 @@ def aggregation_passes(model_name: str, dims) -> int:
     return L + back
 
 
-def main():
+def make_parser():
     ap = argparse.ArgumentParser()
     ap.add_argument("--model", default="gcn", choices=["gcn", "sage"])
     ap.add_argument("--nodes", type=int, default=111_000_000)
@@ -68,16 +68,24 @@ def main():
     ap.add_argument("--kernel-table", default="",
                     help="after the timed epochs, run one more under torch.profiler and write rank 0's per-kernel "
                          "device-time table to this file (a breakdown, never a timing)")
-    args = ap.parse_args()
+    ap.add_argument("--transport", default="all_to_all", choices=["all_to_all", "push"],
+                    help="halo exchange: one NCCL collective per aggregation, or rows stored straight into the receivers' buffers")
+    return ap
 
+
+def run(args):
+    """One measurement; returns the result line (a dict) on rank 0, None elsewhere.  Joins the process group that
+    is already there (bench.py's multi-GPU leg calls this in-process) or starts one under torchrun."""
     dense.MODE = args.dense
-    comm = Communicator(args.bits, is_async=True)
+    multi = int(os.environ.get("WORLD_SIZE", "1")) > 1
+    comm = Communicator(args.bits, is_async=True, transport=args.transport if multi else "all_to_all")
     if "RANK" in os.environ:
         rank, world = comm.init_dist_group("nccl")
     else:
         rank, world = 0, 1
         torch.cuda.set_device(0)
     device = torch.device("cuda", torch.cuda.current_device())
+    torch.cuda.reset_peak_memory_stats()
     Quantizer_for_all_procs(world, args.bits)
     t0 = time.time()
     src, dst, begin = graphgen.partitioned_in_edges("chung_lu", args.nodes, args.edges, args.seed, rank, world, device,
@@ -86,7 +94,7 @@ def main():
     nnz_rank = int(local.shape[1] + remote.shape[1])
     del src, dst
     dims = [args.in_channels] + [args.hidden] * (args.layers - 1) + [args.out_channels]
-    lean = bool(args.lean_halo) and args.bits in (2, 4, 8) and not args.pre and world > 1
+    lean = bool(args.lean_halo) and args.bits in (2, 4, 8) and world > 1
     graph = build_graph(local, remote, begin, rank, world, max(dims), args.bits, bool(args.pre), device=device,
                         lean_halo=lean)
     del local, remote
@@ -120,21 +128,23 @@ def main():
     if world > 1:
         dist.all_reduce(tmax, op=dist.ReduceOp.MAX)
         dist.all_reduce(tsum, op=dist.ReduceOp.SUM)
+    result = None
     if rank == 0:
         passes = aggregation_passes(args.model, dims)
         epoch_s = float(tmax[0])
-        print(json.dumps({
+        result = ({
             "metric": "epoch_time", "value": epoch_s, "unit": "s", "higher_is_better": False, "n_gpus": world,
             "aggregated_edges_per_s": float(tsum[1]) * passes / epoch_s, "aggregation_passes_per_step": passes,
             "config": {"model": args.model, "dims": dims, "nodes": args.nodes, "directed_edges_after_symmetrising":
                        int(tsum[1]), "halo": f"{args.bits}-bit" + (" pre/post" if args.pre else "") + (", no fp32 staging buffers" if lean else ""),
                        "halo_rows_sent_per_exchange": int(tsum[2]), "graph": "Chung-Lu gamma=2.1, relabelled",
                        "epochs_timed": len(times) - 1, "dropout": args.dropout, "optimizer": "Adam lr 0.01",
+                       "exchange": comm.transport,
                        "dense": ("tcgen05, 3 TF32 products per fp32 product, fp32 accumulate" if args.dense == "tf32x3"
                                  else "cuBLAS fp32")},
             "losses": [round(x, 5) for x in losses], "epoch_times_s": [round(x, 4) for x in times],
             "peak_mem_gib_max_rank": float(tmax[3]), "setup_s": round(setup_s, 1), "data": "synthetic",
-        }), flush=True)
+        })
     if args.kernel_table:
         from torch.profiler import ProfilerActivity, profile
 
@@ -145,7 +155,17 @@ def main():
         if rank == 0:
             with open(args.kernel_table, "w") as fh:
                 fh.write(prof.key_averages().table(sort_by="cuda_time_total", row_limit=60, max_name_column_width=90))
-    if world > 1:
+    del model, optimizer, data, graph
+    torch.cuda.empty_cache()
+    return result
+
+
+def main():
+    args = make_parser().parse_args()
+    result = run(args)
+    if result is not None:
+        print(json.dumps(result), flush=True)
+    if dist.is_initialized():
         dist.barrier()
         dist.destroy_process_group()
 

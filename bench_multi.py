@@ -5,9 +5,14 @@ Workload "aggregate_rmat22_per_gpu" (weak scaling): R-MAT with 2^22 vertices per
 N contiguous partitions -- the reference's 1-D partitioning across MPI ranks.  Every rank generates
 the edge stream from the same seed and keeps the in-edges of its own vertex range, so the global
 graph is never held by one process.  One step = Aggregator forward + backward at F = 32, 128, 256:
-send-side gather, halo all-to-all over NCCL overlapped with the local SpMM, remote SpMM; backward the
-transposed chain with the deterministic scatter-add.  Adjacency values are GCN-normalised
-(d_dst^-1/2 d_src^-1/2; remote degrees fetched once with the halo exchange itself).
+halo rows gathered and stored straight into the receivers' buffers (or gathered into a staging buffer
+and exchanged with one NCCL all-to-all: --exchange all_to_all), local SpMM meanwhile, remote SpMM on
+arrival; backward the transposed chain with the deterministic scatter-add.  Adjacency values are
+GCN-normalised (d_dst^-1/2 d_src^-1/2; remote degrees fetched once with the halo exchange itself).
+
+Before anything is timed the exchange path is checked on a small instance (`check` in the JSON line);
+after the aggregation legs the full-batch epoch times of BASELINE configurations 4 and 5 are measured
+on the same GPUs (`epoch`).
 """
 import json
 import math
@@ -97,27 +102,184 @@ def _run_e2e(args, graph, widths, num_bits, is_pre, n, nnz_total, device):
             "pipeline": "h2d / kernels / d2h on three streams, two buffer pairs"}
 
 
+def run_check(comm, rank, world, device, args):
+    """Correctness of the exchange path as it runs here (real NCCL / peer stores, real overlap), on a small
+    instance of the benchmark's graph family (2^14 vertices per GPU), before anything is timed.
+
+      fp32 halo   every rank's forward output and input gradient against A.X / A^T.G computed in fp64 with
+                  plain torch ops from the global edge list: error relative to sum |a||x| of the row;
+      2-bit halo  and pre/post plan: the overlapped run against the same aggregation done without any
+                  overlap (blocking all-to-all, device synchronised after every call): bit for bit, plus a
+                  checksum of the codes both runs put on the wire.
+    Returns the `check` record of the JSON line; `ok` false makes the benchmark exit non-zero."""
+    import torch.distributed as dist
+
+    from gnn_benchmark_b200 import Quantizer_for_all_procs, graphgen
+    from gnn_benchmark_b200.aggregator import Aggregator
+    from gnn_benchmark_b200.data_manager.DataLoader import build_graph
+
+    scale = 14 + int(math.ceil(math.log2(world)))
+    n, F = 1 << scale, 128
+    s, d = graphgen.rmat_edges(scale, 16, seed=77, device=device)
+    s, d = graphgen.symmetrize(s, d, n)
+    s, d = graphgen.relabel(s, d, n, seed=78)
+    begin = graphgen.contiguous_partitions(n, world)
+    b0, b1 = int(begin[rank]), int(begin[rank + 1])
+    g = torch.Generator(device=device).manual_seed(79)  # same stream on every rank: global operands
+    X = torch.randn(n, F, device=device, generator=g)
+    G = torch.randn(n, F, device=device, generator=g)
+    local, remote = graphgen.partition_edges(s, d, begin, rank)
+
+    def run(bits, is_pre, overlapped):
+        saved = (comm.num_bits, comm.transport, comm.is_async)
+        comm.num_bits = bits
+        if not overlapped:
+            comm.transport, comm.is_async = "all_to_all", False
+        Quantizer_for_all_procs(world, bits if bits in (2, 4, 8) else 2)
+        graph = build_graph(local, remote, begin, rank, world, F, bits if bits in (2, 4, 8) else 2, is_pre, device=device)
+        ctx = SimpleNamespace()
+        out = Aggregator.forward(ctx, graph, X[b0:b1].contiguous(), 0, bits, is_pre, True)
+        if not overlapped:
+            torch.cuda.synchronize()
+        codes = 0
+        if bits != 32:
+            codes = int(graph.comm_buf_for_quantization.quantized_send_data_buf.to(torch.int64).sum())
+        grad = Aggregator.backward(ctx, G[b0:b1].contiguous())[1]
+        torch.cuda.synchronize()
+        comm.num_bits, comm.transport, comm.is_async = saved
+        return out, grad, codes
+
+    res = {}
+    # fp32 against the global product in fp64
+    out, grad, _ = run(32, False, True)
+    A_dst, A_src = d, s  # edge (src -> dst): out[dst] += x[src]
+    want_out = torch.zeros(n, F, dtype=torch.float64, device=device).index_add_(0, A_dst, X.double()[A_src])[b0:b1]
+    want_grad = torch.zeros(n, F, dtype=torch.float64, device=device).index_add_(0, A_src, G.double()[A_dst])[b0:b1]
+    sc_out = torch.zeros(n, F, dtype=torch.float64, device=device).index_add_(0, A_dst, X.double().abs()[A_src])[b0:b1]
+    sc_grad = torch.zeros(n, F, dtype=torch.float64, device=device).index_add_(0, A_src, G.double().abs()[A_dst])[b0:b1]
+    err = max(float(((out.double() - want_out).abs() / sc_out.clamp(min=1e-30)).max()),
+              float(((grad.double() - want_grad).abs() / sc_grad.clamp(min=1e-30)).max()))
+    # 2-bit halo and the pre/post plan: overlapped run == run without overlap
+    same = {}
+    sums = {}
+    for name, bits, is_pre in (("int2", 2, False), ("pre_post_fp32", 32, True), ("pre_post_int2", 2, True)):
+        a = run(bits, is_pre, True)
+        b = run(bits, is_pre, False)
+        same[name] = bool(torch.equal(a[0], b[0]) and torch.equal(a[1], b[1]) and a[2] == b[2])
+        sums[name] = a[2]
+        if name == "int2":  # sanity against the exact product: a 2-bit halo is coarse, not wrong
+            q_err = float((a[0].double() - want_out).abs().max() / want_out.abs().max())
+    stats = torch.tensor([err, q_err] + [0.0 if v else 1.0 for v in same.values()], dtype=torch.float64, device=device)
+    dist.all_reduce(stats, op=dist.ReduceOp.MAX)
+    total = torch.tensor([float(sums["int2"])], dtype=torch.float64, device=device)
+    dist.all_reduce(total, op=dist.ReduceOp.SUM)
+    ok = bool(stats[0] <= 1e-5 and stats[1] <= 0.5 and float(stats[2:].max()) == 0.0)
+    res = {"instance": f"R-MAT scale {scale}, {world} partitions, F={F}", "fp32_max_rel_err": float(stats[0]),
+           "int2_max_err_vs_exact_over_max": float(stats[1]),
+           "overlapped_equals_unoverlapped": {k: bool(stats[2 + i] == 0.0) for i, k in enumerate(same)},
+           "int2_codes_checksum": int(total.item()), "ok": ok}
+    return res
+
+
+def _timed_steps(step, steps, device):
+    """ms per step, max over ranks, CUDA events between barriers."""
+    torch.cuda.synchronize()
+    dist.barrier()
+    torch.cuda.synchronize()
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    a.record()
+    for _ in range(steps):
+        step()
+    b.record()
+    torch.cuda.synchronize()
+    dist.barrier()
+    t = torch.tensor([a.elapsed_time(b) / steps], dtype=torch.float64, device=device)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    return float(t.item())
+
+
+class _NoExchange(object):
+    """Context: the same step with the stores and signals of the push transport left out (outputs are then
+    meaningless).  The difference to the full step is the exchange time that is NOT hidden behind compute."""
+
+    class _Done(object):
+        def wait(self):
+            return True
+
+    def __init__(self, plan):
+        self.plan = plan
+
+    def __enter__(self):
+        self.push, self.signal = self.plan.push, self.plan.peers.signal
+        self.plan.push = lambda *a, **k: None
+        self.plan.peers.signal = lambda: _NoExchange._Done()
+
+    def __exit__(self, *a):
+        self.plan.push, self.plan.peers.signal = self.push, self.signal
+
+
+def _epoch_legs(args, world):
+    """Full-batch epoch time (the other half of the metric) on this job's GPUs: BASELINE configuration 4
+    (products-shaped 3-layer GraphSAGE, the whole graph cut into `world` partitions: strong scaling) and
+    configuration 5 (papers100M-shaped 3-layer GCN, 2-bit halo) with 111 M / 8 vertices per GPU -- the full
+    configuration at 8 GPUs, the same per-GPU load below (the full graph does not fit 4 GPUs)."""
+    import bench_epoch
+
+    transport = "push" if args.exchange == "pipelined" else "all_to_all"
+    legs = {}
+    runs = [
+        ("config4_sage_fp32", ["--model", "sage", "--nodes", "2450000", "--edges", "61900000", "--in-channels", "100",
+                               "--hidden", "256", "--out-channels", "47", "--train-frac", "0.08", "--bits", "32", "--epochs", "5"]),
+        ("config4_sage_int2", ["--model", "sage", "--nodes", "2450000", "--edges", "61900000", "--in-channels", "100",
+                               "--hidden", "256", "--out-channels", "47", "--train-frac", "0.08", "--bits", "2", "--epochs", "5"]),
+        ("config5_gcn_int2", ["--model", "gcn", "--nodes", str(111_000_000 * world // 8), "--edges",
+                              str(1_600_000_000 * world // 8), "--in-channels", "128", "--hidden", "256", "--out-channels",
+                              "172", "--train-frac", "0.01", "--bits", "2", "--epochs", "4"]),
+    ]
+    for name, argv in runs:
+        try:
+            r = bench_epoch.run(bench_epoch.make_parser().parse_args(argv + ["--transport", transport]))
+            if r is not None:
+                legs[name] = {"epoch_s": r["value"], "aggregated_edges_per_s": r["aggregated_edges_per_s"],
+                              "aggregation_passes_per_step": r["aggregation_passes_per_step"], "config": r["config"],
+                              "losses": r["losses"], "peak_mem_gib_max_rank": r["peak_mem_gib_max_rank"],
+                              "setup_s": r["setup_s"]}
+        except Exception as exc:  # the aggregation line above must not depend on these legs
+            legs[name] = {"error": repr(exc)[:300]}
+            torch.cuda.empty_cache()
+    return legs
+
+
 def run_multi_gpu(args):
     import benchlib as bench
     from gnn_benchmark_b200 import Communicator, Quantizer_for_all_procs, TimeRecorder, graphgen
     from gnn_benchmark_b200.aggregator import Aggregator
     from gnn_benchmark_b200.data_manager.DataLoader import build_graph
 
-    num_bits = int(os.environ.get("GNNAGG_BENCH_BITS", "32"))  # halo format of the headline number
-    is_pre = os.environ.get("GNNAGG_BENCH_PRE", "0") == "1"
-    # GNNAGG_BENCH_PIPELINE=1: fp32 halo exchanged peer by peer, each peer's rows aggregated on arrival
-    # (measured equal to the one-shot all-to-all at 2 and 4 GPUs, so the one-shot exchange is the default)
-    pipeline = os.environ.get("GNNAGG_BENCH_PIPELINE", "0") == "1"
-    comm = Communicator(num_bits, is_async=True, pipeline_peers=pipeline)
+    num_bits, is_pre = args.bits, bool(args.pre)
+    transport = "push" if args.exchange == "pipelined" else "all_to_all"
+    comm = Communicator(num_bits, is_async=True, transport=transport, push_groups=3)
     rank, world = comm.init_dist_group("nccl")
     device = torch.device("cuda", torch.cuda.current_device())
+    TimeRecorder(1, 1, enabled=False)
+    widths = args.widths
+    scale = args.scale + int(math.ceil(math.log2(world)))
+
+    check = None
+    if not args.no_check:
+        check = run_check(comm, rank, world, device, args)
+        if not check["ok"]:
+            if rank == 0:
+                print(json.dumps({"metric": "aggregated_edges_per_s", "value": None, "n_gpus": world, "check": check,
+                                  "error": "the exchange path failed its correctness check; nothing was timed"}), flush=True)
+            dist.barrier()
+            dist.destroy_process_group()
+            raise SystemExit(1)
+        torch.cuda.empty_cache()
+
     # the graph always carries the packed-halo buffers, so the 2-bit variant can be timed on it too
     plan_bits = num_bits if num_bits in (2, 4, 8) else 2
     Quantizer_for_all_procs(world, plan_bits)
-    TimeRecorder(1, 1, enabled=False)
-    widths = bench.WIDTHS
-    scale = bench.SCALE + int(math.ceil(math.log2(world)))
-
     t0 = time.time()
     src, dst, begin = graphgen.partitioned_in_edges("rmat", 1 << scale, bench.EDGE_FACTOR << scale, bench.SEED, rank, world,
                                                     device, relabel=world > 1, scale=scale)
@@ -137,110 +299,107 @@ def run_multi_gpu(args):
     X = {F: torch.randn(n, F, device=device, generator=g) for F in widths}
     G = {F: torch.randn(n, F, device=device, generator=g) for F in widths}
 
-    def step(bits=num_bits):
-        for F in widths:
-            ctx = SimpleNamespace()
-            Aggregator.forward(ctx, graph, X[F], 0, bits, is_pre, True)
-            Aggregator.backward(ctx, G[F])
+    def make_step(bits):
+        def step():
+            for F in widths:
+                ctx = SimpleNamespace()
+                Aggregator.forward(ctx, graph, X[F], 0, bits, is_pre, True)
+                Aggregator.backward(ctx, G[F])
+        return step
 
-    def time_variant(bits, steps=3):
-        """ms per step (max over ranks) with another halo format on the same graph."""
+    def time_variant(bits, steps=3, exchange=None):
+        """ms per step (max over ranks) with another halo format / exchange on the same graph."""
+        saved = (comm.num_bits, comm.transport)
         comm.num_bits = bits
+        if exchange is not None:
+            comm.transport = exchange
+        step = make_step(bits)
         for _ in range(2):
-            step(bits)
-        torch.cuda.synchronize()
-        dist.barrier()
-        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        a.record()
-        for _ in range(steps):
-            step(bits)
-        b.record()
-        torch.cuda.synchronize()
-        dist.barrier()
-        t = torch.tensor([a.elapsed_time(b) / steps], dtype=torch.float64, device=device)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        comm.num_bits = num_bits
-        return float(t.item())
+            step()
+        ms = _timed_steps(step, steps, device)
+        comm.num_bits, comm.transport = saved
+        return ms
 
+    step = make_step(num_bits)
     warmup = max(args.warmup, 3)
     for _ in range(warmup):
         step()
-    torch.cuda.synchronize()
-    dist.barrier()
-    torch.cuda.synchronize()
     with bench.ClockSampler(torch.cuda.current_device()) as clk:
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        e0.record()
-        for _ in range(args.steps):
-            step()
-        e1.record()
-        torch.cuda.synchronize()
-        dist.barrier()
-        torch.cuda.synchronize()
-    t_local = e0.elapsed_time(e1) / 1e3 / args.steps
-    stats = torch.tensor([t_local, float(nnz), float(sum(graph.comm_splits.send_splits)),
-                          float(sum(graph.comm_splits.recv_splits))], dtype=torch.float64, device=device)
-    t_max = stats[0:1].clone()
-    dist.all_reduce(t_max, op=dist.ReduceOp.MAX)
-    tot = stats.clone()
-    dist.all_reduce(tot, op=dist.ReduceOp.SUM)
-    t_step = float(t_max.item())
-    edges_per_step = 2 * len(widths) * float(tot[1].item())
+        t_step = _timed_steps(step, args.steps, device) / 1e3
+    stats = torch.tensor([float(nnz), float(sum(graph.comm_splits.send_splits)), float(sum(graph.comm_splits.recv_splits))],
+                         dtype=torch.float64, device=device)
+    dist.all_reduce(stats, op=dist.ReduceOp.SUM)
+    nnz_total = float(stats[0].item())
+    edges_per_step = 2 * len(widths) * nnz_total
 
-    # the exchange alone (not overlapped), widest feature, forward direction: NVLink fraction
-    nv = None
-    if world > 1 and num_bits == 32:
-        F = max(widths)
-        graph.comm_buf.resize_buffer(graph.comm_splits, F, 32)
-        ts = []
-        for _ in range(5):
-            dist.barrier()
-            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            a.record()
-            h = comm.comm_with_fp32(graph.comm_splits, graph.comm_buf, "forward")
-            if h is not None:
-                h.wait()
-            b.record()
-            torch.cuda.synchronize()
-            ts.append(a.elapsed_time(b) / 1e3)
-        t_x = torch.tensor([sorted(ts)[len(ts) // 2]], dtype=torch.float64, device=device)
-        dist.all_reduce(t_x, op=dist.ReduceOp.MAX)
-        sent = max(sum(graph.comm_splits.send_splits), sum(graph.comm_splits.recv_splits)) * F * 4
-        sent_t = torch.tensor([float(sent)], dtype=torch.float64, device=device)
-        dist.all_reduce(sent_t, op=dist.ReduceOp.MAX)
-        gbs = float(sent_t.item()) / float(t_x.item()) / 1e9
-        nv = {"exchange_ms": float(t_x.item()) * 1e3, "bytes_per_rank_per_direction": int(sent_t.item()),
-              "achieved_gbs": gbs, "frac_of_measured_770": gbs / 770.0, "frac_of_nominal_900": gbs / 900.0, "F": F}
+    # how much of the exchange is NOT hidden behind compute, and what the links carry
+    exposed = nv = None
+    plan = getattr(graph, "push_plan", None)
+    if plan is not None:
+        with _NoExchange(plan):
+            compute_ms = _timed_steps(step, 3, device)
+        exposed = {"ms_per_step": t_step * 1e3 - compute_ms, "compute_only_ms_per_step": compute_ms,
+                   "how": "step time minus the same step with the stores and signals left out"}
+        if num_bits == 32 and not is_pre:
+            F = max(widths)
+            graph.comm_buf.resize_buffer(graph.comm_splits, F, 32)
 
-    variants = None
+            def exchange_only():
+                cur = torch.cuda.current_stream()
+                plan.push("forward", "rows", X[F], 4 * F, (rank + 1) % world, world - 1, graph.idx_nodes_send_to_others_i32)
+                plan.peers.signal().wait()
+
+            exchange_only()
+            ms = _timed_steps(exchange_only, 5, device)
+            sent = torch.tensor([float(max(sum(graph.comm_splits.send_splits), sum(graph.comm_splits.recv_splits)) * F * 4)],
+                                dtype=torch.float64, device=device)
+            dist.all_reduce(sent, op=dist.ReduceOp.MAX)
+            gbs = float(sent.item()) / (ms / 1e3) / 1e9
+            nv = {"exchange_ms": ms, "bytes_per_rank_per_direction": int(sent.item()), "achieved_gbs": gbs,
+                  "frac_of_measured_770": gbs / 770.0, "frac_of_nominal_900": gbs / 900.0, "F": F,
+                  "what": "gather + store of all halo rows into the peers' buffers + signal, nothing else running"}
+
+    variants = {}
     if world > 1 and num_bits == 32:
         ms2 = time_variant(2)
-        variants = {"int2_halo": {"ms_per_step": ms2, "value": edges_per_step / (ms2 / 1e3), "unit": "edges/s",
-                                  "note": "per-row min/max 2-bit codes + bf16 parameters on the wire (the "
-                                          "reference's quantised mode), unpack fused into the receive-side SpMM"}}
-    e2e = _run_e2e(args, graph, widths, num_bits, is_pre, n, float(tot[1].item()), device)
+        variants["int2_halo"] = {"ms_per_step": ms2, "value": edges_per_step / (ms2 / 1e3), "unit": "edges/s",
+                                 "note": "per-row min/max 2-bit codes + bf16 parameters on the wire (the reference's "
+                                         "quantised mode); pack fused into the gather / the transposed SpMM, unpack fused "
+                                         "into the receive-side SpMM"}
+    if plan is not None:
+        ms_a2a = time_variant(num_bits, exchange="all_to_all")
+        variants["nccl_all_to_all"] = {"ms_per_step": ms_a2a, "value": edges_per_step / (ms_a2a / 1e3), "unit": "edges/s",
+                                       "note": "same graph and kernels, one NCCL all-to-all per aggregation instead of "
+                                               "direct stores (send-side gather into a staging buffer)"}
+    e2e = None if args.no_e2e else _run_e2e(args, graph, widths, num_bits, is_pre, n, nnz_total, device)
     clocks = clk.summary()
+    halo_rows = int(stats[1].item())
+    del graph, X, G, plan
+    torch.cuda.empty_cache()
+    epochs = None if args.no_epoch else _epoch_legs(args, world)
     if rank == 0:
         peak, peak_kind = bench.measured_peak_gbs()
-        cfg = bench.workload_config(world)
-        cfg.update({"rows_per_gpu": n, "nnz_total": int(tot[1].item()), "partitions": world,
-                    "halo_rows_sent_total": int(tot[2].item()), "halo": f"{num_bits}-bit" + (" pre/post" if is_pre else ""),
-                    "exchange": "peer-by-peer, aggregated on arrival" if (pipeline and num_bits == 32 and not is_pre)
-                    else "one all-to-all per aggregation",
+        cfg = bench.workload_config(world, args.scale, widths)
+        cfg.update({"rows_per_gpu": n, "nnz_total": int(nnz_total), "partitions": world,
+                    "halo_rows_sent_total": halo_rows, "halo": f"{num_bits}-bit" + (" pre/post" if is_pre else ""),
+                    "exchange": ("rows stored straight into the receivers' buffers (gnnagg_push_rows), peers served in "
+                                 f"{min(comm.push_groups, world - 1)} groups, each aggregated on arrival"
+                                 if transport == "push" else "one NCCL all-to-all per aggregation"),
                     "setup_s": round(setup_s, 1), "parallelism": f"1-D vertex partition x{world}"})
         by = sum(bench.spmm_algorithmic_bytes(n, nnz, F) for F in widths) * 2
+        launches_per_call = 2 * 2 + (1 if transport == "push" else 1)  # local + remote SpMM (chunk + fix-up), store / gather
         line = {
             "metric": "aggregated_edges_per_s", "value": edges_per_step / t_step, "unit": "edges/s", "n_gpus": world,
             "steps": args.steps, "warmup": warmup, "ms_per_step": t_step * 1e3, "higher_is_better": True,
             "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic", "config": cfg,
-            "clocks": clocks,
-            "e2e": e2e,
-            "gpu_launches": args.steps * len(widths) * (2 * 2 * (1 if world == 1 else 2) + (1 if world > 1 else 0)),
+            "value_int2_halo": variants.get("int2_halo", {}).get("value"),
+            "check": check, "clocks": clocks, "e2e": e2e,
+            "gpu_launches": args.steps * len(widths) * 2 * launches_per_call,
             "roofline": {"bound": "hbm", "kernel": "spmm_chunk_kernel (all SpMM calls of a step, rank 0)",
                          "achieved": by / t_step / 1e9, "peak": peak, "unit": "GB/s", "frac": by / t_step / 1e9 / peak,
-                         "peak_kind": peak_kind + " copy bandwidth", "traffic": None,
-                         "note": "whole step including the exchange; SpMM algorithmic bytes only"},
-            "nvlink": nv, "variants": variants, "cpu_baseline": None,
+                         "frac_is": "algorithmic SpMM bytes of rank 0 / whole step time (exchange included) / peak",
+                         "peak_kind": peak_kind + " copy bandwidth", "traffic": None},
+            "exposed_exchange": exposed, "nvlink": nv, "variants": variants, "cpu_baseline": None, "epoch": epochs,
         }
         print(json.dumps(line), flush=True)
     dist.barrier()
