@@ -11,11 +11,12 @@ from .time_recorder import TimeRecorder
 from .data_manager import (CommBuffer, CommBufferForQuantization, CommSplits, DistributedGraph,
                            DistributedGraphForPre, DataProcessor, DataProcessorForPreAggresive, load_data)
 from .communicator import Communicator
+from .assigner import Assigner
 from .aggregator import Aggregator
 
 __all__ = [
     "SparseTensor", "SPMM_forward", "SPMM_backward", "build_plan", "QuantizerForPureBits", "QuantizerForMixedBits",
     "Quantizer_for_all_procs", "TimeRecorder", "CommBuffer", "CommBufferForQuantization", "CommSplits",
     "DistributedGraph", "DistributedGraphForPre", "DataProcessor", "DataProcessorForPreAggresive", "load_data",
-    "Communicator", "Aggregator",
+    "Communicator", "Aggregator", "Assigner",
 ]

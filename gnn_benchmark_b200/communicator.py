@@ -239,6 +239,60 @@ class Communicator(object):
             rec.record_communication_time(t)
         return handle
 
+    def comm_with_mixed_quantization(self, recv_buf, send_buf, recv_splits, send_splits, nodes_num_bits_tensor):
+        """Halo exchange with a bit width per row (communicator.py:383-489 of the reference; there the
+        call from comm() is commented out, the method itself is complete).  Every row of send_buf is
+        quantised with its own width from nodes_num_bits_tensor (8 / 4 / 2; fp32, one value per row) into
+        a ragged byte buffer (row i at [range[i], range[i+1]), range = cumsum(ceil(bits_i * F / 8))); the
+        parameters [bits, zero_point, scale] travel first, as bf16, so that the receiver can size its
+        byte buffer; then the codes.  Returns, like the reference,
+            (handle of the code exchange, quantized_recv_buf, dequantized_nodes_feat_range, dequantized_params)
+        for QuantizerForMixedBits.dequantize_intX_to_fp32(quantized_recv_buf, recv_buf, range, params)
+        after handle.wait().  The parameters the receiver decodes with are the bf16-rounded ones."""
+        from .quantizer import QuantizerForMixedBits
+
+        rec = TimeRecorder.ctx
+        dev = send_buf.device
+        num_send_nodes, num_recv_nodes = int(sum(send_splits)), int(sum(recv_splits))
+        feat_len = send_buf.size(1)
+        t = rec.start() if rec else None
+        send_params = torch.empty((num_send_nodes, 3), dtype=torch.float32, device=dev)
+        send_params[:, 0] = nodes_num_bits_tensor.to(dev)
+        quantized_nodes_feat_range = QuantizerForMixedBits.get_quantized_nodes_feat_range(
+            num_send_nodes, feat_len, send_params[:, 0])
+        quantized_send_buf = torch.empty(int(quantized_nodes_feat_range[-1].item()), dtype=torch.uint8, device=dev)
+        QuantizerForMixedBits.quantize_fp32_to_intX(send_buf, quantized_send_buf, quantized_nodes_feat_range, send_params)
+        if rec:
+            rec.record_quantization_time(t)
+        t = rec.start() if rec else None
+        recv_params = torch.empty((num_recv_nodes, 3), dtype=torch.bfloat16, device=dev)
+        dist.all_to_all_single(recv_params, send_params.to(torch.bfloat16), list(recv_splits), list(send_splits),
+                               async_op=False)
+        dequantized_params = recv_params.to(torch.float32)
+        dequantized_nodes_feat_range = QuantizerForMixedBits.get_quantized_nodes_feat_range(
+            num_recv_nodes, feat_len, dequantized_params[:, 0])
+        quantized_recv_splits, quantized_send_splits = self.get_splits_for_comm_quantized_data(
+            recv_splits, send_splits, dequantized_nodes_feat_range, quantized_nodes_feat_range)
+        quantized_recv_buf = torch.empty(int(dequantized_nodes_feat_range[-1].item()), dtype=torch.uint8, device=dev)
+        comm_handle = dist.all_to_all_single(quantized_recv_buf, quantized_send_buf, quantized_recv_splits,
+                                             quantized_send_splits, async_op=self.is_async)
+        if rec:
+            rec.record_communication_time(t)
+        return comm_handle, quantized_recv_buf, dequantized_nodes_feat_range, dequantized_params
+
+    @staticmethod
+    def get_splits_for_comm_quantized_data(recv_splits, send_splits, dequantized_nodes_feat_range,
+                                           quantized_nodes_feat_range):
+        """Bytes per peer of the ragged code buffers (communicator.py:327-381): differences of the byte
+        ranges at the per-peer row boundaries."""
+        def per_peer(splits, byte_range):
+            rows = torch.zeros(len(splits) + 1, dtype=torch.int64)
+            rows[1:] = torch.as_tensor(splits, dtype=torch.int64).cumsum(0)
+            at = byte_range.to("cpu")[rows]
+            return (at[1:] - at[:-1]).tolist()
+
+        return per_peer(recv_splits, dequantized_nodes_feat_range), per_peer(send_splits, quantized_nodes_feat_range)
+
     def _exchange_together(self, parts):
         """Several all-to-alls with row splits -- parts = [(recv, send, recv_splits, send_splits), ...] --
         as ONE exchange.  The reference sends the parameters and the codes of a packed halo as two
