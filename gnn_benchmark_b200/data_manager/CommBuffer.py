@@ -25,8 +25,10 @@ class CommBuffer(object):
         self.lean = bool(lean) and bits in (2, 4, 8)
         buf_device = "meta" if self.lean else device
         if plan is not None and not self.lean:
-            self.send_buf = plan.region("send_buf", size_send_buf, torch.float32).zero_()
-            self.recv_buf = plan.region("recv_buf", size_recv_buf, torch.float32).zero_()
+            # no zero fill here: the allocation was zeroed before its address was published, and from then
+            # on a peer's rows may arrive at any time
+            self.send_buf = plan.region("send_buf", size_send_buf, torch.float32)
+            self.recv_buf = plan.region("recv_buf", size_recv_buf, torch.float32)
         else:
             self.send_buf = torch.zeros(size_send_buf, dtype=torch.float32, device=buf_device)
             self.recv_buf = torch.zeros(size_recv_buf, dtype=torch.float32, device=buf_device)
@@ -56,7 +58,7 @@ class CommBufferForQuantization(object):
 
             def wire(name, shape, dtype):  # the buffers that receive rows from other ranks
                 if plan is not None:
-                    return plan.region(name, shape, dtype).zero_()
+                    return plan.region(name, shape, dtype)  # zeroed before its address was published
                 return torch.zeros(shape, dtype=dtype, device=device)
 
             self.quantized_send_data_buf = wire("q_send_data", (sum(comm_splits.send_splits_int2), feat_len), torch.uint8)

@@ -52,12 +52,16 @@ class NcclPeers(object):
         return out
 
     def share(self, nbytes: int):
-        """-> (this rank's uint8 buffer of nbytes, [address of every rank's buffer as seen from this
-        device]).  nbytes must be the same on every rank."""
+        """-> (this rank's zero-filled uint8 buffer of nbytes, [address of every rank's buffer as seen from
+        this device]).  nbytes must be the same on every rank.  The fill is complete before any peer can
+        learn the address: once it is published, rows may arrive at any time."""
         import torch.distributed._symmetric_memory as symm_mem
 
         buf = symm_mem.empty(nbytes, dtype=torch.uint8, device=self.device)
+        buf.zero_()
+        torch.cuda.synchronize(self.device)
         handle = symm_mem.rendezvous(buf, dist.group.WORLD.group_name)
+        dist.barrier()  # nobody stores before every rank is through its rendezvous
         ptrs = [int(p) for p in handle.buffer_ptrs]
         self._keep = getattr(self, "_keep", []) + [handle]
         return buf, ptrs

@@ -424,8 +424,9 @@ def test_push_transport_matches_all_to_all(cuda_lib, P, bits, is_pre, F, groups)
 
         results[transport] = FakeWorld(P).run(rank_fn)
     for r in range(P):
-        for a, b in zip(results["all_to_all"][r], results["push"][r]):
+        for i, (a, b) in enumerate(zip(results["all_to_all"][r], results["push"][r])):
             if groups == 1 or a.dtype == np.uint8:
                 np.testing.assert_array_equal(a, b)
             else:
-                assert np.abs(a - b).max() <= 1e-5 * max(1.0, np.abs(a).max())
+                bad = np.nonzero(np.abs(a - b).max(axis=1) > 1e-5 * max(1.0, np.abs(a).max()))[0]
+                assert bad.size == 0, f"rank {r}, array {i}: {bad.size} of {a.shape[0]} rows differ, first {bad[:8]}"
