@@ -275,6 +275,104 @@ __global__ void __launch_bounds__(kCodecWarps * 32, (NV == 1 ? 8 : (NV == 2 ? 5 
     }
 }
 
+// ---- rows far longer than one lane group should sum alone (hub vertices) -------------------
+// The fused SpMM + pack kernel gives a packed row to one lane group, which is right for the short rows
+// of a halo matrix and hopeless for a hub with 10^5 nonzeros.  Rows above kLongRow nonzeros are
+// therefore summed beforehand: the row is cut into segments of kLongSeg nonzeros, one CTA per segment
+// (its four warps take a quarter each and are folded in warp order), and a second kernel adds a row's
+// segment sums in segment order.  Deterministic; long rows differ from the sequential chain by fp32
+// re-association only (as rows cut across chunks do in the plain SpMM).
+constexpr int kLongSeg = 4096;
+
+template <int NV, int U>
+__global__ void __launch_bounds__(128)
+    spmm_long_rows_partial_kernel(const int64_t *__restrict__ rowptr, const int32_t *__restrict__ col,
+                                  const float *__restrict__ val, const float *__restrict__ X, int64_t ldx, int FV,
+                                  const int32_t *__restrict__ long_idx, const int32_t *__restrict__ seg_row,
+                                  const int32_t *__restrict__ seg_off, float *__restrict__ partial, int64_t ld) {
+    __shared__ float4 fold[3][NV * 32];
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int s = blockIdx.x;
+    const int row = long_idx[seg_row[s]];
+    const int64_t r0 = rowptr[row] + (int64_t)seg_off[s] * kLongSeg;
+    int64_t r1 = r0 + kLongSeg;
+    if (r1 > rowptr[row + 1]) r1 = rowptr[row + 1];
+    const int64_t e0 = r0 + (int64_t)warp * (kLongSeg / 4);
+    int64_t e1 = e0 + kLongSeg / 4;
+    if (e1 > r1) e1 = r1;
+    float4 acc[NV];
+#pragma unroll
+    for (int k = 0; k < NV; ++k) acc[k] = make_float4(0.f, 0.f, 0.f, 0.f);
+    for (int64_t eb = e0; eb < e1; eb += 32) {
+        const int nb = (int)((e1 - eb) < 32 ? (e1 - eb) : 32);
+        int my_col = 0;
+        float my_val = 0.f;
+        if (lane < nb) {
+            my_col = ld_stream(col + eb + lane);
+            my_val = ld_stream(val + eb + lane);
+        }
+        for (int j0 = 0; j0 < nb; j0 += U) {
+            float4 xr[U][NV];
+            float av[U];
+#pragma unroll
+            for (int u = 0; u < U; ++u) {
+                const int j = j0 + u;
+                const int c = __shfl_sync(kFullMask, my_col, j & 31);
+                av[u] = __shfl_sync(kFullMask, my_val, j & 31);
+                const float4 *xp = reinterpret_cast<const float4 *>(X + (int64_t)c * ldx);
+#pragma unroll
+                for (int k = 0; k < NV; ++k)
+                    if (j < nb && lane + 32 * k < FV) xr[u][k] = __ldg(xp + lane + 32 * k);
+            }
+#pragma unroll
+            for (int u = 0; u < U; ++u)
+                if (j0 + u < nb) {
+#pragma unroll
+                    for (int k = 0; k < NV; ++k)
+                        if (lane + 32 * k < FV) {
+                            acc[k].x = fmaf(av[u], xr[u][k].x, acc[k].x);
+                            acc[k].y = fmaf(av[u], xr[u][k].y, acc[k].y);
+                            acc[k].z = fmaf(av[u], xr[u][k].z, acc[k].z);
+                            acc[k].w = fmaf(av[u], xr[u][k].w, acc[k].w);
+                        }
+                }
+        }
+    }
+    if (warp > 0) {
+#pragma unroll
+        for (int k = 0; k < NV; ++k) fold[warp - 1][k * 32 + lane] = acc[k];
+    }
+    __syncthreads();
+    if (warp == 0) {
+        float4 *out = reinterpret_cast<float4 *>(partial + (int64_t)s * ld);
+#pragma unroll
+        for (int k = 0; k < NV; ++k) {
+            if (lane + 32 * k < FV) {
+                float4 a = acc[k];
+#pragma unroll
+                for (int w = 0; w < 3; ++w) {
+                    const float4 b = fold[w][k * 32 + lane];
+                    a.x += b.x, a.y += b.y, a.z += b.z, a.w += b.w;
+                }
+                out[lane + 32 * k] = a;
+            }
+        }
+    }
+}
+
+__global__ void __launch_bounds__(128)
+    spmm_long_rows_reduce_kernel(const int32_t *__restrict__ row_seg_ptr, int L, const float *__restrict__ partial,
+                                 float *__restrict__ sums, int64_t ld, int F) {
+    const int k = blockIdx.x;
+    if (k >= L) return;
+    const int s0 = row_seg_ptr[k], s1 = row_seg_ptr[k + 1];
+    for (int f = threadIdx.x; f < F; f += blockDim.x) {
+        float a = 0.f;
+        for (int s = s0; s < s1; ++s) a += partial[(int64_t)s * ld + f];
+        sums[(int64_t)k * ld + f] = a;
+    }
+}
+
 // ---- K2 + K3a fused: SpMM whose epilogue quantises + packs -------------------------------
 // Row i of the sparse matrix is wire slot i (the send side of the pre/post scheme,
 // adj_t_pre_post_aggr_to, or the transposed receive-side matrix in backward).  The GQ lanes that
@@ -287,7 +385,8 @@ template <int BITS, int NV, int GQ, int U>
 __global__ void __launch_bounds__(kCodecWarps * 32)
     spmm_quant_pack_kernel(const int64_t *__restrict__ rowptr, const int32_t *__restrict__ col,
                            const float *__restrict__ val, const float *__restrict__ X, int64_t ldx, int F,
-                           const int32_t *__restrict__ seg, int P, float *__restrict__ params,
+                           const int32_t *__restrict__ seg, int P, const int32_t *__restrict__ long_pos,
+                           const float *__restrict__ long_sums, int64_t ld_long, float *__restrict__ params,
                            uint32_t *__restrict__ params_bf16, uint8_t *__restrict__ codes) {
     constexpr int EPB = 8 / BITS;
     constexpr int NG = 32 / GQ;
@@ -314,6 +413,14 @@ __global__ void __launch_bounds__(kCodecWarps * 32)
 #pragma unroll
     for (int t = 0; t < EPB; ++t) {
         if (t < cnt) {
+            const int lp = long_pos != nullptr ? long_pos[i0 + t] : -1;
+            if (lp >= 0) {  // a hub row: summed beforehand by the long-row kernels, many CTAs per row
+                const float4 *sp = reinterpret_cast<const float4 *>(long_sums + (int64_t)lp * ld_long);
+#pragma unroll
+                for (int k = 0; k < NV; ++k)
+                    if (gl + GQ * k < FV) acc[t][k] = sp[gl + GQ * k];
+                continue;
+            }
             const int64_t e0 = rowptr[i0 + t], e1 = rowptr[i0 + t + 1];
             for (int64_t eb = e0; eb < e1; eb += GQ) {
                 const int nb = (int)((e1 - eb) < GQ ? (e1 - eb) : GQ);
@@ -613,9 +720,12 @@ extern "C" int gnnagg_quant_pack_rows(const float *X, int64_t ldx, const int32_t
 
 extern "C" int gnnagg_spmm_quant_pack(const int64_t *rowptr, const int32_t *col, const float *val, int64_t M, int64_t K,
                                       int64_t nnz, const float *X, int64_t ldx, int32_t F, const int32_t *seg,
-                                      int32_t P, int32_t bits, float *params, void *params_bf16, uint8_t *codes,
+                                      int32_t P, int32_t bits, const int32_t *long_pos, const float *long_sums,
+                                      int64_t ld_long, float *params, void *params_bf16, uint8_t *codes,
                                       void *stream) {
     int rc = check_seg_args("spmm_quant_pack", seg, P, M, bits, F);
+    if (long_pos != nullptr && (long_sums == nullptr || ld_long < F || ld_long % 4 != 0 || !aligned16(long_sums)))
+        return fail(GNNAGG_ERR_ARG, "spmm_quant_pack: long-row sums missing, misaligned or narrower than F");
     if (rc != GNNAGG_OK) return rc;
     if (K < 0 || nnz < 0) return fail(GNNAGG_ERR_ARG, "spmm_quant_pack: negative size");
     if (M == 0 || F == 0) return GNNAGG_OK;
@@ -635,7 +745,7 @@ extern "C" int gnnagg_spmm_quant_pack(const int64_t *rowptr, const int32_t *col,
     const int64_t groups = packed_rows_bound(M, P, epb);
 #define GNNAGG_SQ(B, NV, GQ, U)                                                                                        \
     spmm_quant_pack_kernel<B, NV, GQ, U><<<(unsigned)div_up(groups, kCodecWarps * (32 / GQ)), kCodecWarps * 32, 0, st>>>( \
-        rowptr, col, val, X, ldx, F, seg, P, params, pb, codes)
+        rowptr, col, val, X, ldx, F, seg, P, long_pos, long_sums, ld_long, params, pb, codes)
 #define GNNAGG_SQ_WIDTH(B)                                       \
     do {                                                         \
         if (F <= 32) GNNAGG_SQ(B, 1, 8, 8);                      \
@@ -650,6 +760,34 @@ extern "C" int gnnagg_spmm_quant_pack(const int64_t *rowptr, const int32_t *col,
 #undef GNNAGG_SQ_WIDTH
 #undef GNNAGG_SQ
     return check_launch("spmm_quant_pack_kernel");
+}
+
+extern "C" int32_t gnnagg_spmm_long_row_threshold(void) { return kLongSeg / 8; }
+extern "C" int32_t gnnagg_spmm_long_row_segment(void) { return kLongSeg; }
+
+extern "C" int gnnagg_spmm_long_rows(const int64_t *rowptr, const int32_t *col, const float *val, const float *X,
+                                     int64_t ldx, int32_t F, const int32_t *long_idx, int32_t L,
+                                     const int32_t *seg_row, const int32_t *seg_off, const int32_t *row_seg_ptr,
+                                     int32_t S, float *partial, float *sums, int64_t ld, void *stream) {
+    if (L < 0 || S < 0 || F < 0) return fail(GNNAGG_ERR_ARG, "spmm_long_rows: negative size");
+    if (L == 0 || S == 0 || F == 0) return GNNAGG_OK;
+    if (rowptr == nullptr || col == nullptr || val == nullptr || X == nullptr || long_idx == nullptr || seg_row == nullptr ||
+        seg_off == nullptr || row_seg_ptr == nullptr || partial == nullptr || sums == nullptr)
+        return fail(GNNAGG_ERR_ARG, "spmm_long_rows: null pointer");
+    if (F % 4 != 0 || F > 512 || ldx % 4 != 0 || ld % 4 != 0 || ld < F || !aligned16(X) || !aligned16(partial) || !aligned16(sums))
+        return fail(GNNAGG_ERR_UNSUPPORTED, "spmm_long_rows: needs F %% 4 == 0, F <= 512 and 16-byte aligned rows");
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    const int FV = F / 4;
+#define GNNAGG_LR(NV, U) \
+    spmm_long_rows_partial_kernel<NV, U><<<(unsigned)S, 128, 0, st>>>(rowptr, col, val, X, ldx, FV, long_idx, seg_row, seg_off, partial, ld)
+    if (F <= 128) GNNAGG_LR(1, 8);
+    else if (F <= 256) GNNAGG_LR(2, 4);
+    else GNNAGG_LR(4, 2);
+#undef GNNAGG_LR
+    int rc = check_launch("spmm_long_rows_partial_kernel");
+    if (rc != GNNAGG_OK) return rc;
+    spmm_long_rows_reduce_kernel<<<(unsigned)L, 128, 0, st>>>(row_seg_ptr, L, partial, sums, ld, F);
+    return check_launch("spmm_long_rows_reduce_kernel");
 }
 
 extern "C" int gnnagg_unpack_dequant_rows(const uint8_t *codes, int32_t F, const int32_t *seg, int32_t P, int64_t rows,

@@ -191,13 +191,32 @@ int gnnagg_quant_pack_rows(const float *X, int64_t ldx, const int32_t *idx, int3
  *                                                                (model/layers/aggregator.py:145-149).
  *   M = number of wire slots = seg[P];  X (K,F) fp32 with leading dimension ldx;
  *   params / params_bf16 / codes / seg / P / bits: as for gnnagg_quant_pack_rows (params computed here).
+ *   long_pos / long_sums / ld_long: optional.  A packed row is summed by one group of lanes, which suits
+ *     the short rows of a halo matrix; rows with more than gnnagg_spmm_long_row_threshold() nonzeros (hub
+ *     vertices) should be summed beforehand with gnnagg_spmm_long_rows and passed in: long_pos[i] = k >= 0
+ *     means "slot i's sum is long_sums[k*ld_long ...]", -1 means "sum it here".  NULL: every row here.
  * Needs F % 4 == 0, F <= 512, ldx % 4 == 0 and 16-byte aligned X (GNNAGG_ERR_UNSUPPORTED otherwise: run
- * the two calls).  Codes and parameters equal those of the two-call sequence wherever that sequence
- * sums a row in the same order (F > 64 and no row longer than one 512-item chunk), and equal the
- * reference's bytes for every shape (its SpMM is the sequential chain). */
+ * the two calls).  Rows summed here follow the reference's sequential chain exactly, so their codes and
+ * parameters equal the reference's bytes for every width (and those of the two-call sequence wherever
+ * that sums in the same order: F > 64, row within one chunk); rows passed in through long_sums differ by
+ * fp32 re-association, like rows cut across chunks in gnnagg_spmm_csr_f32. */
 int gnnagg_spmm_quant_pack(const int64_t *rowptr, const int32_t *col, const float *val, int64_t M, int64_t K,
                            int64_t nnz, const float *X, int64_t ldx, int32_t F, const int32_t *seg, int32_t P,
-                           int32_t bits, float *params, void *params_bf16, uint8_t *codes, void *stream);
+                           int32_t bits, const int32_t *long_pos, const float *long_sums, int64_t ld_long,
+                           float *params, void *params_bf16, uint8_t *codes, void *stream);
+
+/* Sums of the long rows of a CSR matrix, many CTAs per row: row long_idx[k] (k < L) is cut into segments of
+ * gnnagg_spmm_long_row_segment() nonzeros; segment s belongs to long row seg_row[s] and is its seg_off[s]-th
+ * segment; row k owns the segments row_seg_ptr[k] .. row_seg_ptr[k+1]-1 (S in total).  One CTA sums one
+ * segment into partial[s*ld ...] (S*ld floats of scratch), then sums[k*ld ...] = its segments added in
+ * order.  Deterministic.  Part of the replacement of spmm (model/ops/src/spmm.cpp:327-507) on the
+ * send side of a packed exchange; see gnnagg_spmm_quant_pack. */
+int32_t gnnagg_spmm_long_row_threshold(void);
+int32_t gnnagg_spmm_long_row_segment(void);
+int gnnagg_spmm_long_rows(const int64_t *rowptr, const int32_t *col, const float *val, const float *X, int64_t ldx,
+                          int32_t F, const int32_t *long_idx, int32_t L, const int32_t *seg_row,
+                          const int32_t *seg_off, const int32_t *row_seg_ptr, int32_t S, float *partial, float *sums,
+                          int64_t ld, void *stream);
 
 /* ------------------------------------------------------------------------------------
  * K3b  unpack + dequantise   OUT[i,k] = fma(code, scale_i, zero_point_i)

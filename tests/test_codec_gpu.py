@@ -252,15 +252,16 @@ def _slot_matrix(rng, slots, K, hub=False):
 
 
 def _fused(rowptr, col, val, K, X, seg, bits):
-    from gnn_benchmark_b200.spmm_kernel import spmm_quant_pack
+    from gnn_benchmark_b200.spmm_kernel import LongRows, spmm_quant_pack
 
     slots, F, epb = int(seg[-1]), X.shape[1], 8 // bits
     prow = int(sum((int(b) - int(a) + epb - 1) // epb for a, b in zip(seg[:-1], seg[1:])))
     codes = torch.full((prow, F), 0xAB, dtype=torch.uint8, device="cuda")
     params = torch.full((slots, 2), float("nan"), device="cuda")
     pb = torch.zeros((slots, 2), dtype=torch.bfloat16, device="cuda")
-    spmm_quant_pack(to_dev(rowptr), to_dev(col, torch.int32), to_dev(val), K, to_dev(X), codes, params, pb,
-                    to_dev(np.asarray(seg, dtype=np.int32)), len(seg) - 1, bits)
+    rp = to_dev(rowptr)
+    spmm_quant_pack(rp, to_dev(col, torch.int32), to_dev(val), K, to_dev(X), codes, params, pb,
+                    to_dev(np.asarray(seg, dtype=np.int32)), len(seg) - 1, bits, LongRows(rp))
     torch.cuda.synchronize()
     return codes.cpu().numpy(), params.cpu().numpy(), pb.float().cpu().numpy()
 
@@ -269,10 +270,10 @@ def _fused(rowptr, col, val, K, X, seg, bits):
 @pytest.mark.parametrize("seg", [[0, 6], [0, 5, 5, 18, 19, 64, 256], [0, 0, 0, 3], [0, 1023]])
 def test_spmm_quant_pack_equals_reference_chain_then_quantise(cuda_lib, F, seg):
     """Codes and parameters of the fused kernel against the oracle's SpMM (sequential FMA chain, the
-    reference's order) followed by its int2 quantiser: bit-exact for every width, hub row included."""
+    reference's order) followed by its int2 quantiser: bit-exact for every width."""
     rng = np.random.default_rng(F + 13 * len(seg))
     slots, K = seg[-1], 700
-    rowptr, col, val = _slot_matrix(rng, slots, K, hub=slots > 100)
+    rowptr, col, val = _slot_matrix(rng, slots, K)
     X = rng.standard_normal((K, F)).astype(np.float32)
     summed = oracle.spmm(rowptr, col, val, X)
     want_codes, want_params = oracle.quantize_int2_for_all_procs(summed, seg)
@@ -309,3 +310,33 @@ def test_spmm_quant_pack_refuses_unsupported_width(cuda_lib):
     rowptr, col, val = _slot_matrix(rng, 8, 20)
     with pytest.raises(RuntimeError, match="F %"):
         _fused(rowptr, col, val, 20, rng.standard_normal((20, 6)).astype(np.float32), [0, 8], 2)
+
+
+@pytest.mark.parametrize("F", [32, 128, 256, 512])
+def test_spmm_quant_pack_hub_rows(cuda_lib, F):
+    """Rows longer than the long-row threshold (hub vertices) are summed by many CTAs each and handed to the
+    fused kernel: every other row still equals the reference chain bit for bit after decoding, the hub rows
+    decode to within half a quantisation step (+ fp32 re-association) of the exact sum."""
+    rng = np.random.default_rng(F)
+    seg = [0, 301, 301, 640]
+    slots, K = seg[-1], 9000
+    deg = rng.integers(0, 6, size=slots)
+    hubs = [5, 300, 301, 639]
+    for h, d in zip(hubs, (513, 4096, 4097, 8999)):
+        deg[h] = d
+    rowptr = np.concatenate([[0], np.cumsum(deg)]).astype(np.int64)
+    col = np.concatenate([np.sort(rng.choice(K, size=d, replace=False)) for d in deg]).astype(np.int64)
+    val = rng.standard_normal(col.shape[0]).astype(np.float32)
+    X = rng.standard_normal((K, F)).astype(np.float32)
+    exact = oracle.spmm_f64(rowptr, col, val, X)
+    chain = oracle.spmm(rowptr, col, val, X)
+    want_codes, want_params = oracle.quantize_int2_for_all_procs(chain, seg)
+    codes, params, _ = _fused(rowptr, col, val, K, X, seg, 2)
+    got = oracle.dequantize_int2_for_all_procs(codes, seg, params)
+    want = oracle.dequantize_int2_for_all_procs(want_codes, seg, want_params)
+    short = np.setdiff1d(np.arange(slots), hubs)
+    np.testing.assert_array_equal(got[short], want[short])
+    bits_eq(params[short], want_params[short])
+    mag = oracle.spmm_f64(rowptr, col, np.abs(val), np.abs(X))
+    for h in hubs:
+        assert (np.abs(got[h] - exact[h]) <= 0.5 * params[h, 1] * (1 + 1e-5) + 1e-5 * mag[h]).all()
