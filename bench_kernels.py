@@ -3,6 +3,7 @@ profiles/ are taken on, and the per-kernel bandwidth / throughput figures quoted
 
     python bench_kernels.py codec [--rows 2097152] [--bits 2] [--widths 256,128,32] [--iters 10]
     python bench_kernels.py dense [--rows 2450000] [--shapes 256x256,256x100,48x256] [--iters 10]
+    python bench_kernels.py halo  [--parts 2] [--scale 22] [--widths 256,128,32] [--bits 2]
 
 codec: quantise+pack, gather+quantise+pack, unpack+dequantise on a halo-sized buffer, one JSON line
 per feature width.  Algorithmic bytes per row: quantise 4F + F*bits/8 + 12 (fp32 row in; codes, fp32
@@ -150,8 +151,79 @@ def main_dense(argv):
 
 
 
+def main_halo(argv):
+    """The kernels either side of a packed halo exchange on ONE rank's share of the benchmark graph (R-MAT,
+    2^22 vertices per partition, randomly relabelled, partition 0 of --parts): forward gather+pack and
+    fused-unpack remote SpMM, backward transposed SpMM with the packing epilogue (beside the two-call
+    sequence it replaces: SpMM into an fp32 buffer, then quantise+pack) and the fused-unpack scatter-add."""
+    from gnn_benchmark_b200 import SparseTensor, graphgen
+    from gnn_benchmark_b200.aggregator import gather_rows
+    from gnn_benchmark_b200.data_manager.DataLoader import _scatter_matrix
+    from gnn_benchmark_b200.spmm_kernel import (SPMM_backward, SPMM_backward_quant_pack, SPMM_forward_packed)
+
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--parts", type=int, default=2)
+    ap.add_argument("--scale", type=int, default=22, help="log2 of the vertices per partition")
+    ap.add_argument("--widths", type=str, default="256,128,32")
+    ap.add_argument("--bits", type=int, default=2)
+    ap.add_argument("--iters", type=int, default=5)
+    args = ap.parse_args(argv)
+    dev = torch.device("cuda", 0)
+    P, bits = args.parts, args.bits
+    scale = args.scale + (P - 1).bit_length()
+    src, dst, begin = graphgen.partitioned_in_edges("rmat", 1 << scale, 16 << scale, 20261127, 0, P, dev, relabel=True,
+                                                    scale=scale)
+    n = int(begin[1])
+    rem = src >= n
+    halo_ids, slot = torch.unique(src[rem], return_inverse=True)
+    A = SparseTensor(row=dst[rem], col=slot, sparse_sizes=(n, halo_ids.numel()))
+    del src, dst, rem, slot
+    K = halo_ids.numel()
+    owner = torch.searchsorted(begin.to(dev), halo_ids, right=True) - 1
+    counts = torch.bincount(owner, minlength=P)[:P].tolist()
+    seg = torch.tensor([0] + list(torch.tensor(counts).cumsum(0).tolist()), dtype=torch.int32, device=dev)
+    epb = 8 // bits
+    prow = sum((c + epb - 1) // epb for c in counts)
+    q = Quantizer_for_all_procs(P, bits)
+    g = torch.Generator(device=dev).manual_seed(0)
+    idx = torch.randint(0, n, (K,), device=dev, generator=g).to(torch.int32)
+    S = _scatter_matrix(idx.to(torch.int64), n)
+
+    def timed(fn):
+        for _ in range(2):
+            fn()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        for _ in range(args.iters):
+            fn()
+        b.record()
+        torch.cuda.synchronize()
+        return a.elapsed_time(b) / args.iters
+
+    for F in (int(w) for w in args.widths.split(",")):
+        x = torch.randn(n, F, device=dev, generator=g)
+        out = torch.empty(n, F, device=dev)
+        codes = torch.empty(prow, F, dtype=torch.uint8, device=dev)
+        params = torch.empty(K, 2, device=dev)
+        pb = torch.empty(K, 2, dtype=torch.bfloat16, device=dev)
+        buf = torch.empty(K, F, device=dev)
+        line = {"F": F, "rows": n, "halo_rows": K, "nnz_remote": A.nnz(), "bits": bits}
+        line["gather_pack_ms"] = timed(lambda: q.quantize_fp32_to_intX(x, codes, params, seg, params_bf16=pb, gather_idx=idx))
+        line["remote_spmm_fused_unpack_ms"] = timed(lambda: SPMM_forward_packed(A, codes, pb, seg, P, bits, out))
+
+        def two_calls():
+            SPMM_backward(A, x, buf, accumulate=False)
+            q.quantize_fp32_to_intX(buf, codes, params, seg, params_bf16=pb)
+
+        line["backward_spmm_then_pack_ms"] = timed(two_calls)
+        line["backward_spmm_pack_fused_ms"] = timed(lambda: SPMM_backward_quant_pack(A, x, codes, params, pb, seg, P, bits))
+        line["scatter_fused_unpack_ms"] = timed(lambda: SPMM_forward_packed(S, codes, pb, seg, P, bits, out))
+        line["gather_rows_ms"] = timed(lambda: gather_rows(x, idx, buf))
+        print(json.dumps(line), flush=True)
+
+
 if __name__ == "__main__":
-    legs = {"codec": main_codec, "dense": main_dense}
+    legs = {"codec": main_codec, "dense": main_dense, "halo": main_halo}
     if len(sys.argv) < 2 or sys.argv[1] not in legs:
-        raise SystemExit("usage: python bench_kernels.py {codec|dense} [options]")
+        raise SystemExit("usage: python bench_kernels.py {codec|dense|halo} [options]")
     legs[sys.argv[1]](sys.argv[2:])

@@ -31,6 +31,8 @@ SIGNATURES = {
                                          _vp, _vp, _sz, _vp]),
     "gnnagg_spmm_csr_f32_static_scratch": (ctypes.c_int, [_vp, _vp, _vp, _i64, _i64, _i64, _vp, _i64, _vp, _i64, _i32,
                                                           _i32, _vp, _vp]),
+    "gnnagg_csr_to_csc_workspace_bytes": (_sz, [_i64, _i64, _i64]),
+    "gnnagg_csr_to_csc": (ctypes.c_int, [_vp, _vp, _vp, _i64, _i64, _i64, _vp, _vp, _vp, _vp, _sz, _vp]),
     "gnnagg_csr_validate": (ctypes.c_int, [_vp, _vp, _i64, _i64, _i64, _vp, _vp]),
     "gnnagg_gather_rows_f32": (ctypes.c_int, [_vp, _i64, _vp, _i64, _i32, _vp, _i64, _vp]),
     "gnnagg_push_rows": (ctypes.c_int, [_vp, _i64, _vp, _i32, _vp, _i32, _i32, _i32, _vp, _i64, _i64, _vp]),

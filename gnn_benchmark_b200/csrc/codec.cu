@@ -380,7 +380,7 @@ __global__ void __launch_bounds__(128)
 // nonzero in CSR order, starting from zero: the reference's chain (model/ops/src/spmm.cpp:97-126)
 // -- keep the sums in registers and hand them to quant_pack_group, so the fp32 send buffer is never
 // written to or read from HBM.  Column indices / values are read GQ at a time (coalesced) and
-// broadcast inside the group; U gathers are in flight per lane.
+// broadcast inside the group; EPB * U gathers are in flight per lane.
 template <int BITS, int NV, int GQ, int U>
 __global__ void __launch_bounds__(kCodecWarps * 32)
     spmm_quant_pack_kernel(const int64_t *__restrict__ rowptr, const int32_t *__restrict__ col,
@@ -410,8 +410,15 @@ __global__ void __launch_bounds__(kCodecWarps * 32)
 #pragma unroll
         for (int k = 0; k < NV; ++k) acc[t][k] = make_float4(0.f, 0.f, 0.f, 0.f);
 
+    // The group's rows advance TOGETHER: in every step one nonzero of each row is gathered, so EPB * U
+    // independent 16-byte loads per lane are in flight instead of U, and the three dependent latencies of a
+    // short row (row pointers, index batch, feature rows) are paid once per packed row, not once per row.
+    int64_t e0[EPB];
+    int len[EPB];
+    int maxlen = 0;
 #pragma unroll
     for (int t = 0; t < EPB; ++t) {
+        e0[t] = 0, len[t] = 0;
         if (t < cnt) {
             const int lp = long_pos != nullptr ? long_pos[i0 + t] : -1;
             if (lp >= 0) {  // a hub row: summed beforehand by the long-row kernels, many CTAs per row
@@ -419,42 +426,54 @@ __global__ void __launch_bounds__(kCodecWarps * 32)
 #pragma unroll
                 for (int k = 0; k < NV; ++k)
                     if (gl + GQ * k < FV) acc[t][k] = sp[gl + GQ * k];
-                continue;
+            } else {
+                e0[t] = rowptr[i0 + t];
+                len[t] = (int)(rowptr[i0 + t + 1] - e0[t]);
+                maxlen = max(maxlen, len[t]);
             }
-            const int64_t e0 = rowptr[i0 + t], e1 = rowptr[i0 + t + 1];
-            for (int64_t eb = e0; eb < e1; eb += GQ) {
-                const int nb = (int)((e1 - eb) < GQ ? (e1 - eb) : GQ);
-                int my_col = 0;
-                float my_val = 0.f;
-                if (gl < nb) {
-                    my_col = ld_stream(col + eb + gl);
-                    my_val = ld_stream(val + eb + gl);
-                }
-                for (int j0 = 0; j0 < nb; j0 += U) {
-                    float4 xr[U][NV];
-                    float av[U];
+        }
+    }
+    for (int base = 0; base < maxlen; base += GQ) {
+        int my_col[EPB];
+        float my_val[EPB];
 #pragma unroll
-                    for (int u = 0; u < U; ++u) {
-                        const int j = j0 + u;
-                        const int c = __shfl_sync(gmask, my_col, lead + (j & (GQ - 1)));
-                        av[u] = __shfl_sync(gmask, my_val, lead + (j & (GQ - 1)));
-                        const float4 *xp = reinterpret_cast<const float4 *>(X + (int64_t)c * ldx);
+        for (int t = 0; t < EPB; ++t) {
+            my_col[t] = 0, my_val[t] = 0.f;
+            if (base + gl < len[t]) {
+                my_col[t] = ld_stream(col + e0[t] + base + gl);
+                my_val[t] = ld_stream(val + e0[t] + base + gl);
+            }
+        }
+        const int nb = min(GQ, maxlen - base);
+        for (int j0 = 0; j0 < nb; j0 += U) {
+            float4 xr[EPB][U][NV];
+            float av[EPB][U];
+#pragma unroll
+            for (int u = 0; u < U; ++u) {
+                const int j = j0 + u;
+#pragma unroll
+                for (int t = 0; t < EPB; ++t) {
+                    const int c = __shfl_sync(gmask, my_col[t], lead + (j & (GQ - 1)));
+                    av[t][u] = __shfl_sync(gmask, my_val[t], lead + (j & (GQ - 1)));
+                    const float4 *xp = reinterpret_cast<const float4 *>(X + (int64_t)c * ldx);
+#pragma unroll
+                    for (int k = 0; k < NV; ++k)
+                        if (base + j < len[t] && j < nb && gl + GQ * k < FV) xr[t][u][k] = __ldg(xp + gl + GQ * k);
+                }
+            }
+#pragma unroll
+            for (int u = 0; u < U; ++u) {
+#pragma unroll
+                for (int t = 0; t < EPB; ++t) {
+                    if (base + j0 + u < len[t] && j0 + u < nb) {  // every row keeps its own CSR order
 #pragma unroll
                         for (int k = 0; k < NV; ++k)
-                            if (j < nb && gl + GQ * k < FV) xr[u][k] = __ldg(xp + gl + GQ * k);
-                    }
-#pragma unroll
-                    for (int u = 0; u < U; ++u) {
-                        if (j0 + u < nb) {
-#pragma unroll
-                            for (int k = 0; k < NV; ++k)
-                                if (gl + GQ * k < FV) {
-                                    acc[t][k].x = fmaf(av[u], xr[u][k].x, acc[t][k].x);
-                                    acc[t][k].y = fmaf(av[u], xr[u][k].y, acc[t][k].y);
-                                    acc[t][k].z = fmaf(av[u], xr[u][k].z, acc[t][k].z);
-                                    acc[t][k].w = fmaf(av[u], xr[u][k].w, acc[t][k].w);
-                                }
-                        }
+                            if (gl + GQ * k < FV) {
+                                acc[t][k].x = fmaf(av[t][u], xr[t][u][k].x, acc[t][k].x);
+                                acc[t][k].y = fmaf(av[t][u], xr[t][u][k].y, acc[t][k].y);
+                                acc[t][k].z = fmaf(av[t][u], xr[t][u][k].z, acc[t][k].z);
+                                acc[t][k].w = fmaf(av[t][u], xr[t][u][k].w, acc[t][k].w);
+                            }
                     }
                 }
             }
@@ -718,6 +737,15 @@ extern "C" int gnnagg_quant_pack_rows(const float *X, int64_t ldx, const int32_t
     return check_launch("quant_pack_generic_kernel");
 }
 
+// Gather steps issued back to back by the fused SpMM + pack kernel: 8 / bits rows advance together, so
+// rows * steps * NV 16-byte loads are in flight per lane -- eight, or sixteen for 2-bit codes on rows of
+// more than 128 floats, where one step alone would leave the memory system idle.
+static constexpr int sq_steps(int bits, int nv) {
+    const int rows = 8 / bits;
+    const int u = 8 / (rows * nv);
+    return (rows == 4 && nv == 2) ? 2 : (u < 1 ? 1 : u);
+}
+
 extern "C" int gnnagg_spmm_quant_pack(const int64_t *rowptr, const int32_t *col, const float *val, int64_t M, int64_t K,
                                       int64_t nnz, const float *X, int64_t ldx, int32_t F, const int32_t *seg,
                                       int32_t P, int32_t bits, const int32_t *long_pos, const float *long_sums,
@@ -748,11 +776,11 @@ extern "C" int gnnagg_spmm_quant_pack(const int64_t *rowptr, const int32_t *col,
         rowptr, col, val, X, ldx, F, seg, P, long_pos, long_sums, ld_long, params, pb, codes)
 #define GNNAGG_SQ_WIDTH(B)                                       \
     do {                                                         \
-        if (F <= 32) GNNAGG_SQ(B, 1, 8, 8);                      \
-        else if (F <= 64) GNNAGG_SQ(B, 1, 16, 8);                \
-        else if (F <= 128) GNNAGG_SQ(B, 1, 32, 8);               \
-        else if (F <= 256) GNNAGG_SQ(B, 2, 32, 4);               \
-        else GNNAGG_SQ(B, 4, 32, 2);                             \
+        if (F <= 32) GNNAGG_SQ(B, 1, 8, sq_steps(B, 1));           \
+        else if (F <= 64) GNNAGG_SQ(B, 1, 16, sq_steps(B, 1));     \
+        else if (F <= 128) GNNAGG_SQ(B, 1, 32, sq_steps(B, 1));    \
+        else if (F <= 256) GNNAGG_SQ(B, 2, 32, sq_steps(B, 2));    \
+        else GNNAGG_SQ(B, 4, 32, sq_steps(B, 4));                  \
     } while (0)
     if (bits == 2) GNNAGG_SQ_WIDTH(2);
     else if (bits == 4) GNNAGG_SQ_WIDTH(4);

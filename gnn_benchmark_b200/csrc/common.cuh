@@ -56,6 +56,19 @@ __device__ __forceinline__ float ld_stream(const float *p) { return __ldcs(p); }
 __device__ __forceinline__ void st_stream_v4(float *p, float4 v) { __stcs(reinterpret_cast<float4 *>(p), v); }
 __device__ __forceinline__ void st_stream(float *p, float v) { __stcs(p, v); }
 
+// Asynchronous 4-byte global -> shared copies (index / value tiles of the SpMM): no register is tied up
+// while the data is in flight; a group is complete for the issuing thread after cp_async_wait and for
+// the rest of its warp after a __syncwarp() that follows.
+__device__ __forceinline__ void cp_async_4(void *smem, const void *gmem) {
+    const uint32_t s = static_cast<uint32_t>(__cvta_generic_to_shared(smem));
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(s), "l"(gmem) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() {
+    asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
+}
+
 constexpr int kMaxSeg = 1024;  // peer segments per call
 
 // Packed-row prefix of the segments into shared memory: pbase[p] = sum_{q<p} ceil(n_q/epb).

@@ -35,7 +35,10 @@ __global__ void __launch_bounds__(256)
     const int gl = threadIdx.x & (G - 1);
     const int64_t groups_per_block = blockDim.x >> log2g;
     const int64_t stride = groups_per_block * gridDim.x;
-    for (int64_t v = (int64_t)blockIdx.x * groups_per_block + (threadIdx.x >> log2g); v < total; v += stride) {
+    const int64_t first = (int64_t)blockIdx.x * groups_per_block + (threadIdx.x >> log2g);
+
+    // send-list row v of the served peers -> where it is read and where it goes
+    auto locate = [&](int64_t v, const T *&in, T *&out) {
         int lo = 0, hi = num_peers - 1;  // peer slot j with spre[j] <= v < spre[j+1] (empty peers skipped)
         while (lo < hi) {
             const int mid = (lo + hi + 1) >> 1;
@@ -49,9 +52,43 @@ __global__ void __launch_bounds__(256)
         const int64_t r = v - spre[lo];          // row inside this rank's block for peer p
         const int64_t i = (int64_t)seg[p] + r;   // row of the send list
         const int64_t s = idx ? (int64_t)idx[i] : i;
-        const T *in = reinterpret_cast<const T *>(src + s * ld_src);
-        T *out = reinterpret_cast<T *>(reinterpret_cast<uint8_t *>(dst[p]) + r * ld_dst);
-        for (int u = gl; u < units; u += G) out[u] = __ldg(in + u);
+        in = reinterpret_cast<const T *>(src + s * ld_src);
+        out = reinterpret_cast<T *>(reinterpret_cast<uint8_t *>(dst[p]) + r * ld_dst);
+    };
+
+    if (units <= 2 * G) {
+        // The grid is kept small (the SpMM running beside this kernel needs the SMs), so every lane keeps
+        // several rows in flight: the loads of four rows are issued before the first store.
+        constexpr int ROWS = 4;
+        for (int64_t v0 = first; v0 < total; v0 += ROWS * stride) {
+            T a[ROWS][2];
+            T *out[ROWS];
+#pragma unroll
+            for (int q = 0; q < ROWS; ++q) {
+                const int64_t v = v0 + q * stride;
+                out[q] = nullptr;
+                if (v < total) {
+                    const T *in;
+                    locate(v, in, out[q]);
+                    if (gl < units) a[q][0] = __ldg(in + gl);
+                    if (gl + G < units) a[q][1] = __ldg(in + gl + G);
+                }
+            }
+#pragma unroll
+            for (int q = 0; q < ROWS; ++q) {
+                if (out[q] != nullptr) {
+                    if (gl < units) out[q][gl] = a[q][0];
+                    if (gl + G < units) out[q][gl + G] = a[q][1];
+                }
+            }
+        }
+    } else {
+        for (int64_t v = first; v < total; v += stride) {
+            const T *in;
+            T *out;
+            locate(v, in, out);
+            for (int u = gl; u < units; u += G) out[u] = __ldg(in + u);
+        }
     }
 }
 
@@ -76,9 +113,12 @@ extern "C" int gnnagg_push_rows(const void *src, int64_t ld_src, const int32_t *
     int log2g = 0;
     while ((1 << log2g) < units && log2g < 5) ++log2g;
     const int64_t groups_per_block = 256 >> log2g;
-    int64_t blocks = div_up(rows_hint, groups_per_block);
-    const int64_t cap = (int64_t)kNumSMs * 16;
+    // two 256-thread CTAs per SM at most: a quarter of an SM's thread slots, enough to fill NVLink with four
+    // rows in flight per lane group, and room for the SpMM that runs on the compute stream meanwhile
+    int64_t blocks = div_up(rows_hint, groups_per_block * 4);
+    const int64_t cap = (int64_t)kNumSMs * 2;
     if (blocks > cap) blocks = cap;
+    if (blocks < 1) blocks = 1;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     const uint8_t *s8 = static_cast<const uint8_t *>(src);
 #define GNNAGG_PUSH(T) \

@@ -6,8 +6,8 @@
 //   that lands inside a row no longer than a chunk is moved forward to the end of that
 //   row, so only hub rows (longer than a chunk) are ever shared between warps.
 // Per chunk a warp
-//   - streams its slice of col/val with coalesced 128-byte loads (one nonzero per lane),
-//     broadcasts them with shuffles,
+//   - streams its slice of col/val into shared memory with asynchronous copies, one 256-nonzero
+//     tile ahead of its use, and reads every nonzero from there with a broadcast load,
 //   - gathers feature rows with 128-bit loads: G = min(32, F/4 rounded up to a power of
 //     two) lanes cover one feature row, so S = 32/G nonzeros are fetched per warp load
 //     instruction and U such instructions are issued back to back before any is consumed
@@ -45,6 +45,9 @@ namespace gnnagg {
 constexpr int kWarpsPerBlock = GNNAGG_SPMM_WARPS;
 // register cap per thread = 65536 / (threads per CTA * min CTAs per SM)
 constexpr int min_blocks_per_sm(int nv) { return nv == 1 ? GNNAGG_SPMM_MINBLOCKS_NARROW : GNNAGG_SPMM_MINBLOCKS_WIDE; }
+// nonzeros of a chunk are staged through shared memory in tiles of this many (two tiles per warp, the next
+// one in flight while the current one is consumed)
+constexpr int kTile = 256;
 constexpr uint32_t kPlanMagic = 0x4d50534eu;  // "NSPM"
 constexpr int kDefaultItems = 512;
 
@@ -190,9 +193,13 @@ __global__ void __launch_bounds__(kWarpsPerBlock * 32, min_blocks_per_sm(NV))
     constexpr int SEGCAP = QB ? kMaxSeg + 1 : 1;
     __shared__ int sseg[SEGCAP];
     __shared__ int pbase[SEGCAP];
+    __shared__ int s_col[kWarpsPerBlock][2][kTile];
+    __shared__ float s_val[kWarpsPerBlock][2][kTile];
+    __shared__ uint32_t s_prm[QB ? kWarpsPerBlock : 1][2][QB ? kTile : 1];
     if (QB) build_packed_prefix(q.seg, q.P, EPB, pbase, sseg);  // before any warp leaves: it synchronises the CTA
     const int lane = threadIdx.x & 31;
-    const int64_t c = (int64_t)blockIdx.x * kWarpsPerBlock + (threadIdx.x >> 5);
+    const int wib = threadIdx.x >> 5;
+    const int64_t c = (int64_t)blockIdx.x * kWarpsPerBlock + wib;
     if (c >= nchunks) return;
     const int gl = lane % G, grp = lane / G;
 
@@ -200,6 +207,22 @@ __global__ void __launch_bounds__(kWarpsPerBlock * 32, min_blocks_per_sm(NV))
     int r = chunk_row[c];
     const int r1 = chunk_row[c + 1];
     const int n = (int)(e1 - e0);
+
+    // Column indices and values of the chunk travel global -> shared asynchronously, a tile ahead of their
+    // use; every gather step then reads its nonzero with a broadcast shared-memory load.
+    const int ntiles = (n + kTile - 1) / kTile;
+    auto issue_tile = [&](int k) {
+        const int base = k * kTile;
+        const int cnt = (n - base) < kTile ? (n - base) : kTile;
+        int *dc = s_col[wib][k & 1];
+        float *dv = s_val[wib][k & 1];
+        for (int i = lane; i < cnt; i += 32) {
+            cp_async_4(dc + i, col + e0 + base + i);
+            cp_async_4(dv + i, val + e0 + base + i);
+        }
+        cp_async_commit();
+    };
+    if (ntiles > 0) issue_tile(0);
 
     int voff[NV];
     bool vok[NV];
@@ -298,30 +321,38 @@ __global__ void __launch_bounds__(kWarpsPerBlock * 32, min_blocks_per_sm(NV))
     uint32_t pq[QB ? U : 1];  // the slot's bf16 (zero_point, scale) pair, widened when applied
     int shq[QB ? U : 1];
 
-    for (int eb = 0; eb < n; eb += 32) {
-        int my_col = 0;
-        float my_val = 0.f;
-        uint32_t my_prm = 0u;
-        if (eb + lane < n) {
-            my_col = ld_stream(col + e0 + eb + lane);
-            my_val = ld_stream(val + e0 + eb + lane);
-            if (QB) {
-                // wire slot -> (packed row, bit position) and its bf16 parameters, once per nonzero
-                const int pseg = find_segment(sseg, q.P, my_col);
-                const int j = my_col - sseg[pseg];
-                my_prm = __ldg(q.params + my_col);
-                my_col = ((pbase[pseg] + j / EPB) << 3) | ((EPB - 1 - j % EPB) * QB);
-            }
+    for (int tile = 0; tile < ntiles; ++tile) {
+        const int eb = tile * kTile;
+        if (tile + 1 < ntiles) {
+            issue_tile(tile + 1);
+            cp_async_wait<1>();
+        } else {
+            cp_async_wait<0>();
         }
-        const int in_batch = (n - eb) < 32 ? (n - eb) : 32;
+        __syncwarp();
+        int *tcol = s_col[wib][tile & 1];
+        const float *tval = s_val[wib][tile & 1];
+        uint32_t *tprm = s_prm[QB ? wib : 0][tile & 1];
+        const int in_batch = (n - eb) < kTile ? (n - eb) : kTile;
+        if (QB) {
+            // wire slot -> (packed row, bit position) and its bf16 parameters, once per nonzero
+            for (int i = lane; i < in_batch; i += 32) {
+                const int slot = tcol[i];
+                const int pseg = find_segment(sseg, q.P, slot);
+                const int j = slot - sseg[pseg];
+                tprm[i] = __ldg(q.params + slot);
+                tcol[i] = ((pbase[pseg] + j / EPB) << 3) | ((EPB - 1 - j % EPB) * QB);
+            }
+            __syncwarp();
+        }
         const int nsteps = (in_batch + S - 1) / S;
         const int full_steps = in_batch / S;  // steps in which every lane group holds a nonzero
 
-        auto fetch = [&](int u, int src_lane, bool ok) {
-            const int cc = __shfl_sync(kFullMask, my_col, src_lane);
-            av[u] = __shfl_sync(kFullMask, my_val, src_lane);
+        auto fetch = [&](int u, int j, bool ok) {  // j: position of the nonzero inside the tile
+            const int cc = tcol[j];
+            av[u] = tval[j];
             if (QB) {
-                pq[u] = __shfl_sync(kFullMask, my_prm, src_lane);
+                pq[u] = tprm[j];
                 shq[u] = cc & 7;
                 const uint32_t *wp = reinterpret_cast<const uint32_t *>(q.codes + (int64_t)(cc >> 3) * q.F);
 #pragma unroll
@@ -372,9 +403,9 @@ __global__ void __launch_bounds__(kWarpsPerBlock * 32, min_blocks_per_sm(NV))
             bool ok[U];
 #pragma unroll
             for (int u = 0; u < U; ++u) {
-                const int j = (s0 + u) * S + grp;  // position inside the 32-nonzero batch
+                const int j = (s0 + u) * S + grp;  // position inside the tile
                 ok[u] = j < in_batch;
-                fetch(u, j & 31, ok[u]);
+                fetch(u, ok[u] ? j : 0, ok[u]);
             }
 #pragma unroll
             for (int u = 0; u < U; ++u) {
@@ -394,6 +425,7 @@ __global__ void __launch_bounds__(kWarpsPerBlock * 32, min_blocks_per_sm(NV))
                 }
             }
         }
+        __syncwarp();  // every lane is done with this tile before the copy of the tile after next lands in it
     }
     // Row ends that follow the chunk's last nonzero (including empty rows).
     while (r < r1) {

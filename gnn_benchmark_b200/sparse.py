@@ -162,7 +162,20 @@ class SparseTensor:
             self._row_T = torch.zeros(0, dtype=torch.int32, device=dev)
             self._value_T = torch.zeros(0, dtype=torch.float32, device=dev)
             return
-        # CSR order is row-ascending, so a stable sort by column leaves rows ascending in a column
+        if self._rowptr.is_cuda:
+            # the library's transpose: a stable radix sort of the nonzeros by column
+            lib = _lib.lib()
+            ws = torch.empty(lib.gnnagg_csr_to_csc_workspace_bytes(self._M, self._K, nnz), dtype=torch.uint8, device=dev)
+            self._colptr = torch.empty(self._K + 1, dtype=torch.int64, device=dev)
+            self._row_T = torch.empty(nnz, dtype=torch.int32, device=dev)
+            self._value_T = torch.empty(nnz, dtype=torch.float32, device=dev)
+            rc = lib.gnnagg_csr_to_csc(self._rowptr.data_ptr(), self._col.data_ptr(), self._value.data_ptr(), self._M,
+                                       self._K, nnz, self._colptr.data_ptr(), self._row_T.data_ptr(),
+                                       self._value_T.data_ptr(), ws.data_ptr(), ws.numel(), _lib.stream_ptr(dev))
+            _lib.check(rc, "csr_to_csc")
+            return
+        # host tensors (plan tests on CPU): CSR order is row-ascending, so a stable sort by column leaves
+        # rows ascending in a column
         col64 = self._col.to(torch.int64)
         sorted_col, perm = torch.sort(col64, stable=True)
         rows = torch.repeat_interleave(torch.arange(self._M, device=dev, dtype=torch.int32),

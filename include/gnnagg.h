@@ -74,6 +74,18 @@ int gnnagg_spmm_csr_f32(const int64_t *rowptr, const int32_t *col, const float *
                         int32_t accumulate, const void *plan, void *scratch, size_t scratch_bytes,
                         void *stream);
 
+/* CSR -> CSC: the operand of the transposed product (SPMM_backward), built once per matrix.  Replaces the
+ * `src.storage.colptr() / row_T() / value_T()` arrays the reference takes from its sparse-tensor package
+ * and caches on the matrix (model/ops/spmm_kernel.py:76-80).  Stable: rows ascend inside every column,
+ * duplicated entries keep their CSR order.
+ *   colptr int64[K+1], row_T int32[nnz], val_T fp32[nnz]: outputs;
+ *   workspace: gnnagg_csr_to_csc_workspace_bytes(M, K, nnz) bytes, 256-byte aligned (about 16 bytes per
+ *   nonzero: a stable 8-bit-digit radix sort of (column, position) pairs).  M, K, nnz < 2^31. */
+size_t gnnagg_csr_to_csc_workspace_bytes(int64_t M, int64_t K, int64_t nnz);
+int gnnagg_csr_to_csc(const int64_t *rowptr, const int32_t *col, const float *val, int64_t M, int64_t K, int64_t nnz,
+                      int64_t *colptr, int32_t *row_T, float *val_T, void *workspace, size_t workspace_bytes,
+                      void *stream);
+
 /* K3b + K4 fused: the same SpMM with the dense operand given as a row-packed quantised halo buffer
  * instead of fp32 rows.  Column index c of the sparse matrix is a wire slot; its feature row is
  * decoded on the fly as fma(code, scale_c, zero_point_c) with the bf16 wire parameters -- exactly

@@ -250,3 +250,24 @@ def test_packed_operand_equals_unpack_then_spmm(cuda_lib, bits, F):
         spmm_kernel.spmm_packed(rp, c, v, K, codes, pb, segd, len(seg) - 1, bits, got, plan, accumulate=accumulate)
         torch.cuda.synchronize()
         np.testing.assert_array_equal(got.cpu().numpy().view(np.uint32), want.cpu().numpy().view(np.uint32))
+
+
+@pytest.mark.parametrize("M,K,deg,hubs", [(1, 1, 1, 0), (50, 37, 3, 0), (3000, 70000, 5, 2), (20000, 300, 40, 3), (257, 1 << 17, 2, 0)])
+def test_csr_to_csc_matches_stable_sort(cuda_lib, M, K, deg, hubs):
+    """gnnagg_csr_to_csc against a stable sort by column on the host: column pointers, row order inside a
+    column (ascending, duplicates in CSR order) and values, bit for bit."""
+    from gnn_benchmark_b200 import SparseTensor
+
+    rng = np.random.default_rng(M + K)
+    rowptr, col, val = random_csr(rng, M, K, deg, hubs=hubs, hub_len=min(K, 3000))
+    if col.size > 4:  # duplicated entries must keep their order
+        col[1] = col[0]
+        val[1] = val[0] + 1.0
+    A = SparseTensor(rowptr=to_dev(rowptr), col=to_dev(col), value=to_dev(val), sparse_sizes=(M, K))
+    colptr, row_T, val_T = A.storage.colptr(), A.storage.row_T(), A.storage.value_T()
+    torch.cuda.synchronize()
+    rows = np.repeat(np.arange(M), np.diff(rowptr))
+    order = np.argsort(col, kind="stable")
+    np.testing.assert_array_equal(colptr.cpu().numpy(), np.concatenate([[0], np.cumsum(np.bincount(col, minlength=K))]))
+    np.testing.assert_array_equal(row_T.cpu().numpy(), rows[order])
+    np.testing.assert_array_equal(val_T.cpu().numpy(), val[order])
