@@ -38,12 +38,9 @@ SIGNATURES = {
     "gnnagg_push_rows": (ctypes.c_int, [_vp, _i64, _vp, _i32, _vp, _i32, _i32, _i32, _vp, _i64, _i64, _vp]),
     "gnnagg_scale_rows_f32": (ctypes.c_int, [_vp, _i64, _vp, _i64, _i32, _i32, _vp, _vp, _i64, _vp]),
     "gnnagg_quant_pack_rows": (ctypes.c_int, [_vp, _i64, _vp, _i32, _vp, _i32, _i64, _i32, _i32, _vp, _vp, _vp, _vp]),
-    "gnnagg_spmm_quant_pack": (ctypes.c_int, [_vp, _vp, _vp, _i64, _i64, _i64, _vp, _i64, _i32, _vp, _i32, _i32, _vp, _vp, _i64,
-                                              _vp, _vp, _vp, _vp]),
-    "gnnagg_spmm_long_row_threshold": (_i32, []),
-    "gnnagg_spmm_long_row_segment": (_i32, []),
-    "gnnagg_spmm_long_rows": (ctypes.c_int, [_vp, _vp, _vp, _vp, _i64, _i32, _vp, _i32, _vp, _vp, _vp, _i32, _vp, _vp, _i64,
-                                             _vp]),
+    "gnnagg_spmm_quant_pack_scratch_bytes": (_sz, [_i64, _i64, _i32]),
+    "gnnagg_spmm_quant_pack": (ctypes.c_int, [_vp, _vp, _vp, _i64, _i64, _i64, _vp, _i64, _i32, _vp, _i32, _i32, _vp, _vp, _vp,
+                                              _vp, _vp, _sz, _vp]),
     "gnnagg_unpack_dequant_rows": (ctypes.c_int, [_vp, _i32, _vp, _i32, _i64, _i32, _vp, _vp, _vp, _i64, _vp]),
     "gnnagg_quant_v1_rows": (ctypes.c_int, [_vp, _i64, _i64, _i32, _vp, _vp, _vp, _vp]),
     "gnnagg_dequant_v1_rows": (ctypes.c_int, [_vp, _i64, _i32, _vp, _vp, _vp, _i64, _vp]),

@@ -26,7 +26,7 @@
 // accumulating).
 #include <limits.h>
 
-#include "common.cuh"
+#include "codec.cuh"
 
 namespace gnnagg {
 
@@ -181,22 +181,38 @@ struct PackedOperand {
     int F;
 };
 
-template <int G, int NV, int VW, int U, bool ACC, bool FULL, int QB>
+// PK: 0 = rows are written to Y; 2 / 4 / 8 = rows are quantised + packed as soon as they are summed and Y
+// is never touched (the send side of a packed exchange).  A row that lies inside one chunk is encoded
+// from the registers that hold its sum; the tail of a row that began in an earlier chunk is parked in
+// `pk.head` and the fix-up kernel encodes the row after adding the parked pieces.
+struct PackOut {
+    uint8_t *codes;         // zero-filled (sum_p ceil(n_p / (8/PK)), F) bytes
+    float *params;          // (M, 2) fp32 [zero_point, scale]
+    uint32_t *params_bf16;  // optional (M) bf16 pairs
+    const int32_t *seg;     // P+1 prefix of per-peer row counts
+    int P;
+    int F;
+    float *head;            // per chunk: the partial sum of its first row when that row began earlier
+};
+
+template <int G, int NV, int VW, int U, bool ACC, bool FULL, int QB, int PK>
 __global__ void __launch_bounds__(kWarpsPerBlock * 32, min_blocks_per_sm(NV))
     spmm_chunk_kernel(const int64_t *__restrict__ rowptr, const int32_t *__restrict__ col,
                       const float *__restrict__ val, int64_t M, const float *__restrict__ X, int64_t ldx,
                       float *__restrict__ Y, int64_t ldy, int FV,
                       const int64_t *__restrict__ chunk_nz, const int32_t *__restrict__ chunk_row, int64_t nchunks,
-                      float *__restrict__ carry, int carry_ld, PackedOperand q) {
+                      float *__restrict__ carry, int carry_ld, PackedOperand q, PackOut pk) {
     constexpr int S = 32 / G;  // nonzeros fetched per warp-wide gather instruction
     constexpr int EPB = QB ? 8 / QB : 1;
-    constexpr int SEGCAP = QB ? kMaxSeg + 1 : 1;
+    constexpr int SEGCAP = (QB || PK) ? kMaxSeg + 1 : 1;
+    static_assert(!(QB && PK), "a packed operand and a packed result are separate launches");
     __shared__ int sseg[SEGCAP];
     __shared__ int pbase[SEGCAP];
     __shared__ int s_col[kWarpsPerBlock][2][kTile];
     __shared__ float s_val[kWarpsPerBlock][2][kTile];
     __shared__ uint32_t s_prm[QB ? kWarpsPerBlock : 1][2][QB ? kTile : 1];
     if (QB) build_packed_prefix(q.seg, q.P, EPB, pbase, sseg);  // before any warp leaves: it synchronises the CTA
+    if (PK) build_packed_prefix(pk.seg, pk.P, 8 / (PK ? PK : 8), pbase, sseg);
     const int lane = threadIdx.x & 31;
     const int wib = threadIdx.x >> 5;
     const int64_t c = (int64_t)blockIdx.x * kWarpsPerBlock + wib;
@@ -302,6 +318,30 @@ __global__ void __launch_bounds__(kWarpsPerBlock * 32, min_blocks_per_sm(NV))
                 for (int k = 0; k < NV; ++k)
 #pragma unroll
                     for (int i = 0; i < VW; ++i) acc[k].v[i] += __shfl_xor_sync(kFullMask, acc[k].v[i], off);
+        }
+        if (PK) {
+            if (grp == 0) {
+                if (row_start < 0) {  // the row began in an earlier chunk: the fix-up kernel finishes and encodes it
+                    float *hp = pk.head + c * (int64_t)carry_ld;
+#pragma unroll
+                    for (int k = 0; k < NV; ++k)
+                        if (vok[k]) vstore_plain<VW>(hp + voff[k], acc[k]);
+                } else {
+                    constexpr int PKB = PK ? PK : 8;
+                    constexpr int PEPB = 8 / PKB;
+                    const int pseg = find_segment(sseg, pk.P, r);
+                    const int j = r - sseg[pseg];
+                    float4 xv[1][NV];
+#pragma unroll
+                    for (int k = 0; k < NV; ++k)
+                        xv[0][k] = make_float4(acc[k].v[0], acc[k].v[VW > 1 ? 1 : 0], acc[k].v[VW > 2 ? 2 : 0],
+                                               acc[k].v[VW > 3 ? 3 : 0]);
+                    const unsigned gmask = G == 32 ? kFullMask : ((1u << G) - 1u);
+                    quant_pack_group<PKB, NV, G, 1>(xv, 1, r, (int64_t)pbase[pseg] + j / PEPB, gl, gmask, 0, FV, pk.F, 0,
+                                                    pk.params, pk.params_bf16, pk.codes, (PEPB - 1 - j % PEPB) * PKB);
+                }
+            }
+            return;
         }
         // accumulating onto an empty row changes nothing: skip the store
         const bool untouched = acc_mode && row_start >= 0 && next_end == row_start;
@@ -475,6 +515,59 @@ __global__ void __launch_bounds__(kWarpsPerBlock * 32)
     }
 }
 
+// Packing twin of the fix-up kernel: the first chunk of a run that parks into `row` adds the run's parked
+// sums in chunk order onto the tail the finishing chunk left in `head` (the same additions, in the same
+// order, as spmm_fixup_kernel applies to Y) and encodes the row.
+template <int BITS>
+__global__ void __launch_bounds__(kWarpsPerBlock * 32)
+    spmm_fixup_pack_kernel(const int64_t *__restrict__ rowptr, int64_t M, const int64_t *__restrict__ chunk_nz,
+                           const int32_t *__restrict__ chunk_row, int64_t nchunks, const float *__restrict__ carry,
+                           int carry_ld, PackOut pk) {
+    constexpr int EPB = 8 / BITS;
+    __shared__ int sseg[kMaxSeg + 1];
+    __shared__ int pbase[kMaxSeg + 1];
+    build_packed_prefix(pk.seg, pk.P, EPB, pbase, sseg);
+    const int lane = threadIdx.x & 31;
+    const int64_t c = (int64_t)blockIdx.x * kWarpsPerBlock + (threadIdx.x >> 5);
+    if (c >= nchunks) return;
+    const int row = chunk_row[c + 1];
+    if (row >= M) return;
+    const int64_t rs = rowptr[row];
+    if (chunk_nz[c + 1] <= rs) return;                              // chunk c parks nothing
+    if (c > 0 && chunk_row[c] == row && chunk_nz[c] > rs) return;  // chunk c-1 leads this run
+    int64_t last = c;
+    while (last + 1 < nchunks && chunk_row[last + 2] == row) ++last;  // chunks c..last all park into `row`
+    const int FV = pk.F >> 2;
+    float4 xv[1][4];
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+        const int vi = lane + 32 * k;
+        xv[0][k] = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (vi < FV) {
+            float4 sum = make_float4(0.f, 0.f, 0.f, 0.f);
+            for (int64_t j = c; j <= last; ++j) {
+                const float4 t = *(reinterpret_cast<const float4 *>(carry + j * (int64_t)carry_ld) + vi);
+                sum.x += t.x, sum.y += t.y, sum.z += t.z, sum.w += t.w;
+            }
+            const float4 h = *(reinterpret_cast<const float4 *>(pk.head + (last + 1) * (int64_t)carry_ld) + vi);
+            xv[0][k] = make_float4(h.x + sum.x, h.y + sum.y, h.z + sum.z, h.w + sum.w);
+        }
+    }
+    const int pseg = find_segment(sseg, pk.P, row);
+    const int j = row - sseg[pseg];
+    quant_pack_group<BITS, 4, 32, 1>(xv, 1, row, (int64_t)pbase[pseg] + j / EPB, lane, kFullMask, 0, FV, pk.F, 0, pk.params,
+                                     pk.params_bf16, pk.codes, (EPB - 1 - j % EPB) * BITS);
+}
+
+// Zero fill of exactly the packed rows the segments need (their number lives on the device).
+__global__ void zero_codes_kernel(const int32_t *__restrict__ seg, int P, int epb, int F, uint8_t *__restrict__ codes) {
+    __shared__ int pbase[kMaxSeg + 1];
+    build_packed_prefix(seg, P, epb, pbase);
+    const int64_t words = (int64_t)pbase[P] * (F >> 2);
+    uint32_t *w = reinterpret_cast<uint32_t *>(codes);
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < words; i += (int64_t)gridDim.x * blockDim.x) w[i] = 0u;
+}
+
 __global__ void csr_validate_kernel(const int64_t *__restrict__ rowptr, const int32_t *__restrict__ col, int64_t M,
                                     int64_t K, int64_t nnz, int32_t *status) {
     const int64_t stride = (int64_t)gridDim.x * blockDim.x;
@@ -496,14 +589,28 @@ template <int G, int NV, int VW, int U>
 static void launch_chunks(const int64_t *rowptr, const int32_t *col, const float *val, int64_t M, const float *X,
                           int64_t ldx, float *Y, int64_t ldy, int FV, int accumulate, const int64_t *chunk_nz,
                           const int32_t *chunk_row, int64_t nchunks, float *carry, int carry_ld, int qbits,
-                          const PackedOperand &q, cudaStream_t st) {
+                          const PackedOperand &q, int pkbits, const PackOut &pk, cudaStream_t st) {
     const unsigned blocks = (unsigned)div_up(nchunks, kWarpsPerBlock);
     const bool full = (FV == G * NV) && VW == 4;
+    if (VW == 4 && pkbits != 0) {  // packing epilogue: fp32 operand, no accumulation, 128-bit path only
+#define GNNAGG_GO_PK(FULL, PK)                                                                                  \
+    spmm_chunk_kernel<G, NV, VW, U, false, FULL, 0, (VW == 4 ? PK : 0)><<<blocks, kWarpsPerBlock * 32, 0, st>>>( \
+        rowptr, col, val, M, X, ldx, Y, ldy, FV, chunk_nz, chunk_row, nchunks, carry, carry_ld, q, pk)
+        if (pkbits == 2) {
+            if (full) GNNAGG_GO_PK((VW == 4), 2); else GNNAGG_GO_PK(false, 2);
+        } else if (pkbits == 4) {
+            if (full) GNNAGG_GO_PK((VW == 4), 4); else GNNAGG_GO_PK(false, 4);
+        } else {
+            if (full) GNNAGG_GO_PK((VW == 4), 8); else GNNAGG_GO_PK(false, 8);
+        }
+#undef GNNAGG_GO_PK
+        return;
+    }
     // a packed gather is 4 bytes per lane instead of 16: where registers allow, keep more in flight
     constexpr int UQ = NV == 2 ? 8 : U;  // F in (128, 256]: eight packed gathers in flight instead of four
 #define GNNAGG_GO(ACC, FULL, QB)                                                                              \
-    spmm_chunk_kernel<G, NV, VW, (QB ? UQ : U), ACC, FULL, QB><<<blocks, kWarpsPerBlock * 32, 0, st>>>(       \
-        rowptr, col, val, M, X, ldx, Y, ldy, FV, chunk_nz, chunk_row, nchunks, carry, carry_ld, q)
+    spmm_chunk_kernel<G, NV, VW, (QB ? UQ : U), ACC, FULL, QB, 0><<<blocks, kWarpsPerBlock * 32, 0, st>>>(    \
+        rowptr, col, val, M, X, ldx, Y, ldy, FV, chunk_nz, chunk_row, nchunks, carry, carry_ld, q, pk)
     if (VW == 4 && qbits != 0) {  // packed operand: 128-bit path only, per-vector predicates kept
         if (qbits == 2) {
             if (accumulate) GNNAGG_GO(true, false, (VW == 4 ? 2 : 0)); else GNNAGG_GO(false, false, (VW == 4 ? 2 : 0));
@@ -524,10 +631,11 @@ template <int VW>
 static void dispatch_width(int FV, const int64_t *rowptr, const int32_t *col, const float *val, int64_t M,
                            const float *X, int64_t ldx, float *Y, int64_t ldy, int accumulate,
                            const int64_t *chunk_nz, const int32_t *chunk_row, int64_t nchunks, float *carry,
-                           int carry_ld, int qbits, const PackedOperand &q, cudaStream_t st) {
+                           int carry_ld, int qbits, const PackedOperand &q, int pkbits, const PackOut &pk,
+                           cudaStream_t st) {
 #define GNNAGG_LAUNCH(G, NV, U)                                                                                 \
     launch_chunks<G, NV, VW, U>(rowptr, col, val, M, X, ldx, Y, ldy, FV, accumulate, chunk_nz, chunk_row, nchunks, \
-                                carry, carry_ld, qbits, q, st)
+                                carry, carry_ld, qbits, q, pkbits, pk, st)
     if (FV <= 2)
         GNNAGG_LAUNCH(2, 1, 2);
     else if (FV <= 4)
@@ -621,12 +729,13 @@ static int spmm_launch(const char *who, const int64_t *rowptr, const int32_t *co
         float *Ys = Y + f0;
         PackedOperand qs = q;
         if (qbits != 0) qs.codes = q.codes + f0;  // one byte per column: the strip starts f0 bytes into each packed row
+        const PackOut nopack = {nullptr, nullptr, nullptr, nullptr, 0, 0, nullptr};
         if (vec4)
             dispatch_width<4>(fs / 4, rowptr, col, val, M, Xs, ldx, Ys, ldy, accumulate, cnz, crow, nc, carry, carry_ld,
-                              qbits, qs, st);
+                              qbits, qs, 0, nopack, st);
         else
             dispatch_width<1>(fs, rowptr, col, val, M, Xs, ldx, Ys, ldy, accumulate, cnz, crow, nc, carry, carry_ld, 0, qs,
-                              st);
+                              0, nopack, st);
         int rc = check_launch("spmm_chunk_kernel");
         if (rc != GNNAGG_OK) return rc;
         spmm_fixup_kernel<<<(unsigned)div_up(nc, kWarpsPerBlock), kWarpsPerBlock * 32, 0, st>>>(
@@ -660,6 +769,58 @@ extern "C" int gnnagg_spmm_csr_q(const int64_t *rowptr, const int32_t *col, cons
     PackedOperand q = {codes, static_cast<const uint32_t *>(params_bf16), seg, P, F};
     return spmm_launch("spmm_q", rowptr, col, val, M, K, nnz, nullptr, 0, Y, ldy, F, accumulate, plan, scratch,
                        scratch_bytes, bits, q, stream);
+}
+
+extern "C" size_t gnnagg_spmm_quant_pack_scratch_bytes(int64_t M, int64_t nnz, int32_t F) {
+    return 2 * gnnagg_spmm_scratch_bytes(M, nnz, F);  // parked sums of cut rows + the tails of the chunks that finish them
+}
+
+extern "C" int gnnagg_spmm_quant_pack(const int64_t *rowptr, const int32_t *col, const float *val, int64_t M, int64_t K,
+                                      int64_t nnz, const float *X, int64_t ldx, int32_t F, const int32_t *seg,
+                                      int32_t P, int32_t bits, float *params, void *params_bf16, uint8_t *codes,
+                                      const void *plan, void *scratch, size_t scratch_bytes, void *stream) {
+    if (M < 0 || K < 0 || nnz < 0 || F < 0) return fail(GNNAGG_ERR_ARG, "spmm_quant_pack: negative size");
+    if (bits != 2 && bits != 4 && bits != 8) return fail(GNNAGG_ERR_ARG, "spmm_quant_pack: bits must be 2, 4 or 8");
+    if (seg == nullptr || P < 1) return fail(GNNAGG_ERR_ARG, "spmm_quant_pack: bad seg / P");
+    if (P > kMaxSeg) return fail(GNNAGG_ERR_UNSUPPORTED, "spmm_quant_pack: more than %d segments", kMaxSeg);
+    if (M == 0 || F == 0) return GNNAGG_OK;
+    if (rowptr == nullptr || params == nullptr || codes == nullptr || plan == nullptr ||
+        (nnz > 0 && (col == nullptr || val == nullptr || X == nullptr)))
+        return fail(GNNAGG_ERR_ARG, "spmm_quant_pack: null pointer");
+    if (ldx < F) return fail(GNNAGG_ERR_ARG, "spmm_quant_pack: ldx < F");
+    if (M > INT32_MAX - 64 || K > INT32_MAX) return fail(GNNAGG_ERR_UNSUPPORTED, "spmm_quant_pack: M, K must fit int32");
+    const bool ok = (F % 4 == 0) && F <= 512 && (ldx % 4 == 0) && aligned16(X) &&
+                    (reinterpret_cast<uintptr_t>(codes) % 4 == 0) && (reinterpret_cast<uintptr_t>(params) % 8 == 0) &&
+                    (params_bf16 == nullptr || reinterpret_cast<uintptr_t>(params_bf16) % 4 == 0);
+    if (!ok)
+        return fail(GNNAGG_ERR_UNSUPPORTED,
+                    "spmm_quant_pack: needs F %% 4 == 0, F <= 512 and 16-byte aligned dense rows; use gnnagg_spmm_csr_f32 "
+                    "followed by gnnagg_quant_pack_rows");
+    const size_t half = gnnagg_spmm_scratch_bytes(M, nnz, F);
+    if (scratch == nullptr || scratch_bytes < 2 * half || !aligned16(scratch))
+        return fail(GNNAGG_ERR_SCRATCH, "spmm_quant_pack: scratch missing, smaller than %zu bytes or not 16-byte aligned", 2 * half);
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    const int64_t nc = num_chunks(M, nnz, chunk_items());
+    const int64_t *cnz = plan_chunk_nz(plan);
+    const int32_t *crow = plan_chunk_row(plan, nc);
+    float *carry = static_cast<float *>(scratch);
+    const int carry_ld = (F + 3) & ~3;
+    PackOut pk = {codes, params, static_cast<uint32_t *>(params_bf16), seg, P, F,
+                  reinterpret_cast<float *>(static_cast<char *>(scratch) + half)};
+    if (bits != 8) {  // codes are OR-ed in row by row: start from zero
+        zero_codes_kernel<<<kNumSMs * 4, 256, 0, st>>>(seg, P, 8 / bits, F, codes);
+        const int rc0 = check_launch("zero_codes_kernel");
+        if (rc0 != GNNAGG_OK) return rc0;
+    }
+    const PackedOperand none = {nullptr, nullptr, nullptr, 0, 0};
+    dispatch_width<4>(F / 4, rowptr, col, val, M, X, ldx, nullptr, 0, 0, cnz, crow, nc, carry, carry_ld, 0, none, bits, pk, st);
+    int rc = check_launch("spmm_chunk_kernel (packing epilogue)");
+    if (rc != GNNAGG_OK) return rc;
+    const unsigned fb = (unsigned)div_up(nc, kWarpsPerBlock);
+    if (bits == 2) spmm_fixup_pack_kernel<2><<<fb, kWarpsPerBlock * 32, 0, st>>>(rowptr, M, cnz, crow, nc, carry, carry_ld, pk);
+    else if (bits == 4) spmm_fixup_pack_kernel<4><<<fb, kWarpsPerBlock * 32, 0, st>>>(rowptr, M, cnz, crow, nc, carry, carry_ld, pk);
+    else spmm_fixup_pack_kernel<8><<<fb, kWarpsPerBlock * 32, 0, st>>>(rowptr, M, cnz, crow, nc, carry, carry_ld, pk);
+    return check_launch("spmm_fixup_pack_kernel");
 }
 
 extern "C" int gnnagg_csr_validate(const int64_t *rowptr, const int32_t *col, int64_t M, int64_t K, int64_t nnz,

@@ -118,61 +118,11 @@ def quant_pack_fusable(other: torch.Tensor) -> bool:
             and F % 4 == 0 and 0 < F <= 512 and other.stride(0) % 4 == 0 and other.data_ptr() % 16 == 0)
 
 
-class LongRows(object):
-    """The rows of a CSR matrix with more nonzeros than one lane group should sum alone (hub vertices),
-    cut into fixed-size segments for `gnnagg_spmm_long_rows`.  Built once per sparsity pattern."""
-
-    def __init__(self, rowptr: torch.Tensor):
-        lib = _lib.lib()
-        thr, seg = lib.gnnagg_spmm_long_row_threshold(), lib.gnnagg_spmm_long_row_segment()
-        dev = rowptr.device
-        deg = rowptr[1:] - rowptr[:-1]
-        idx = torch.nonzero(deg > thr).view(-1)
-        self.L = int(idx.numel())
-        self.S = 0
-        if self.L == 0:
-            return
-        nseg = (deg[idx] + (seg - 1)) // seg
-        ptr = torch.zeros(self.L + 1, dtype=torch.int64, device=dev)
-        torch.cumsum(nseg, 0, out=ptr[1:])
-        self.S = int(ptr[-1])
-        seg_row = torch.repeat_interleave(torch.arange(self.L, device=dev), nseg)
-        self.seg_off = (torch.arange(self.S, device=dev) - ptr[seg_row]).to(torch.int32)
-        self.seg_row = seg_row.to(torch.int32)
-        self.row_seg_ptr = ptr.to(torch.int32)
-        self.long_idx = idx.to(torch.int32)
-        self.long_pos = torch.full((rowptr.numel() - 1,), -1, dtype=torch.int32, device=dev)
-        self.long_pos[idx] = torch.arange(self.L, dtype=torch.int32, device=dev)
-
-
-_long_scratch = {}
-
-
-def _sum_long_rows(long: LongRows, rowptr, col, value, other: torch.Tensor):
-    """-> (L, ld) fp32 sums of the long rows of CSR @ other (scratch owned by this module, per stream)."""
-    F = other.size(1)
-    ld = (F + 3) // 4 * 4
-    need = (long.S + long.L) * ld
-    key = (other.device.index, _lib.stream_ptr(other.device))
-    buf = _long_scratch.get(key)
-    if buf is None or buf.numel() < need:
-        buf = torch.empty(need, dtype=torch.float32, device=other.device)
-        _long_scratch[key] = buf
-    partial, sums = buf[:long.S * ld], buf[long.S * ld: need]
-    rc = _lib.lib().gnnagg_spmm_long_rows(rowptr.data_ptr(), col.data_ptr(), value.data_ptr(), other.data_ptr(),
-                                          other.stride(0), F, long.long_idx.data_ptr(), long.L, long.seg_row.data_ptr(),
-                                          long.seg_off.data_ptr(), long.row_seg_ptr.data_ptr(), long.S,
-                                          partial.data_ptr(), sums.data_ptr(), ld, _lib.stream_ptr(other.device))
-    _lib.check(rc, "spmm_long_rows")
-    return sums, ld
-
-
 def spmm_quant_pack(rowptr, col, value, K: int, other: torch.Tensor, codes: torch.Tensor, params: torch.Tensor,
-                    params_bf16, seg: torch.Tensor, num_segments: int, bits: int, long: LongRows = None) -> None:
+                    params_bf16, seg: torch.Tensor, num_segments: int, bits: int, plan: torch.Tensor) -> None:
     """codes, params = quantise_pack(CSR[M,K] @ other) without the fp32 product ever reaching memory;
-    row i of the matrix is wire slot i, `seg` the per-peer slot prefix.  `long`: the matrix's LongRows
-    (hub rows are then summed by many CTAs each before the fused kernel runs)."""
-    _lib.require_cuda(rowptr, col, value, other, codes, params, params_bf16, seg)
+    row i of the matrix is wire slot i, `seg` the per-peer slot prefix, `plan` the matrix's SpMM plan."""
+    _lib.require_cuda(rowptr, col, value, other, codes, params, params_bf16, seg, plan)
     if other.dtype != torch.float32 or codes.dtype != torch.uint8 or params.dtype != torch.float32:
         raise RuntimeError("spmm_quant_pack: expected float32 operand / params and uint8 codes")
     M, F = rowptr.numel() - 1, other.size(1)
@@ -181,15 +131,13 @@ def spmm_quant_pack(rowptr, col, value, K: int, other: torch.Tensor, codes: torc
         raise RuntimeError("spmm_quant_pack: shape mismatch")
     if M == 0 or F == 0:
         return
-    long_pos = sums = None
-    ld = 0
-    if long is not None and long.L > 0:
-        sums, ld = _sum_long_rows(long, rowptr, col, value, other)
-        long_pos = long.long_pos
-    rc = _lib.lib().gnnagg_spmm_quant_pack(rowptr.data_ptr(), _lib.ptr(col), _lib.ptr(value), M, K, col.numel(),
-                                           other.data_ptr(), other.stride(0), F, seg.data_ptr(), num_segments, bits,
-                                           _lib.ptr(long_pos), _lib.ptr(sums), ld, params.data_ptr(),
-                                           _lib.ptr(params_bf16), codes.data_ptr(), _lib.stream_ptr(other.device))
+    nnz = col.numel()
+    lib = _lib.lib()
+    scratch = _get_scratch(other.device, lib.gnnagg_spmm_quant_pack_scratch_bytes(M, nnz, F))
+    rc = lib.gnnagg_spmm_quant_pack(rowptr.data_ptr(), _lib.ptr(col), _lib.ptr(value), M, K, nnz, other.data_ptr(),
+                                    other.stride(0), F, seg.data_ptr(), num_segments, bits, params.data_ptr(),
+                                    _lib.ptr(params_bf16), codes.data_ptr(), plan.data_ptr(), scratch.data_ptr(),
+                                    scratch.numel(), _lib.stream_ptr(other.device))
     _lib.check(rc, "spmm_quant_pack")
 
 
@@ -197,10 +145,11 @@ def SPMM_forward_quant_pack(src: SparseTensor, other, codes, params, params_bf16
     """quantise_pack(src @ other): SPMM_forward into the send buffer followed by the quantiser
     (model/layers/aggregator.py:48-49 + communicator.py:281-284 of the reference) as one pass."""
     rowptr, col, value = src.csr()
-    if getattr(src, "_long_rows", None) is None:
-        src._long_rows = LongRows(rowptr)
-    spmm_quant_pack(rowptr, col, value, src.sparse_size(1), other, codes, params, params_bf16, seg, num_segments, bits,
-                    src._long_rows)
+    plan = src.get_work_range()
+    if plan.size(0) == 0:
+        plan = build_plan(rowptr, src.nnz())
+        src.set_work_range(plan)
+    spmm_quant_pack(rowptr, col, value, src.sparse_size(1), other, codes, params, params_bf16, seg, num_segments, bits, plan)
     return None
 
 
@@ -208,10 +157,12 @@ def SPMM_backward_quant_pack(src: SparseTensor, other, codes, params, params_bf1
     """quantise_pack(src^T @ other) on the cached CSC arrays (the backward twin,
     model/layers/aggregator.py:145-149 + the quantiser)."""
     colptr = src.storage.colptr()
-    if getattr(src, "_long_rows_T", None) is None:
-        src._long_rows_T = LongRows(colptr)
+    plan = src.get_work_range_for_transpose()
+    if plan.size(0) == 0:
+        plan = build_plan(colptr, src.nnz())
+        src.set_work_range_for_transpose(plan)
     spmm_quant_pack(colptr, src.storage.row_T(), src.storage.value_T(), src.sparse_size(0), other, codes, params,
-                    params_bf16, seg, num_segments, bits, src._long_rows_T)
+                    params_bf16, seg, num_segments, bits, plan)
     return None
 
 

@@ -191,10 +191,11 @@ int gnnagg_quant_pack_rows(const float *X, int64_t ldx, const int32_t *idx, int3
                            void *params_bf16, uint8_t *codes, void *stream);
 
 /* K2 + K3a fused: SpMM whose output rows are quantised + packed in its epilogue instead of stored.
- * Row i of the CSR matrix is wire slot i; its sum over the nonzeros (one fused multiply-add each, in
- * CSR order, starting from zero: the chain of model/ops/src/spmm.cpp:97-126) stays in registers and
- * goes straight into the encoder of gnnagg_quant_pack_rows, so the fp32 send buffer of the exchange is
- * never written or read.  Replaces the pair
+ * Row i of the CSR matrix is wire slot i.  The kernel is gnnagg_spmm_csr_f32's (same plan, same chunking,
+ * same summation order); where that one would store a finished row it encodes the row from the registers
+ * that hold it and ORs its codes into the packed buffer, so the fp32 send buffer of the exchange is never
+ * written or read.  Rows cut across chunks (hub vertices) are finished and encoded by the fix-up kernel.
+ * Replaces the pair
  *   SPMM_forward(adj_t_pre_post_aggr_to, x, send_buf)            (model/layers/aggregator.py:48-49)
  *   quantize_tensor_for_all_procs(send_buf, ...)                 (communicator.py:281-284,
  *                                                                 model/ops/src/quantization_arm.cpp:364-435)
@@ -202,33 +203,16 @@ int gnnagg_quant_pack_rows(const float *X, int64_t ldx, const int32_t *idx, int3
  *   SPMM_backward(remote_adj_t | adj_t_pre_post_aggr_from, grad, recv_buf) + quantise
  *                                                                (model/layers/aggregator.py:145-149).
  *   M = number of wire slots = seg[P];  X (K,F) fp32 with leading dimension ldx;
- *   params / params_bf16 / codes / seg / P / bits: as for gnnagg_quant_pack_rows (params computed here).
- *   long_pos / long_sums / ld_long: optional.  A packed row is summed by one group of lanes, which suits
- *     the short rows of a halo matrix; rows with more than gnnagg_spmm_long_row_threshold() nonzeros (hub
- *     vertices) should be summed beforehand with gnnagg_spmm_long_rows and passed in: long_pos[i] = k >= 0
- *     means "slot i's sum is long_sums[k*ld_long ...]", -1 means "sum it here".  NULL: every row here.
+ *   params / params_bf16 / codes / seg / P / bits: as for gnnagg_quant_pack_rows (params computed here);
+ *   plan: gnnagg_spmm_plan_build of this matrix; scratch: gnnagg_spmm_quant_pack_scratch_bytes(M, nnz, F).
  * Needs F % 4 == 0, F <= 512, ldx % 4 == 0 and 16-byte aligned X (GNNAGG_ERR_UNSUPPORTED otherwise: run
- * the two calls).  Rows summed here follow the reference's sequential chain exactly, so their codes and
- * parameters equal the reference's bytes for every width (and those of the two-call sequence wherever
- * that sums in the same order: F > 64, row within one chunk); rows passed in through long_sums differ by
- * fp32 re-association, like rows cut across chunks in gnnagg_spmm_csr_f32. */
+ * the two calls).  Codes and parameters are bit-identical to gnnagg_spmm_csr_f32(accumulate = 0) followed
+ * by gnnagg_quant_pack_rows, for every width and row length. */
+size_t gnnagg_spmm_quant_pack_scratch_bytes(int64_t M, int64_t nnz, int32_t F);
 int gnnagg_spmm_quant_pack(const int64_t *rowptr, const int32_t *col, const float *val, int64_t M, int64_t K,
                            int64_t nnz, const float *X, int64_t ldx, int32_t F, const int32_t *seg, int32_t P,
-                           int32_t bits, const int32_t *long_pos, const float *long_sums, int64_t ld_long,
-                           float *params, void *params_bf16, uint8_t *codes, void *stream);
-
-/* Sums of the long rows of a CSR matrix, many CTAs per row: row long_idx[k] (k < L) is cut into segments of
- * gnnagg_spmm_long_row_segment() nonzeros; segment s belongs to long row seg_row[s] and is its seg_off[s]-th
- * segment; row k owns the segments row_seg_ptr[k] .. row_seg_ptr[k+1]-1 (S in total).  One CTA sums one
- * segment into partial[s*ld ...] (S*ld floats of scratch), then sums[k*ld ...] = its segments added in
- * order.  Deterministic.  Part of the replacement of spmm (model/ops/src/spmm.cpp:327-507) on the
- * send side of a packed exchange; see gnnagg_spmm_quant_pack. */
-int32_t gnnagg_spmm_long_row_threshold(void);
-int32_t gnnagg_spmm_long_row_segment(void);
-int gnnagg_spmm_long_rows(const int64_t *rowptr, const int32_t *col, const float *val, const float *X, int64_t ldx,
-                          int32_t F, const int32_t *long_idx, int32_t L, const int32_t *seg_row,
-                          const int32_t *seg_off, const int32_t *row_seg_ptr, int32_t S, float *partial, float *sums,
-                          int64_t ld, void *stream);
+                           int32_t bits, float *params, void *params_bf16, uint8_t *codes, const void *plan,
+                           void *scratch, size_t scratch_bytes, void *stream);
 
 /* ------------------------------------------------------------------------------------
  * K3b  unpack + dequantise   OUT[i,k] = fma(code, scale_i, zero_point_i)
