@@ -33,9 +33,17 @@ from .time_recorder import TimeRecorder
 # Set to False to get the reference's two-step sequence, e.g. to inspect comm_buf.recv_buf.
 FUSE_UNPACK = True
 # Packed halo modes: quantise + pack as the epilogue of the SpMM that produces the rows to send (forward:
-# pre-aggregation; backward: transposed receive-side matrix), so comm_buf.send_buf / recv_buf are not
-# written.  Set to False for the reference's two-step sequence.
-FUSE_PACK = True
+# pre-aggregation; backward: transposed receive-side matrix), so comm_buf.send_buf / recv_buf are never
+# written.  "lean": only where those fp32 buffers do not exist (lean halo buffers) -- with the buffers there,
+# SpMM into them followed by the pack kernel is the faster pair below 256 columns (the encoder inside the
+# SpMM costs instruction-cache misses); True: always; False: never (the reference's two-step sequence).
+FUSE_PACK = "lean"
+
+
+def _fuse_pack(graph) -> bool:
+    if FUSE_PACK == "lean":
+        return bool(getattr(graph.comm_buf, "lean", False))
+    return bool(FUSE_PACK)
 
 
 def _world_size() -> int:
@@ -156,7 +164,7 @@ class Aggregator(torch.autograd.Function):
             send_buf = graph.comm_buf.send_buf
             q = graph.comm_buf_for_quantization
             fused_pack = False
-            if is_pre_delay and packed and FUSE_PACK and quant_pack_fusable(x):
+            if is_pre_delay and packed and _fuse_pack(graph) and quant_pack_fusable(x):
                 # pre-aggregation with the quantise + pack step as its epilogue
                 SPMM_forward_quant_pack(graph.adj_t_pre_post_aggr_to, x, q.quantized_send_data_buf,
                                         q.quantized_send_params_buf_fp32, q.quantized_send_params_buf_bf16,
@@ -276,7 +284,7 @@ class Aggregator(torch.autograd.Function):
                                                        before_send=make_block)
             if rec:
                 rec.record_pre_aggregate_time(t)
-        elif world_size > 1 and packed and FUSE_PACK and quant_pack_fusable(g):
+        elif world_size > 1 and packed and _fuse_pack(graph) and quant_pack_fusable(g):
             # halo gradients: the transposed receive-side SpMM packs its rows in its epilogue, so the fp32
             # halo buffer is never needed (the receive-side buffers are the ones sent: the roles swap)
             _resize(graph, feat_len, num_bits)

@@ -72,7 +72,8 @@ def _push(plan, direction, cur, jobs, groups):
 
 
 def forward(graph, x, feat_len, num_bits, is_pre_delay, packed, world_size, rec):
-    from .aggregator import _prefix as prefix, _remote_parts as remote_parts, _resize as resize, _send_idx as send_idx
+    from .aggregator import (_fuse_pack as fuse_pack, _prefix as prefix, _remote_parts as remote_parts,
+                             _resize as resize, _send_idx as send_idx)
 
     plan = graph.push_plan
     P, r = world_size, plan.rank
@@ -83,12 +84,17 @@ def forward(graph, x, feat_len, num_bits, is_pre_delay, packed, world_size, rec)
     n_groups = Communicator.ctx.push_groups if (not packed and not is_pre_delay) else 1
     groups = _groups(P, r, n_groups)
     if packed:
-        if is_pre_delay:
-            if not quant_pack_fusable(x):
-                raise RuntimeError("push transport, packed pre/post path: feature rows must suit the fused pack kernel")
+        if is_pre_delay and fuse_pack(graph) and quant_pack_fusable(x):
             SPMM_forward_quant_pack(graph.adj_t_pre_post_aggr_to, x, q.quantized_send_data_buf,
                                     q.quantized_send_params_buf_fp32, q.quantized_send_params_buf_bf16,
                                     q.quantized_work_range_per_proc, P, _bits())
+        elif is_pre_delay:
+            if getattr(graph.comm_buf, "lean", False):
+                raise RuntimeError("lean halo buffers: feature rows must suit the fused pack kernel")
+            SPMM_forward(graph.adj_t_pre_post_aggr_to, x, graph.comm_buf.send_buf, accumulate=False)
+            Quantizer_for_all_procs.ctx.quantize_fp32_to_intX(
+                graph.comm_buf.send_buf, q.quantized_send_data_buf, q.quantized_send_params_buf_fp32,
+                q.quantized_work_range_per_proc, params_bf16=q.quantized_send_params_buf_bf16)
         else:
             Quantizer_for_all_procs.ctx.quantize_fp32_to_intX(
                 x, q.quantized_send_data_buf, q.quantized_send_params_buf_fp32, q.quantized_work_range_per_proc,
@@ -135,8 +141,8 @@ def forward(graph, x, feat_len, num_bits, is_pre_delay, packed, world_size, rec)
 
 
 def backward(graph, g, feat_len, num_bits, is_pre_delay, packed, world_size, rec):
-    from .aggregator import (_prefix as prefix, _remote_parts as remote_parts, _resize as resize,
-                             _scatter_adj as scatter_adj)
+    from .aggregator import (_fuse_pack as fuse_pack, _prefix as prefix, _remote_parts as remote_parts,
+                             _resize as resize, _scatter_adj as scatter_adj)
 
     plan = graph.push_plan
     P, r = world_size, plan.rank
@@ -149,11 +155,16 @@ def backward(graph, g, feat_len, num_bits, is_pre_delay, packed, world_size, rec
     groups = _groups(P, r, n_groups)
     t = rec.start() if rec else None
     if packed:
-        if not quant_pack_fusable(g):
-            raise RuntimeError("push transport, packed halo: gradient rows must suit the fused pack kernel")
-        if have_halo:
+        if have_halo and fuse_pack(graph) and quant_pack_fusable(g):
             SPMM_backward_quant_pack(adj, g, q.quantized_recv_data_buf, q.quantized_recv_params_buf_fp32,
                                      q.quantized_recv_params_buf_bf16, q.dequantized_work_range_per_proc, P, _bits())
+        elif have_halo:
+            if getattr(graph.comm_buf, "lean", False):
+                raise RuntimeError("lean halo buffers: gradient rows must suit the fused pack kernel")
+            SPMM_backward(adj, g, graph.comm_buf.recv_buf, accumulate=False)
+            Quantizer_for_all_procs.ctx.quantize_fp32_to_intX(
+                graph.comm_buf.recv_buf, q.quantized_recv_data_buf, q.quantized_recv_params_buf_fp32,
+                q.dequantized_work_range_per_proc, params_bf16=q.quantized_recv_params_buf_bf16)
         signals = _push(plan, "backward", cur, [("codes", q.quantized_recv_data_buf, feat_len, None),
                                                 ("params", q.quantized_recv_params_buf_bf16, 4, None)], groups)
     elif len(groups) == 1:

@@ -112,14 +112,14 @@ __device__ __forceinline__ void quant_exact_rows(const float4 (&xv)[ROWS][NV], c
 // by the GQ lanes of one group: per-row min / max, parameters, codes, stores.
 //   ROWS == 8 / BITS: the rows are the <= EPB rows of packed row R (the stand-alone pack kernel, which
 //     loads them from memory) and the packed bytes are written with plain stores;
-//   ROWS == 1: one input row whose codes go to bit position sh0 of packed row R (the SpMM that packs
-//     each row as soon as it is summed); the rows that share its bytes are written by other warps at
-//     other times, so the codes are OR-ed into the zero-initialised buffer with atomics.
+//   ROWS == 1: one input row whose codes belong at bit position sh0 of its packed row (the SpMM that
+//     encodes each row as soon as it is summed); nothing is stored, the shifted codes are returned in
+//     `wout` and the caller merges the rows that share a packed row.
 template <int BITS, int NV, int GQ, int ROWS = 8 / BITS>
 __device__ __forceinline__ void quant_pack_group(const float4 (&xv)[ROWS][NV], int cnt, int i0, int64_t R, int gl,
                                                  unsigned gmask, int lead, int FV, int F, int params_given,
                                                  float *__restrict__ params, uint32_t *__restrict__ params_bf16,
-                                                 uint8_t *__restrict__ codes, int sh0 = 0) {
+                                                 uint8_t *__restrict__ codes, int sh0 = 0, uint32_t *wout = nullptr) {
     constexpr int EPB = 8 / BITS;
     constexpr float LEVELS = (float)((1 << BITS) - 1);
     float zp[ROWS], rinv[ROWS], sc[ROWS];
@@ -217,15 +217,15 @@ __device__ __forceinline__ void quant_pack_group(const float4 (&xv)[ROWS][NV], i
     if (__any_sync(gmask, unsure)) {
         quant_exact_rows<BITS, NV, GQ, ROWS>(xv, zp, sc, cnt, gl, FV, params_given != 0, sh0, words);
     }
-    uint32_t *out = reinterpret_cast<uint32_t *>(codes + R * (int64_t)F);
+    if (ROWS == EPB && wout == nullptr) {
+        uint32_t *out = reinterpret_cast<uint32_t *>(codes + R * (int64_t)F);
 #pragma unroll
-    for (int k = 0; k < NV; ++k)
-        if (gl + GQ * k < FV) {
-            if (ROWS == EPB)
-                __stcs(out + gl + GQ * k, words[k]);
-            else if (words[k] != 0u)
-                atomicOr(out + gl + GQ * k, words[k]);
-        }
+        for (int k = 0; k < NV; ++k)
+            if (gl + GQ * k < FV) __stcs(out + gl + GQ * k, words[k]);
+    } else {
+#pragma unroll
+        for (int k = 0; k < NV; ++k) wout[k] = (gl + GQ * k < FV) ? words[k] : 0u;
+    }
 
 }
 

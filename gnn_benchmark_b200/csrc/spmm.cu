@@ -195,8 +195,18 @@ struct PackOut {
     float *head;            // per chunk: the partial sum of its first row when that row began earlier
 };
 
+// The encoder is a few hundred instructions; inlined at every place a row can end it would push the gather
+// loop out of the instruction cache (measured: warps stalled on instruction fetch 15x more often than on
+// anything else).  One out-of-line copy per kernel, called once per row.
+template <int BITS, int NV, int G>
+__device__ __noinline__ void encode_row(const float4 (&xv)[1][NV], int row, int gl, int FV, int F, float *params,
+                                        uint32_t *params_bf16, int sh, uint32_t (&w)[NV]) {
+    const unsigned gmask = G == 32 ? kFullMask : ((1u << G) - 1u);
+    quant_pack_group<BITS, NV, G, 1>(xv, 1, row, 0, gl, gmask, 0, FV, F, 0, params, params_bf16, nullptr, sh, w);
+}
+
 template <int G, int NV, int VW, int U, bool ACC, bool FULL, int QB, int PK>
-__global__ void __launch_bounds__(kWarpsPerBlock * 32, min_blocks_per_sm(NV))
+__global__ void __launch_bounds__(kWarpsPerBlock * 32, (PK ? GNNAGG_SPMM_MINBLOCKS_WIDE : min_blocks_per_sm(NV)))
     spmm_chunk_kernel(const int64_t *__restrict__ rowptr, const int32_t *__restrict__ col,
                       const float *__restrict__ val, int64_t M, const float *__restrict__ X, int64_t ldx,
                       float *__restrict__ Y, int64_t ldy, int FV,
@@ -309,6 +319,27 @@ __global__ void __launch_bounds__(kWarpsPerBlock * 32, min_blocks_per_sm(NV))
         load_y(next_row_needs_y() ? r + 1 : (int)M, ynext);
     };
 
+    // Packing epilogue: consecutive rows share a packed row (8 / PK rows per byte), and a warp meets them one
+    // after the other, so the codes of the packed row in progress are merged in registers.  A packed row
+    // whose rows were all encoded here is written with one plain store; one that is shared with another
+    // chunk, or with a row the fix-up kernel finishes, is OR-ed into the zero-filled buffer.
+    int pend_R = -1, pend_n = 0, pend_cnt = 0;
+    uint32_t pend_w[PK ? NV : 1];
+    auto flush_pending = [&]() {
+        if (PK && pend_R >= 0 && grp == 0) {
+            uint32_t *out = reinterpret_cast<uint32_t *>(pk.codes + (int64_t)pend_R * pk.F);
+#pragma unroll
+            for (int k = 0; k < (PK ? NV : 1); ++k)
+                if (vok[k]) {
+                    if (pend_n == pend_cnt)
+                        __stcs(out + gl + k * G, pend_w[k]);
+                    else if (pend_w[k] != 0u)
+                        atomicOr(out + gl + k * G, pend_w[k]);
+                }
+        }
+        pend_R = -1;
+    };
+
     // Fold the S lane groups and write row r (its last nonzero is in this chunk).
     auto flush_row = [&]() {
         if (S > 1) {
@@ -336,9 +367,20 @@ __global__ void __launch_bounds__(kWarpsPerBlock * 32, min_blocks_per_sm(NV))
                     for (int k = 0; k < NV; ++k)
                         xv[0][k] = make_float4(acc[k].v[0], acc[k].v[VW > 1 ? 1 : 0], acc[k].v[VW > 2 ? 2 : 0],
                                                acc[k].v[VW > 3 ? 3 : 0]);
-                    const unsigned gmask = G == 32 ? kFullMask : ((1u << G) - 1u);
-                    quant_pack_group<PKB, NV, G, 1>(xv, 1, r, (int64_t)pbase[pseg] + j / PEPB, gl, gmask, 0, FV, pk.F, 0,
-                                                    pk.params, pk.params_bf16, pk.codes, (PEPB - 1 - j % PEPB) * PKB);
+                    const int R = pbase[pseg] + j / PEPB;
+                    if (R != pend_R) {
+                        flush_pending();
+                        pend_R = R, pend_n = 0;
+                        const int left = sseg[pseg + 1] - (sseg[pseg] + (j / PEPB) * PEPB);  // rows of this packed row
+                        pend_cnt = left < PEPB ? left : PEPB;
+#pragma unroll
+                        for (int k = 0; k < (PK ? NV : 1); ++k) pend_w[k] = 0u;
+                    }
+                    uint32_t w[NV];
+                    encode_row<PKB, NV, G>(xv, r, gl, FV, pk.F, pk.params, pk.params_bf16, (PEPB - 1 - j % PEPB) * PKB, w);
+#pragma unroll
+                    for (int k = 0; k < (PK ? NV : 1); ++k) pend_w[k] |= w[k];
+                    if (++pend_n == pend_cnt) flush_pending();
                 }
             }
             return;
@@ -472,6 +514,7 @@ __global__ void __launch_bounds__(kWarpsPerBlock * 32, min_blocks_per_sm(NV))
         flush_row();
         advance_row();
     }
+    if (PK) flush_pending();
     // A hub row continues in the next chunk: park the partial sum.
     if (r1 < M && e1 > rowptr[r1]) {
         if (S > 1) {
@@ -555,8 +598,14 @@ __global__ void __launch_bounds__(kWarpsPerBlock * 32)
     }
     const int pseg = find_segment(sseg, pk.P, row);
     const int j = row - sseg[pseg];
-    quant_pack_group<BITS, 4, 32, 1>(xv, 1, row, (int64_t)pbase[pseg] + j / EPB, lane, kFullMask, 0, FV, pk.F, 0, pk.params,
-                                     pk.params_bf16, pk.codes, (EPB - 1 - j % EPB) * BITS);
+    uint32_t w[4];
+    const int64_t R = (int64_t)pbase[pseg] + j / EPB;
+    quant_pack_group<BITS, 4, 32, 1>(xv, 1, row, R, lane, kFullMask, 0, FV, pk.F, 0, pk.params, pk.params_bf16, pk.codes,
+                                     (EPB - 1 - j % EPB) * BITS, w);
+    uint32_t *out = reinterpret_cast<uint32_t *>(pk.codes + R * pk.F);
+#pragma unroll
+    for (int k = 0; k < 4; ++k)
+        if (lane + 32 * k < FV && w[k] != 0u) atomicOr(out + lane + 32 * k, w[k]);
 }
 
 // Zero fill of exactly the packed rows the segments need (their number lives on the device).
@@ -807,7 +856,7 @@ extern "C" int gnnagg_spmm_quant_pack(const int64_t *rowptr, const int32_t *col,
     const int carry_ld = (F + 3) & ~3;
     PackOut pk = {codes, params, static_cast<uint32_t *>(params_bf16), seg, P, F,
                   reinterpret_cast<float *>(static_cast<char *>(scratch) + half)};
-    if (bits != 8) {  // codes are OR-ed in row by row: start from zero
+    {  // packed rows shared between chunks (and rows finished by the fix-up kernel) are OR-ed in: start from zero
         zero_codes_kernel<<<kNumSMs * 4, 256, 0, st>>>(seg, P, 8 / bits, F, codes);
         const int rc0 = check_launch("zero_codes_kernel");
         if (rc0 != GNNAGG_OK) return rc0;

@@ -299,7 +299,7 @@ def test_lean_halo_buffers_give_identical_results(cuda_lib, monkeypatch, P, F, b
     TimeRecorder(1, 1)
     results = {}
     for lean in (False, True):
-        monkeypatch.setattr(agg_mod, "FUSE_PACK", lean)  # staged run: the reference's two-step sequence
+        monkeypatch.setattr(agg_mod, "FUSE_PACK", "lean")  # staged run: SpMM into the fp32 buffer, then pack
 
         def rank_fn(rank):
             local, remote = graphgen.partition_edges(s_t, d_t, begin, rank)
