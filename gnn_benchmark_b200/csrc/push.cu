@@ -12,9 +12,18 @@
 
 namespace gnnagg {
 
+// Stores to a peer wait for NVLink; while they wait they hold the SM's path to the memory system, and every
+// other warp of that SM waits with them (measured: with store CTAs on all SMs the SpMM on the compute
+// stream made no progress until the exchange was over).  The exchange therefore runs on a FEW SMs, with
+// large CTAs that keep them to themselves, like the channels of a collective library; the rest of the GPU
+// belongs to the SpMM.  24 CTAs x 1024 threads x four rows in flight per lane group is several MB in
+// flight, far more than NVLink's bandwidth-delay product.
+constexpr int kPushCTAs = 24;
+constexpr int kPushThreads = 1024;
+
 // UNIT bytes per lane access (16 / 4 / 1); `units` of them per row; G = 2^log2g lanes per row.
 template <typename T>
-__global__ void __launch_bounds__(256)
+__global__ void __launch_bounds__(kPushThreads)
     push_rows_kernel(const uint8_t *__restrict__ src, int64_t ld_src, const int32_t *__restrict__ idx, int units,
                      int log2g, const int32_t *__restrict__ seg, int P, int first_peer, int num_peers,
                      const uint64_t *__restrict__ dst, int64_t ld_dst) {
@@ -112,17 +121,14 @@ extern "C" int gnnagg_push_rows(const void *src, int64_t ld_src, const int32_t *
     const int units = row_bytes / unit;
     int log2g = 0;
     while ((1 << log2g) < units && log2g < 5) ++log2g;
-    const int64_t groups_per_block = 256 >> log2g;
-    // two 256-thread CTAs per SM at most: a quarter of an SM's thread slots, enough to fill NVLink with four
-    // rows in flight per lane group, and room for the SpMM that runs on the compute stream meanwhile
+    const int64_t groups_per_block = kPushThreads >> log2g;
     int64_t blocks = div_up(rows_hint, groups_per_block * 4);
-    const int64_t cap = (int64_t)kNumSMs * 2;
-    if (blocks > cap) blocks = cap;
+    if (blocks > kPushCTAs) blocks = kPushCTAs;
     if (blocks < 1) blocks = 1;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     const uint8_t *s8 = static_cast<const uint8_t *>(src);
 #define GNNAGG_PUSH(T) \
-    push_rows_kernel<T><<<(unsigned)blocks, 256, 0, st>>>(s8, ld_src, idx, units, log2g, seg, P, first_peer, num_peers, dst, ld_dst)
+    push_rows_kernel<T><<<(unsigned)blocks, kPushThreads, 0, st>>>(s8, ld_src, idx, units, log2g, seg, P, first_peer, num_peers, dst, ld_dst)
     if (unit == 16) GNNAGG_PUSH(uint4);
     else if (unit == 4) GNNAGG_PUSH(uint32_t);
     else GNNAGG_PUSH(uint8_t);
