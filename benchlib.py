@@ -42,9 +42,9 @@ def spmm_compulsory_bytes(M, K, nnz, F, accumulate=False, rowptr_bytes=8):
 
 
 def spmm_kernel_source_hash():
-    """Identifies the SpMM kernel a DRAM-traffic capture belongs to: sha256 over its two source files."""
+    """Identifies the SpMM kernel a DRAM-traffic capture belongs to: sha256 over its source files."""
     h = hashlib.sha256()
-    for name in ("spmm.cu", "common.cuh"):
+    for name in ("spmm.cu", "common.cuh", "codec.cuh"):
         with open(os.path.join(ROOT, "gnn_benchmark_b200", "csrc", name), "rb") as f:
             h.update(f.read())
     return h.hexdigest()[:16]

@@ -50,6 +50,8 @@ SIGNATURES = {
     "gnnagg_dense_tf32x3_f32": (ctypes.c_int, [_vp, _i64, _vp, _i64, _vp, _i64, _i64, _i32, _i32, _vp, _i32, _vp, _sz,
                                                _vp]),
     "gnnagg_dense_status": (ctypes.c_int, [_vp, _vp]),
+    "gnnagg_dense_status_clear": (ctypes.c_int, [_vp, _vp]),
+    "gnnagg_dense_stall_test": (ctypes.c_int, [_i32, _i64]),
     "gnnagg_dense_wgrad_workspace_bytes": (_sz, [_i32, _i32]),
     "gnnagg_dense_wgrad_tf32x3_f32": (ctypes.c_int, [_vp, _i64, _vp, _i64, _i64, _i32, _i32, _vp, _i64, _vp, _sz, _vp]),
     "gnnagg_dropout_ln_relu_partial_bytes": (_sz, [_i32]),

@@ -58,7 +58,7 @@ constexpr int BIAS_BYTES = kMaxN * 4;
 constexpr int kNumBarriers = 3 * kStages + 4 + 1;
 constexpr int SMEM_BYTES = 1024 + kStages * STAGE_BYTES + EPI_BYTES + BIAS_BYTES + 256;
 constexpr int kThreads = 320;
-constexpr unsigned long long kWaitLimitNs = 1000ull * 1000ull * 1000ull;
+constexpr unsigned long long kWaitLimitNs = 1000ull * 1000ull * 1000ull;  // every launch but the stall test's
 constexpr int kStatusBytes = 256;
 
 static_assert(SMEM_BYTES <= 227 * 1024, "shared memory budget");
@@ -97,14 +97,14 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
 // Bounded wait.  Returns false when another role has raised `abort_flag` or when this wait ran out
 // of time (it then raises the flag and leaves `code` in the status word, first writer wins).
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int *abort_flag, int *status,
-                                          int code) {
+                                          int code, unsigned long long limit_ns) {
     if (mbar_try_wait(bar, parity)) return true;
     const unsigned long long t0 = globaltimer_ns();
     uint32_t n = 0;
     while (!mbar_try_wait(bar, parity)) {
         if ((++n & 31u) == 0) {
             if (*abort_flag != 0) return false;
-            if (globaltimer_ns() - t0 > kWaitLimitNs) {
+            if (globaltimer_ns() - t0 > limit_ns) {
                 *abort_flag = 1;
                 atomicCAS(status, 0, code);
                 return false;
@@ -230,6 +230,8 @@ struct GemmParams {
     int *status;
     int64_t M, ldc;
     int N, n_pad, K, accumulate, num_tiles, tma_store, b_box_rows;
+    unsigned long long wait_ns;  // limit of every wait
+    uint32_t tx_excess;          // bytes announced to the load barrier beyond what the loads deliver (stall test only)
 };
 
 enum : int {
@@ -308,12 +310,12 @@ gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
                 for (int kb = 0; kb < KB; ++kb, ++it) {
                     const int s = it % kStages;
                     const uint32_t ph = (it / kStages) & 1u;
-                    if (!mbar_wait(bar_empty(s), ph ^ 1u, abort_flag, p.status, kErrWaitEmpty)) {
+                    if (!mbar_wait(bar_empty(s), ph ^ 1u, abort_flag, p.status, kErrWaitEmpty, p.wait_ns)) {
                         ok = false;
                         break;
                     }
                     const uint32_t sa = smem_u32(stage_base + s * STAGE_BYTES);
-                    mbar_arrive_expect_tx(bar_full(s), (uint32_t)A_TILE_BYTES + 2u * b_bytes);
+                    mbar_arrive_expect_tx(bar_full(s), (uint32_t)A_TILE_BYTES + 2u * b_bytes + p.tx_excess);
                     tma_load_2d(sa, &map_a, bar_full(s), kb * BK, m0);
                     tma_load_2d(sa + 2 * A_TILE_BYTES, &map_bhi, bar_full(s), kb * BK, 0);
                     tma_load_2d(sa + 2 * A_TILE_BYTES + B_TILE_BYTES, &map_blo, bar_full(s), kb * BK, 0);
@@ -325,7 +327,7 @@ gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
                     const uint32_t j = it - back;
                     const unsigned long long t0 = globaltimer_ns();
                     while (!mbar_try_wait(bar_full(j % kStages), (j / kStages) & 1u)) {
-                        if (globaltimer_ns() - t0 > kWaitLimitNs) {
+                        if (globaltimer_ns() - t0 > p.wait_ns) {
                             atomicCAS(p.status, 0, (int)kErrDrain);
                             break;
                         }
@@ -343,7 +345,7 @@ gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
             for (int tile = blockIdx.x; tile < p.num_tiles && ok; tile += gridDim.x, ++t) {
                 const int b = (int)(t % (uint32_t)nbuf);
                 if (!mbar_wait(bar_acc_empty(b), ((t / (uint32_t)nbuf) & 1u) ^ 1u, abort_flag, p.status,
-                               kErrWaitAccFree)) {
+                               kErrWaitAccFree, p.wait_ns)) {
                     ok = false;
                     break;
                 }
@@ -354,7 +356,7 @@ gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
                 for (int kb = 0; kb < KB; ++kb, ++it) {
                     const int s = it % kStages;
                     const uint32_t ph = (it / kStages) & 1u;
-                    if (!mbar_wait(bar_full(s), ph, abort_flag, p.status, kErrWaitFull)) {
+                    if (!mbar_wait(bar_full(s), ph, abort_flag, p.status, kErrWaitFull, p.wait_ns)) {
                         ok = false;
                         break;
                     }
@@ -379,7 +381,7 @@ gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
                                         k > 0 ? 1u : first);
                     }
                     // the remainder panel is ready a little later
-                    if (!mbar_wait(bar_split(s), ph, abort_flag, p.status, kErrWaitSplit)) {
+                    if (!mbar_wait(bar_split(s), ph, abort_flag, p.status, kErrWaitSplit, p.wait_ns)) {
                         ok = false;
                         break;
                     }
@@ -400,7 +402,7 @@ gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
                 tc_commit(bar_drain);
                 const unsigned long long t0 = globaltimer_ns();
                 while (!mbar_try_wait(bar_drain, 0)) {
-                    if (globaltimer_ns() - t0 > kWaitLimitNs) {
+                    if (globaltimer_ns() - t0 > p.wait_ns) {
                         atomicCAS(p.status, 0, (int)kErrDrain);
                         break;
                     }
@@ -416,7 +418,7 @@ gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
             for (int kb = 0; kb < KB; ++kb, ++it) {
                 const int s = it % kStages;
                 const uint32_t ph = (it / kStages) & 1u;
-                if (!mbar_wait(bar_full(s), ph, abort_flag, p.status, kErrWaitFull)) {
+                if (!mbar_wait(bar_full(s), ph, abort_flag, p.status, kErrWaitFull, p.wait_ns)) {
                     ok = false;
                     break;
                 }
@@ -449,7 +451,7 @@ gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
             const int b = (int)(t % (uint32_t)nbuf);
             // warp-uniform outcome: the tensor-memory loads below are warp-collective
             if (!__all_sync(kFullMask, mbar_wait(bar_acc_full(b), (t / (uint32_t)nbuf) & 1u, abort_flag, p.status,
-                                                 kErrWaitAccFull))) {
+                                                 kErrWaitAccFull, p.wait_ns))) {
                 ok = false;
                 break;
             }
@@ -573,6 +575,8 @@ struct WgradParams {
     int64_t M;
     int N, K, n_pad, kp, blocks_per_cta, total_blocks;
     uint64_t desc;   // shared-memory descriptor without the start address
+    unsigned long long wait_ns;
+    uint32_t tx_excess;
 };
 
 __global__ void __launch_bounds__(WG_THREADS, 1)
@@ -628,13 +632,13 @@ wgrad_tf32x3_kernel(const __grid_constant__ CUtensorMap map_g, const __grid_cons
             for (; it < nkb; ++it) {
                 const int s = it % WG_STAGES;
                 const uint32_t ph = (uint32_t)(it / WG_STAGES) & 1u;
-                if (!mbar_wait(bar_empty(s), ph ^ 1u, abort_flag, p.status, kErrWaitEmpty)) {
+                if (!mbar_wait(bar_empty(s), ph ^ 1u, abort_flag, p.status, kErrWaitEmpty, p.wait_ns)) {
                     ok = false;
                     break;
                 }
                 const uint32_t sa = smem_u32(smem + s * WG_STAGE_BYTES);
                 const int row = (kb0 + it) * WG_ROWS;
-                mbar_arrive_expect_tx(bar_full(s), (uint32_t)(nb_g + nb_x) * WG_BOX_BYTES);
+                mbar_arrive_expect_tx(bar_full(s), (uint32_t)(nb_g + nb_x) * WG_BOX_BYTES + p.tx_excess);
                 for (int b = 0; b < nb_g; ++b) tma_load_2d(sa + b * WG_BOX_BYTES, &map_g, bar_full(s), 32 * b, row);
                 for (int b = 0; b < nb_x; ++b)
                     tma_load_2d(sa + 2 * WG_PANEL_BYTES + b * WG_BOX_BYTES, &map_x, bar_full(s), 32 * b, row);
@@ -644,7 +648,7 @@ wgrad_tf32x3_kernel(const __grid_constant__ CUtensorMap map_g, const __grid_cons
                     const int j = it - back;
                     const unsigned long long t0 = globaltimer_ns();
                     while (!mbar_try_wait(bar_full(j % WG_STAGES), (uint32_t)(j / WG_STAGES) & 1u)) {
-                        if (globaltimer_ns() - t0 > kWaitLimitNs) {
+                        if (globaltimer_ns() - t0 > p.wait_ns) {
                             atomicCAS(p.status, 0, (int)kErrDrain);
                             break;
                         }
@@ -665,13 +669,13 @@ wgrad_tf32x3_kernel(const __grid_constant__ CUtensorMap map_g, const __grid_cons
                     // publish the finished block and wait until warps 2-5 have moved it out
                     tc_commit(bar_acc);
                     if (!mbar_wait(bar_flushed, (uint32_t)(it / WG_FLUSH - 1) & 1u, abort_flag, p.status,
-                                   kErrWaitAccFree)) {
+                                   kErrWaitAccFree, p.wait_ns)) {
                         ok = false;
                         break;
                     }
                     tc_fence_after();
                 }
-                if (!mbar_wait(bar_full(s), ph, abort_flag, p.status, kErrWaitFull)) {
+                if (!mbar_wait(bar_full(s), ph, abort_flag, p.status, kErrWaitFull, p.wait_ns)) {
                     ok = false;
                     break;
                 }
@@ -685,7 +689,7 @@ wgrad_tf32x3_kernel(const __grid_constant__ CUtensorMap map_g, const __grid_cons
                         tc_mma_tf32(tmem_base + (uint32_t)(h * kAccStride),
                                     make_smem_desc_mn(g_raw + h * 4 * WG_BOX_BYTES + ks * 1024, p.desc),
                                     make_smem_desc_mn(x_raw + ks * 1024, p.desc), idesc, (!first || ks > 0) ? 1u : 0u);
-                if (!mbar_wait(bar_split(s), ph, abort_flag, p.status, kErrWaitSplit)) {
+                if (!mbar_wait(bar_split(s), ph, abort_flag, p.status, kErrWaitSplit, p.wait_ns)) {
                     ok = false;
                     break;
                 }
@@ -707,7 +711,7 @@ wgrad_tf32x3_kernel(const __grid_constant__ CUtensorMap map_g, const __grid_cons
                 tc_commit(bar_drain);
                 const unsigned long long t0 = globaltimer_ns();
                 while (!mbar_try_wait(bar_drain, 0)) {
-                    if (globaltimer_ns() - t0 > kWaitLimitNs) {
+                    if (globaltimer_ns() - t0 > p.wait_ns) {
                         atomicCAS(p.status, 0, (int)kErrDrain);
                         break;
                     }
@@ -721,7 +725,7 @@ wgrad_tf32x3_kernel(const __grid_constant__ CUtensorMap map_g, const __grid_cons
         float *out = p.partial + (int64_t)blockIdx.x * p.N * p.kp;
         // block `fidx` of this CTA is complete in tensor memory: add it to the partial in scratch
         auto flush = [&](int fidx) -> bool {
-            const bool ready = mbar_wait(bar_acc, (uint32_t)fidx & 1u, abort_flag, p.status, kErrWaitAccFull);
+            const bool ready = mbar_wait(bar_acc, (uint32_t)fidx & 1u, abort_flag, p.status, kErrWaitAccFull, p.wait_ns);
             if (!__all_sync(kFullMask, ready)) return false;
             tc_fence_after();
             for (int h = 0; h < halves; ++h) {
@@ -757,7 +761,7 @@ wgrad_tf32x3_kernel(const __grid_constant__ CUtensorMap map_g, const __grid_cons
             }
             const int s = it % WG_STAGES;
             const uint32_t ph = (uint32_t)(it / WG_STAGES) & 1u;
-            if (!mbar_wait(bar_full(s), ph, abort_flag, p.status, kErrWaitFull)) {
+            if (!mbar_wait(bar_full(s), ph, abort_flag, p.status, kErrWaitFull, p.wait_ns)) {
                 ok = false;
                 break;
             }
@@ -865,6 +869,14 @@ int make_map(CUtensorMap *map, const float *base, int64_t rows, int64_t cols, in
     return GNNAGG_OK;
 }
 
+// Stall test: the launches that follow announce `tx_excess` bytes that never arrive, so their first wait for a
+// load runs out after `wait_ns` and the kernel takes its abort path.  Zero in normal operation.
+struct StallTest {
+    unsigned long long wait_ns = kWaitLimitNs;
+    uint32_t tx_excess = 0;
+};
+StallTest g_stall;
+
 inline int round_up(int v, int m) { return (v + m - 1) / m * m; }
 inline size_t piece_bytes(int N, int K) { return ((size_t)N * round_up(K, 4) * 4 + 255) / 256 * 256; }
 
@@ -947,6 +959,8 @@ extern "C" int gnnagg_dense_tf32x3_f32(const float *A, int64_t lda, const float 
     p.num_tiles = (int)((M + BM - 1) / BM);
     p.tma_store = tma_store ? 1 : 0;
     p.b_box_rows = b_box_rows;
+    p.wait_ns = g_stall.wait_ns;
+    p.tx_excess = g_stall.tx_excess;
     const int grid = p.num_tiles < kNumSMs ? p.num_tiles : kNumSMs;
     gemm_tf32x3_kernel<<<grid, kThreads, SMEM_BYTES, st>>>(map_a, map_bhi, map_blo, map_c, p);
     return check_launch("gemm_tf32x3_kernel");
@@ -1012,6 +1026,8 @@ extern "C" int gnnagg_dense_wgrad_tf32x3_f32(const float *G, int64_t ldg, const 
     p.total_blocks = (int)((M + WG_ROWS - 1) / WG_ROWS);
     p.blocks_per_cta = (p.total_blocks + kNumSMs - 1) / kNumSMs;
     p.desc = smem_desc_mn_template(WG_BOX_BYTES, 512, 1);
+    p.wait_ns = g_stall.wait_ns;
+    p.tx_excess = g_stall.tx_excess;
     const int grid = (p.total_blocks + p.blocks_per_cta - 1) / p.blocks_per_cta;
     wgrad_tf32x3_kernel<<<grid, WG_THREADS, WG_SMEM_BYTES, st>>>(map_g, map_x, p);
     rc = check_launch("wgrad_tf32x3_kernel");
@@ -1029,4 +1045,19 @@ extern "C" int gnnagg_dense_status(const void *workspace, void *stream) {
     if (e == cudaSuccess) e = cudaStreamSynchronize(st);
     if (e != cudaSuccess) return fail(GNNAGG_ERR_CUDA, "dense_status: %s", cudaGetErrorString(e));
     return code;
+}
+
+extern "C" int gnnagg_dense_status_clear(void *workspace, void *stream) {
+    if (workspace == nullptr) return fail(GNNAGG_ERR_ARG, "dense_status_clear: null workspace");
+    const cudaError_t e = cudaMemsetAsync(workspace, 0, sizeof(int), static_cast<cudaStream_t>(stream));
+    if (e != cudaSuccess) return fail(GNNAGG_ERR_CUDA, "dense_status_clear: %s", cudaGetErrorString(e));
+    return GNNAGG_OK;
+}
+
+extern "C" int gnnagg_dense_stall_test(int32_t tx_excess_bytes, int64_t wait_limit_us) {
+    if (tx_excess_bytes < 0 || tx_excess_bytes > 1024 || wait_limit_us < 0 || wait_limit_us > 1000000)
+        return fail(GNNAGG_ERR_ARG, "dense_stall_test: excess must be 0..1024 bytes, the limit 0..1e6 microseconds");
+    g_stall.tx_excess = (uint32_t)tx_excess_bytes;
+    g_stall.wait_ns = wait_limit_us == 0 ? kWaitLimitNs : (unsigned long long)wait_limit_us * 1000ull;
+    return GNNAGG_OK;
 }

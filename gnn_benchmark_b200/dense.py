@@ -143,6 +143,14 @@ def check_status(device=None) -> None:
                                   _lib.lib().gnnagg_error_string(code).decode()))
 
 
+def clear_status(device=None) -> None:
+    """Reset the status words check_status reads (after a reported time-out has been handled)."""
+    for key, ws in list(_workspaces.items()):
+        if device is not None and torch.device(device).index not in (None, key[0]):
+            continue
+        _lib.check(_lib.lib().gnnagg_dense_status_clear(ws.data_ptr(), _lib.stream_ptr(ws.device)), "dense_status_clear")
+
+
 def scale_rows(x: torch.Tensor, s: torch.Tensor, divide: bool = False, out: torch.Tensor = None,
                bias: torch.Tensor = None) -> torch.Tensor:
     """out[i,:] = x[i,:] * s[i] (or / s[i]) (+ bias); s has one element per row; out=x scales in place."""

@@ -276,6 +276,14 @@ int gnnagg_dense_tf32x3_f32(const float *A, int64_t lda, const float *B, int64_t
                             int64_t M, int32_t N, int32_t K, const float *bias, int32_t accumulate,
                             void *workspace, size_t workspace_bytes, void *stream);
 int gnnagg_dense_status(const void *workspace, void *stream);
+/* Resets the status word of a workspace to 0 (stream-ordered). */
+int gnnagg_dense_status_clear(void *workspace, void *stream);
+/* Test hook (no reference counterpart): while tx_excess_bytes > 0 the dense launches of this process
+ * announce that many bytes more to their load barriers than their copies deliver, so the first wait for a
+ * load runs out after wait_limit_us microseconds and the kernel takes its give-up path (status word set,
+ * copies and MMAs drained, tensor memory freed, return).  (0, 0) restores normal operation and the normal
+ * limit of one second.  Nothing faults or hangs: the copies themselves are unchanged and complete. */
+int gnnagg_dense_stall_test(int32_t tx_excess_bytes, int64_t wait_limit_us);
 
 /* Weight gradient of the same layer, dW[N,K] = G[M,N]^T . X[M,K] (overwritten), on the tensor cores
  * with the same three-product TF32 split; replaces the `grad_out.t() @ input` products of the

@@ -161,3 +161,45 @@ def test_wgrad_rejects_unsupported():
     assert not dense.wgrad_supported(g, x)
     with pytest.raises(RuntimeError):
         dense.wgrad(g, x)
+
+
+def test_bounded_waits_give_up_and_report():
+    """The give-up path of the tensor-core kernels: with the stall hook on, a launch announces 16 bytes
+    more to its load barriers than its copies deliver, so the first wait for a load runs out (3 ms limit
+    here, one second in normal operation).  The kernel must return by itself with the code of that wait
+    in its status word (2: a consumer of the loaded tile; 5: the epilogue warps, whose wait for the
+    accumulator starts at the same moment and may run out first), and the next normal launches on the
+    same device, same workspaces included, must be correct."""
+    from gnn_benchmark_b200 import _lib, dense
+
+    lib = _lib.lib()
+    g = torch.Generator(device="cuda").manual_seed(11)
+    a = torch.randn(256, 64, device="cuda", generator=g)
+    w = torch.randn(16, 64, device="cuda", generator=g)
+    gr = torch.randn(256, 16, device="cuda", generator=g)
+    dense.linear(a, w)          # workspaces exist and are clean before the hook goes on
+    dense.wgrad(gr, a)
+    dense.check_status()
+    for call, codes in ((lambda: dense.linear(a, w), (2, 5)), (lambda: dense.wgrad(gr, a), (2,))):
+        _lib.check(lib.gnnagg_dense_stall_test(16, 3000), "stall_test")
+        try:
+            call()
+            torch.cuda.synchronize()   # the kernel returned: nothing hangs, no CUDA error
+        finally:
+            _lib.check(lib.gnnagg_dense_stall_test(0, 0), "stall_test")
+        with pytest.raises(RuntimeError, match=r"reported status (\d)") as info:
+            dense.check_status()
+        assert int(info.value.args[0].split("reported status ")[1][0]) in codes
+        dense.clear_status()
+        dense.check_status()
+    # the same shapes (same workspaces) and a full-size one, after the give-ups
+    out = dense.linear(a, w)
+    ref = a.double() @ w.double().t()
+    scale = a.abs().double() @ w.abs().double().t()
+    assert ((out.double() - ref).abs() / scale).max().item() <= 2e-6
+    dw = dense.wgrad(gr, a)
+    ref = gr.double().t() @ a.double()
+    scale = gr.abs().double().t() @ a.abs().double()
+    assert ((dw.double() - ref).abs() / scale).max().item() <= 2e-6
+    _case(1000, 256, 256, bias=True, accumulate=False, seed=5)
+    assert lib.gnnagg_dense_stall_test(-1, 0) != 0 and lib.gnnagg_dense_stall_test(16, 10**7) != 0
