@@ -1,7 +1,7 @@
 """Golden vectors of the reference's OWN Aggregator / Communicator / DistSAGE, run here on CPU.
 
-    python tests/golden/make_aggregator_golden.py [reference_root]
-    python tests/golden/make_aggregator_golden.py gcn [reference_root]   # train_gcn_config1.npz (minutes)
+    python tests/golden/make_aggregator_golden.py <reference_root>
+    python tests/golden/make_aggregator_golden.py gcn <reference_root>   # train_gcn_config1.npz (minutes)
 
 What runs: the unmodified Python of the reference (model/layers/aggregator.py, communicator.py,
 quantizer.py, data_manager/*, model/ops/spmm_kernel.py, model/DistSAGE.py, model/layers/sageconv.py)
@@ -464,7 +464,9 @@ TRAIN_CFGS = [
 
 
 def main():
-    ref_root = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+    if len(sys.argv) < 2:
+        sys.exit("usage: make_aggregator_golden.py <reference_root> | gcn <reference_root>")
+    ref_root = sys.argv[1]
     port = 29610
     for case in AGGR_CASES:
         P = AGGR_P[case[0]]
@@ -478,7 +480,9 @@ def main():
 
 
 def main_gcn():
-    ref_root = sys.argv[2] if len(sys.argv) > 2 else "/root/reference"
+    if len(sys.argv) < 3:
+        sys.exit("usage: make_aggregator_golden.py gcn <reference_root>")
+    ref_root = sys.argv[2]
     mp.spawn(gcn_config1_worker, args=(2, 29690, GCN_CONFIG1, ref_root, HERE), nprocs=2, join=True)
     print("wrote train_gcn_config1.npz")
 
