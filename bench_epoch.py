@@ -70,6 +70,8 @@ def make_parser():
                          "device-time table to this file (a breakdown, never a timing)")
     ap.add_argument("--transport", default="all_to_all", choices=["all_to_all", "push"],
                     help="halo exchange: one NCCL collective per aggregation, or rows stored straight into the receivers' buffers")
+    ap.add_argument("--push-engine", default="kernel", choices=["kernel", "copy"],
+                    help="push transport: rows moved by the store kernel, or by device-to-device copies")
     return ap
 
 
@@ -78,7 +80,8 @@ def run(args):
     is already there (bench.py's multi-GPU leg calls this in-process) or starts one under torchrun."""
     dense.MODE = args.dense
     multi = int(os.environ.get("WORLD_SIZE", "1")) > 1
-    comm = Communicator(args.bits, is_async=True, transport=args.transport if multi else "all_to_all")
+    comm = Communicator(args.bits, is_async=True, transport=args.transport if multi else "all_to_all",
+                        push_engine=args.push_engine)
     if "RANK" in os.environ:
         rank, world = comm.init_dist_group("nccl")
     else:

@@ -159,7 +159,7 @@ def main_halo(argv):
     from gnn_benchmark_b200 import SparseTensor, graphgen
     from gnn_benchmark_b200.aggregator import gather_rows
     from gnn_benchmark_b200.data_manager.DataLoader import _scatter_matrix
-    from gnn_benchmark_b200.spmm_kernel import (SPMM_backward, SPMM_backward_quant_pack, SPMM_forward_packed)
+    from gnn_benchmark_b200.spmm_kernel import (SPMM_backward, SPMM_backward_quant_pack, SPMM_forward, SPMM_forward_packed)
 
     ap = argparse.ArgumentParser()
     ap.add_argument("--parts", type=int, default=2)
@@ -218,6 +218,14 @@ def main_halo(argv):
         line["backward_spmm_then_pack_ms"] = timed(two_calls)
         line["backward_spmm_pack_fused_ms"] = timed(lambda: SPMM_backward_quant_pack(A, x, codes, params, pb, seg, P, bits))
         line["scatter_fused_unpack_ms"] = timed(lambda: SPMM_forward_packed(S, codes, pb, seg, P, bits, out))
+
+        # the two-step forms the fused-unpack kernels replace: unpack into the fp32 halo buffer, then the SpMM
+        def unpack_then(mat):
+            q.dequantize_intX_to_fp32(codes, buf, params, seg, params_bf16=pb)
+            SPMM_forward(mat, buf, out, accumulate=True)
+
+        line["unpack_then_remote_spmm_ms"] = timed(lambda: unpack_then(A))
+        line["unpack_then_scatter_ms"] = timed(lambda: unpack_then(S))
         line["gather_rows_ms"] = timed(lambda: gather_rows(x, idx, buf))
         print(json.dumps(line), flush=True)
 

@@ -246,7 +246,7 @@ def _epoch_legs(args, world):
     ]
     for name, argv in runs:
         try:
-            r = bench_epoch.run(bench_epoch.make_parser().parse_args(argv + ["--transport", transport]))
+            r = bench_epoch.run(bench_epoch.make_parser().parse_args(argv + ["--transport", transport, "--push-engine", args.push_engine]))
             if r is not None:
                 legs[name] = {"epoch_s": r["value"], "aggregated_edges_per_s": r["aggregated_edges_per_s"],
                               "aggregation_passes_per_step": r["aggregation_passes_per_step"], "config": r["config"],
@@ -261,12 +261,12 @@ def _epoch_legs(args, world):
 def run_multi_gpu(args):
     import benchlib as bench
     from gnn_benchmark_b200 import Communicator, Quantizer_for_all_procs, TimeRecorder, graphgen
-    from gnn_benchmark_b200.aggregator import Aggregator
+    from gnn_benchmark_b200.aggregator import Aggregator, gather_rows
     from gnn_benchmark_b200.data_manager.DataLoader import build_graph
 
     num_bits, is_pre = args.bits, bool(args.pre)
     transport = "push" if args.exchange == "pipelined" else "all_to_all"
-    comm = Communicator(num_bits, is_async=True, transport=transport, push_groups=3)
+    comm = Communicator(num_bits, is_async=True, transport=transport, push_groups=3, push_engine=args.push_engine)
     rank, world = comm.init_dist_group("nccl")
     device = torch.device("cuda", torch.cuda.current_device())
     TimeRecorder(1, 1, enabled=False)
@@ -353,8 +353,12 @@ def run_multi_gpu(args):
             graph.comm_buf.resize_buffer(graph.comm_splits, F, 32)
 
             def exchange_only():
-                cur = torch.cuda.current_stream()
-                plan.push("forward", "rows", X[F], 4 * F, (rank + 1) % world, world - 1, graph.idx_nodes_send_to_others_i32)
+                if plan.peers.engine == "copy":
+                    gather_rows(X[F], graph.idx_nodes_send_to_others_i32, graph.comm_buf.send_buf)
+                    plan.push("forward", "rows", graph.comm_buf.send_buf, 4 * F, (rank + 1) % world, world - 1)
+                else:
+                    plan.push("forward", "rows", X[F], 4 * F, (rank + 1) % world, world - 1,
+                              graph.idx_nodes_send_to_others_i32)
                 plan.peers.signal().wait()
 
             exchange_only()
@@ -365,7 +369,8 @@ def run_multi_gpu(args):
             gbs = float(sent.item()) / (ms / 1e3) / 1e9
             nv = {"exchange_ms": ms, "bytes_per_rank_per_direction": int(sent.item()), "achieved_gbs": gbs,
                   "frac_of_measured_770": gbs / 770.0, "frac_of_nominal_900": gbs / 900.0, "F": F,
-                  "what": "gather + store of all halo rows into the peers' buffers + signal, nothing else running"}
+                  "what": "gather + store of all halo rows into the peers' buffers + signal, nothing else running",
+                  "engine": plan.peers.engine}
 
     variants = {}
     if world > 1 and num_bits == 32:
@@ -375,6 +380,16 @@ def run_multi_gpu(args):
                                          "quantised mode); pack fused into the gather / the transposed SpMM, unpack fused "
                                          "into the receive-side SpMM"}
     if plan is not None:
+        other = "copy" if plan.peers.engine == "kernel" else "kernel"
+        mine, plan.peers.engine = plan.peers.engine, other
+        ms_o = time_variant(num_bits)
+        ms_o2 = time_variant(2) if num_bits == 32 else None
+        plan.peers.engine = mine
+        variants["push_engine_" + other] = {
+            "ms_per_step": ms_o, "value": edges_per_step / (ms_o / 1e3), "unit": "edges/s",
+            "int2_halo_ms_per_step": ms_o2,
+            "note": ("rows gathered into the send buffer, then one device-to-device copy per peer on the copy engines"
+                     if other == "copy" else "rows stored into the peers' buffers by the store kernel, gather fused in")}
         ms_a2a = time_variant(num_bits, exchange="all_to_all")
         variants["nccl_all_to_all"] = {"ms_per_step": ms_a2a, "value": edges_per_step / (ms_a2a / 1e3), "unit": "edges/s",
                                        "note": "same graph and kernels, one NCCL all-to-all per aggregation instead of "
@@ -390,8 +405,10 @@ def run_multi_gpu(args):
         cfg = bench.workload_config(world, args.scale, widths)
         cfg.update({"rows_per_gpu": n, "nnz_total": int(nnz_total), "partitions": world,
                     "halo_rows_sent_total": halo_rows, "halo": f"{num_bits}-bit" + (" pre/post" if is_pre else ""),
-                    "exchange": ("rows stored straight into the receivers' buffers (gnnagg_push_rows), peers served in "
-                                 f"{min(comm.push_groups, world - 1)} groups, each aggregated on arrival"
+                    "exchange": (("rows stored straight into the receivers' buffers (gnnagg_push_rows)"
+                                  if comm.push_engine == "kernel" else
+                                  "rows copied straight into the receivers' buffers (gnnagg_push_block, copy engines)")
+                                 + f", peers served in {min(comm.push_groups, world - 1)} groups, each aggregated on arrival"
                                  if transport == "push" else "one NCCL all-to-all per aggregation"),
                     "setup_s": round(setup_s, 1), "parallelism": f"1-D vertex partition x{world}"})
         by = sum(bench.spmm_algorithmic_bytes(n, nnz, F) for F in widths) * 2

@@ -35,6 +35,7 @@ SIGNATURES = {
     "gnnagg_csr_to_csc": (ctypes.c_int, [_vp, _vp, _vp, _i64, _i64, _i64, _vp, _vp, _vp, _vp, _sz, _vp]),
     "gnnagg_csr_validate": (ctypes.c_int, [_vp, _vp, _i64, _i64, _i64, _vp, _vp]),
     "gnnagg_gather_rows_f32": (ctypes.c_int, [_vp, _i64, _vp, _i64, _i32, _vp, _i64, _vp]),
+    "gnnagg_push_block": (ctypes.c_int, [_vp, _vp, _sz, _vp]),
     "gnnagg_push_rows": (ctypes.c_int, [_vp, _i64, _vp, _i32, _vp, _i32, _i32, _i32, _vp, _i64, _i64, _vp]),
     "gnnagg_scale_rows_f32": (ctypes.c_int, [_vp, _i64, _vp, _i64, _i32, _i32, _vp, _vp, _i64, _vp]),
     "gnnagg_quant_pack_rows": (ctypes.c_int, [_vp, _i64, _vp, _i32, _vp, _i32, _i64, _i32, _i32, _vp, _vp, _vp, _vp]),

@@ -5,6 +5,8 @@ the kernel `gnnagg_push_rows` stores them straight into the receivers' buffers (
 side stream, and a 4-byte all-reduce queued behind the stores tells every rank that its rows are in.
 
   forward   [free?] push(x[idx] | packed codes+params | pre-aggregated rows) -> signal        (side stream)
+            (push = the store kernel, or with Communicator(push_engine="copy") one device-to-device copy per
+            peer on the copy engines, after a gather into the send buffer where the rows are not contiguous)
             local SpMM                                                                        (compute)
             wait signal -> remote / post SpMM -> raise "free" for the next forward            (compute)
   backward  transposed receive-side SpMM (packs in its epilogue when the halo is packed) ->
@@ -73,7 +75,7 @@ def _push(plan, direction, cur, jobs, groups):
 
 def forward(graph, x, feat_len, num_bits, is_pre_delay, packed, world_size, rec):
     from .aggregator import (_fuse_pack as fuse_pack, _prefix as prefix, _remote_parts as remote_parts,
-                             _resize as resize, _send_idx as send_idx)
+                             _resize as resize, _send_idx as send_idx, gather_rows)
 
     plan = graph.push_plan
     P, r = world_size, plan.rank
@@ -102,6 +104,11 @@ def forward(graph, x, feat_len, num_bits, is_pre_delay, packed, world_size, rec)
         jobs = [("codes", q.quantized_send_data_buf, feat_len, None), ("params", q.quantized_send_params_buf_bf16, 4, None)]
     elif is_pre_delay:
         SPMM_forward(graph.adj_t_pre_post_aggr_to, x, graph.comm_buf.send_buf, accumulate=False)
+        jobs = [("rows", graph.comm_buf.send_buf, 4 * feat_len, None)]
+    elif plan.peers.engine == "copy":
+        # copy engines move contiguous blocks: gather the rows into the send buffer first (after the last
+        # backward's rows, which peers stored there, have been consumed: stream order on this rank)
+        gather_rows(x, send_idx(graph), graph.comm_buf.send_buf)
         jobs = [("rows", graph.comm_buf.send_buf, 4 * feat_len, None)]
     else:
         jobs = [("rows", x, 4 * feat_len, send_idx(graph))]  # the gather is part of the store kernel

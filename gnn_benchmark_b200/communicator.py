@@ -39,15 +39,21 @@ class Communicator(object):
     ctx = None
 
     def __init__(self, num_bits=32, is_async=True, use_barrier=False, pipeline_peers=False, transport="all_to_all",
-                 push_groups=3) -> None:
+                 push_groups=3, push_engine="kernel") -> None:
         """transport (an addition): "all_to_all" -- the reference's exchange, one collective per aggregation
         (NCCL here); "push" -- rows are stored straight into the receivers' buffers over NVLink by the
         kernel that gathers / produces them (peer.py, aggregator_push.py; one node, NCCL process group).
         push_groups: with the fp32 halo on the plain path the peers are served in this many groups, the
         receive-side SpMM of one group overlapping the stores of the next; 1 keeps the ascending-peer
-        summation order of the all-to-all path."""
+        summation order of the all-to-all path.
+        push_engine: "kernel" -- the store kernel moves the rows (gather fused in, a few SMs busy for the
+        length of the exchange); "copy" -- rows are gathered into the send buffer when they are not already
+        contiguous and every peer's block travels as one device-to-device copy on the copy engines (no SM)."""
         if transport not in ("all_to_all", "push"):
             raise ValueError("transport must be 'all_to_all' or 'push'")
+        if push_engine not in ("kernel", "copy"):
+            raise ValueError("push_engine must be 'kernel' or 'copy'")
+        self.push_engine = push_engine
         self.num_bits = num_bits
         self.is_async = is_async
         self.use_barrier = use_barrier
@@ -88,7 +94,7 @@ class Communicator(object):
         if self._peers is None:
             from .peer import NcclPeers
 
-            self._peers = NcclPeers(torch.device("cuda", torch.cuda.current_device()))
+            self._peers = NcclPeers(torch.device("cuda", torch.cuda.current_device()), engine=self.push_engine)
         return self._peers
 
     def push_stream(self, device):

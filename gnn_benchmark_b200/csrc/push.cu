@@ -135,3 +135,15 @@ extern "C" int gnnagg_push_rows(const void *src, int64_t ld_src, const int32_t *
 #undef GNNAGG_PUSH
     return check_launch("push_rows_kernel");
 }
+
+// One peer's block as ONE asynchronous device-to-device copy: the driver runs it on a copy engine, so the
+// block crosses NVLink without occupying an SM (the store kernel above keeps 24 SMs busy for the length
+// of the exchange).  For blocks that are contiguous on both sides -- everything but the forward fp32 halo
+// of the plain plan, whose rows must be gathered first.
+extern "C" int gnnagg_push_block(const void *src, void *dst, size_t bytes, void *stream) {
+    if (bytes == 0) return GNNAGG_OK;
+    if (src == nullptr || dst == nullptr) return fail(GNNAGG_ERR_ARG, "push_block: null pointer");
+    const cudaError_t e = cudaMemcpyAsync(dst, src, bytes, cudaMemcpyDeviceToDevice, static_cast<cudaStream_t>(stream));
+    if (e != cudaSuccess) return fail(GNNAGG_ERR_CUDA, "push_block: %s", cudaGetErrorString(e));
+    return GNNAGG_OK;
+}

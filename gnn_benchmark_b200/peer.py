@@ -38,8 +38,9 @@ def _prefix_i32(counts, device) -> torch.Tensor:
 class NcclPeers(object):
     """One process per GPU on one node, NCCL process group initialised."""
 
-    def __init__(self, device):
+    def __init__(self, device, engine="kernel"):
         self.device = torch.device(device)
+        self.engine = engine  # "kernel": store kernel (gather fused in); "copy": device-to-device copies per peer
         self.rank, self.world = dist.get_rank(), dist.get_world_size()
         # signals travel on a communicator of their own: they never queue behind a large collective of
         # the default group (e.g. a gradient all-reduce) and keep their own issue order
@@ -120,9 +121,10 @@ class PushPlan(object):
         t["backward", "codes"] = ("q_send_data", [before(send_all[p], r, True) for p in range(P)])
         t["forward", "params"] = ("q_recv_params", [before(recv_all[p], r, False) for p in range(P)])
         t["backward", "params"] = ("q_send_params", [before(send_all[p], r, False) for p in range(P)])
-        self._tables = {}
+        self._tables, self._host_tables = {}, {}
         for key, (region, offs) in t.items():
             if region in self.offset:
+                self._host_tables[key] = ([self.bases[p] + self.offset[region] for p in range(P)], offs)
                 base = torch.tensor([self.bases[p] + self.offset[region] for p in range(P)], dtype=torch.int64, device=dev)
                 self._tables[key] = (base, torch.tensor(offs, dtype=torch.int64, device=dev))
         # send-list prefixes on the device: forward sends follow send_splits, backward sends recv_splits
@@ -138,6 +140,7 @@ class PushPlan(object):
         self.counts["forward", "params"] = self.counts["forward", "rows"]
         self.counts["backward", "params"] = self.counts["backward", "rows"]
         self._dst_cache = {}
+        self.src_offset = {k: [0] + [sum(v[:i + 1]) for i in range(P)] for k, v in self.counts.items()}  # host prefixes
         self.free = {"forward": None, "backward": None}  # last "receivers are done with this buffer" signal
 
     def region(self, name: str, shape, dtype) -> torch.Tensor:
@@ -167,6 +170,18 @@ class PushPlan(object):
         if rows == 0:
             return
         ld_src = src.stride(0) * src.element_size()
+        if idx is None and ld_src == row_bytes and self.peers.engine == "copy":
+            # contiguous on both sides: one device-to-device copy per peer, on the copy engines
+            base, offs = self._host_tables[direction, payload]
+            start = self.src_offset[direction, payload]
+            lib, stream = _lib.lib(), _lib.stream_ptr(src.device)
+            for j in range(num_peers):
+                p = (first_peer + j) % self.P
+                if counts[p]:
+                    rc = lib.gnnagg_push_block(src.data_ptr() + start[p] * row_bytes, base[p] + offs[p] * row_bytes,
+                                               counts[p] * row_bytes, stream)
+                    _lib.check(rc, "push_block")
+            return
         dst = self.dst_table(direction, payload, row_bytes)
         rc = _lib.lib().gnnagg_push_rows(src.data_ptr(), ld_src, _lib.ptr(idx), row_bytes,
                                          self.seg[direction, payload].data_ptr(), self.P, first_peer, num_peers,

@@ -159,6 +159,12 @@ int gnnagg_gather_rows_f32(const float *X, int64_t ldx, const int32_t *idx, int6
 int gnnagg_push_rows(const void *src, int64_t ld_src, const int32_t *idx, int32_t row_bytes, const int32_t *seg,
                      int32_t P, int32_t first_peer, int32_t num_peers, const uint64_t *dst, int64_t ld_dst,
                      int64_t rows_hint, void *stream);
+/* The same exchange for a block that is contiguous on both sides (the send buffer's rows for one peer,
+ * packed codes, bf16 parameters): one asynchronous device-to-device copy of `bytes` bytes from src to
+ * dst (an address inside the peer's receive buffer, valid on this device), queued on `stream`.  The
+ * driver runs it on a copy engine: no SM is occupied while the block crosses NVLink.  Replaces the same
+ * all_to_all_single message (communicator.py:101, :307-311). */
+int gnnagg_push_block(const void *src, void *dst, size_t bytes, void *stream);
 
 /* Y[i,:] = X[i,:] * s[i] (divide == 0) or X[i,:] / s[i] (divide == 1, IEEE quotient), plus bias[F] when
  * bias != NULL; Y may alias X.  Replaces the broadcast `out /= graph.in_degrees` of the layer

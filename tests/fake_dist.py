@@ -33,6 +33,7 @@ class ThreadPeers:
 
     def __init__(self, world: "FakeWorld", rank: int):
         self.w, self.rank, self.world = world, rank, world.P
+        self.engine = getattr(world, "push_engine", "kernel")
         self._bufs = []
 
     def gather_objects(self, obj):
@@ -55,9 +56,10 @@ class ThreadPeers:
 
 
 class FakeWorld:
-    def __init__(self, world_size: int):
+    def __init__(self, world_size: int, push_engine: str = "kernel"):
         self._objs = [None] * world_size
         self.P = world_size
+        self.push_engine = push_engine
         self._barrier = threading.Barrier(world_size)
         self._slots = [None] * world_size
         self._local = threading.local()

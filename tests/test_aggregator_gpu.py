@@ -379,13 +379,15 @@ def test_config3_downscaled_codes_bit_exact(cuda_lib, monkeypatch, bits):
         assert np.abs(out - want[b0:b1]).max() <= (2.5 if bits == 2 else 0.05) * max(1.0, scale_abs[b0:b1].max())
 
 
+@pytest.mark.parametrize("engine", ["kernel", "copy"])
 @pytest.mark.parametrize("P,bits,is_pre,F,groups", [
     (2, 32, False, 128, 1), (4, 32, False, 256, 1), (4, 32, False, 100, 3), (5, 32, False, 32, 2), (8, 32, False, 128, 3),
     (3, 32, True, 128, 1), (2, 2, False, 128, 1), (4, 2, False, 256, 3), (3, 2, True, 128, 1), (3, 8, False, 64, 1),
 ])
-def test_push_transport_matches_all_to_all(cuda_lib, P, bits, is_pre, F, groups):
+def test_push_transport_matches_all_to_all(cuda_lib, P, bits, is_pre, F, groups, engine):
     """Communicator(transport="push"): halo rows stored straight into the receivers' buffers by
-    gnnagg_push_rows (gathered on the way), signals instead of a collective.  With one group of peers the
+    gnnagg_push_rows (gathered on the way) or, with push_engine="copy", moved there block by block with
+    device-to-device copies (gnnagg_push_block); signals instead of a collective.  With one group of peers the
     outputs, gradients and wire codes equal the all-to-all path bit for bit; with several groups (fp32 halo,
     plain path) the peers' contributions are added in arrival order: 1e-5 of the summed magnitudes.  Two
     forward + backward rounds, so that buffers are reused behind their "free" signals."""
@@ -404,12 +406,13 @@ def test_push_transport_matches_all_to_all(cuda_lib, P, bits, is_pre, F, groups)
     TimeRecorder(1, 1)
     results = {}
     for transport in ("all_to_all", "push"):
-        Communicator(bits, is_async=True, transport=transport, push_groups=groups)
+        Communicator(bits, is_async=True, transport=transport, push_groups=groups, push_engine=engine)
 
         def rank_fn(rank):
             local, remote = graphgen.partition_edges(s_t, d_t, begin, rank)
             graph = build_graph(local, remote, begin, rank, P, F, bits, is_pre, device="cuda")
             assert (graph.push_plan is not None) == (transport == "push")
+            assert transport != "push" or graph.push_plan.peers.engine == engine
             b0, b1 = int(begin[rank]), int(begin[rank + 1])
             got = []
             for k in range(2):
@@ -422,7 +425,7 @@ def test_push_transport_matches_all_to_all(cuda_lib, P, bits, is_pre, F, groups)
                     got += [q.quantized_recv_data_buf.cpu().numpy(), q.quantized_send_data_buf.cpu().numpy()]
             return got
 
-        results[transport] = FakeWorld(P).run(rank_fn)
+        results[transport] = FakeWorld(P, push_engine=engine).run(rank_fn)
     for r in range(P):
         for i, (a, b) in enumerate(zip(results["all_to_all"][r], results["push"][r])):
             if groups == 1 or a.dtype == np.uint8:
