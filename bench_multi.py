@@ -380,16 +380,21 @@ def run_multi_gpu(args):
                                          "quantised mode); pack fused into the gather / the transposed SpMM, unpack fused "
                                          "into the receive-side SpMM"}
     if plan is not None:
-        other = "copy" if plan.peers.engine == "kernel" else "kernel"
-        mine, plan.peers.engine = plan.peers.engine, other
-        ms_o = time_variant(num_bits)
-        ms_o2 = time_variant(2) if num_bits == 32 else None
+        notes = {"copy": "rows gathered into the send buffer where needed, then one device-to-device copy per peer on "
+                         "the copy engines",
+                 "kernel": "rows stored into the peers' buffers by the store kernel, gather fused in",
+                 "auto": "forward: store kernel with the gather fused in; backward (blocks already contiguous): one "
+                         "device-to-device copy per peer"}
+        mine = plan.peers.engine
+        for other in ("kernel", "copy", "auto"):
+            if other == mine:
+                continue
+            plan.peers.engine = other
+            ms_o = time_variant(num_bits)
+            ms_o2 = time_variant(2) if num_bits == 32 else None
+            variants["push_engine_" + other] = {"ms_per_step": ms_o, "value": edges_per_step / (ms_o / 1e3),
+                                                "unit": "edges/s", "int2_halo_ms_per_step": ms_o2, "note": notes[other]}
         plan.peers.engine = mine
-        variants["push_engine_" + other] = {
-            "ms_per_step": ms_o, "value": edges_per_step / (ms_o / 1e3), "unit": "edges/s",
-            "int2_halo_ms_per_step": ms_o2,
-            "note": ("rows gathered into the send buffer, then one device-to-device copy per peer on the copy engines"
-                     if other == "copy" else "rows stored into the peers' buffers by the store kernel, gather fused in")}
         ms_a2a = time_variant(num_bits, exchange="all_to_all")
         variants["nccl_all_to_all"] = {"ms_per_step": ms_a2a, "value": edges_per_step / (ms_a2a / 1e3), "unit": "edges/s",
                                        "note": "same graph and kernels, one NCCL all-to-all per aggregation instead of "

@@ -48,11 +48,13 @@ class Communicator(object):
         summation order of the all-to-all path.
         push_engine: "kernel" -- the store kernel moves the rows (gather fused in, a few SMs busy for the
         length of the exchange); "copy" -- rows are gathered into the send buffer when they are not already
-        contiguous and every peer's block travels as one device-to-device copy on the copy engines (no SM)."""
+        contiguous and every peer's block travels as one device-to-device copy on the copy engines (no SM);
+        "auto" -- copies for blocks that are contiguous as they are (backward, packed halo, pre/post), the store
+        kernel where the rows must be gathered (forward, plain plan, fp32)."""
         if transport not in ("all_to_all", "push"):
             raise ValueError("transport must be 'all_to_all' or 'push'")
-        if push_engine not in ("kernel", "copy"):
-            raise ValueError("push_engine must be 'kernel' or 'copy'")
+        if push_engine not in ("kernel", "copy", "auto"):
+            raise ValueError("push_engine must be 'kernel', 'copy' or 'auto'")
         self.push_engine = push_engine
         self.num_bits = num_bits
         self.is_async = is_async

@@ -40,7 +40,10 @@ class NcclPeers(object):
 
     def __init__(self, device, engine="kernel"):
         self.device = torch.device(device)
-        self.engine = engine  # "kernel": store kernel (gather fused in); "copy": device-to-device copies per peer
+        # "kernel": the store kernel moves everything (gather fused in); "copy": device-to-device copies per
+        # peer, rows gathered into the send buffer first where needed; "auto": copies for blocks that are
+        # contiguous as they are, the store kernel where a gather is needed
+        self.engine = engine
         self.rank, self.world = dist.get_rank(), dist.get_world_size()
         # signals travel on a communicator of their own: they never queue behind a large collective of
         # the default group (e.g. a gradient all-reduce) and keep their own issue order
@@ -170,7 +173,7 @@ class PushPlan(object):
         if rows == 0:
             return
         ld_src = src.stride(0) * src.element_size()
-        if idx is None and ld_src == row_bytes and self.peers.engine == "copy":
+        if idx is None and ld_src == row_bytes and self.peers.engine in ("copy", "auto"):
             # contiguous on both sides: one device-to-device copy per peer, on the copy engines
             base, offs = self._host_tables[direction, payload]
             start = self.src_offset[direction, payload]

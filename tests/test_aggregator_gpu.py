@@ -379,7 +379,7 @@ def test_config3_downscaled_codes_bit_exact(cuda_lib, monkeypatch, bits):
         assert np.abs(out - want[b0:b1]).max() <= (2.5 if bits == 2 else 0.05) * max(1.0, scale_abs[b0:b1].max())
 
 
-@pytest.mark.parametrize("engine", ["kernel", "copy"])
+@pytest.mark.parametrize("engine", ["kernel", "copy", "auto"])
 @pytest.mark.parametrize("P,bits,is_pre,F,groups", [
     (2, 32, False, 128, 1), (4, 32, False, 256, 1), (4, 32, False, 100, 3), (5, 32, False, 32, 2), (8, 32, False, 128, 3),
     (3, 32, True, 128, 1), (2, 2, False, 128, 1), (4, 2, False, 256, 3), (3, 2, True, 128, 1), (3, 8, False, 64, 1),
