@@ -32,12 +32,24 @@ from .time_recorder import TimeRecorder
 # into the fp32 halo buffer first (same result bit for bit; the fp32 buffer is then left untouched).
 # Set to False to get the reference's two-step sequence, e.g. to inspect comm_buf.recv_buf.
 FUSE_UNPACK = True
+# ... in forward only from this width on: below it the unpack kernel followed by the fp32 SpMM is the faster
+# pair (1.9 M halo rows, 65 M nonzeros, 2 bits: 2.11 vs 2.58 ms at 32 columns, 3.57 vs 3.81 at 128, 7.50 vs 6.88
+# at 256; the packed SpMM pays a slot -> (row, shift, parameters) lookup per nonzero, which wide rows amortise).
+# The backward scatter is fused at every width (fused is never slower there), and so is everything when the
+# fp32 halo buffers do not exist (lean halo buffers).
+FUSE_UNPACK_MIN_WIDTH = 192
 # Packed halo modes: quantise + pack as the epilogue of the SpMM that produces the rows to send (forward:
 # pre-aggregation; backward: transposed receive-side matrix), so comm_buf.send_buf / recv_buf are never
 # written.  "lean": only where those fp32 buffers do not exist (lean halo buffers) -- with the buffers there,
 # SpMM into them followed by the pack kernel is the faster pair below 256 columns (the encoder inside the
 # SpMM costs instruction-cache misses); True: always; False: never (the reference's two-step sequence).
 FUSE_PACK = "lean"
+
+
+def _fuse_unpack_forward(graph, feat_len: int) -> bool:
+    if not FUSE_UNPACK or feat_len % 4 != 0:
+        return False
+    return feat_len >= FUSE_UNPACK_MIN_WIDTH or bool(getattr(graph.comm_buf, "lean", False))
 
 
 def _fuse_pack(graph) -> bool:
@@ -216,7 +228,7 @@ class Aggregator(torch.autograd.Function):
             return out
 
         num_recv_nodes = sum(graph.comm_splits.recv_splits) if world_size > 1 else 0
-        fused = packed and FUSE_UNPACK and feat_len % 4 == 0
+        fused = packed and _fuse_unpack_forward(graph, feat_len)
         if packed and num_recv_nodes != 0 and not fused:
             t = rec.start() if rec else None
             q = graph.comm_buf_for_quantization

@@ -74,8 +74,8 @@ def _push(plan, direction, cur, jobs, groups):
 
 
 def forward(graph, x, feat_len, num_bits, is_pre_delay, packed, world_size, rec):
-    from .aggregator import (_fuse_pack as fuse_pack, _prefix as prefix, _remote_parts as remote_parts,
-                             _resize as resize, _send_idx as send_idx, gather_rows)
+    from .aggregator import (_fuse_pack as fuse_pack, _fuse_unpack_forward as fuse_unpack_forward, _prefix as prefix,
+                             _remote_parts as remote_parts, _resize as resize, _send_idx as send_idx, gather_rows)
 
     plan = graph.push_plan
     P, r = world_size, plan.rank
@@ -128,9 +128,14 @@ def forward(graph, x, feat_len, num_bits, is_pre_delay, packed, world_size, rec)
     if len(groups) == 1:
         signals[0].wait()
         if have_rows:
-            if packed:
+            if packed and fuse_unpack_forward(graph, feat_len):
                 SPMM_forward_packed(adj, q.quantized_recv_data_buf, q.quantized_recv_params_buf_bf16,
                                     q.dequantized_work_range_per_proc, P, _bits(), out)
+            elif packed:  # narrow rows: unpack into the fp32 halo buffer, then the plain SpMM
+                Quantizer_for_all_procs.ctx.dequantize_intX_to_fp32(
+                    q.quantized_recv_data_buf, graph.comm_buf.recv_buf, q.quantized_recv_params_buf_fp32,
+                    q.dequantized_work_range_per_proc, params_bf16=q.quantized_recv_params_buf_bf16)
+                SPMM_forward(adj, graph.comm_buf.recv_buf, out)
             else:
                 SPMM_forward(adj, graph.comm_buf.recv_buf, out)
     else:

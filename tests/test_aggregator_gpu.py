@@ -76,6 +76,7 @@ def test_aggregator_forward_backward(cuda_lib, monkeypatch, fuse, P, num_bits, i
 
     import gnn_benchmark_b200.aggregator as agg_mod
     monkeypatch.setattr(agg_mod, "FUSE_UNPACK", fuse)
+    monkeypatch.setattr(agg_mod, "FUSE_UNPACK_MIN_WIDTH", 0)  # the fused forward at every width
     Communicator(num_bits, is_async=True)
     Quantizer_for_all_procs(P, num_bits)
     TimeRecorder(1, 1, enabled=False)
@@ -332,6 +333,7 @@ def test_config3_downscaled_codes_bit_exact(cuda_lib, monkeypatch, bits):
     from gnn_benchmark_b200.data_manager.DataLoader import build_graph
 
     monkeypatch.setattr(agg_mod, "FUSE_UNPACK", True)
+    monkeypatch.setattr(agg_mod, "FUSE_UNPACK_MIN_WIDTH", 0)
     P, F, scale = 8, 256, 16
     n = 1 << scale
     s_t, d_t = graphgen.rmat_edges(scale, 16, seed=20261128, device="cuda")

@@ -44,6 +44,7 @@ def test_aggregator_against_reference_run(cuda_lib, monkeypatch, fuse, path):
     s_t, d_t = torch.from_numpy(g["src"]).cuda(), torch.from_numpy(g["dst"]).cuda()
     import gnn_benchmark_b200.aggregator as agg_mod
     monkeypatch.setattr(agg_mod, "FUSE_UNPACK", fuse)
+    monkeypatch.setattr(agg_mod, "FUSE_UNPACK_MIN_WIDTH", 0)  # the fused forward at every width
     Communicator(bits, is_async=True)
     Quantizer_for_all_procs(P, bits)
     TimeRecorder(1, 1)
