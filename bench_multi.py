@@ -239,7 +239,8 @@ def _epoch_legs(args, world):
         ("config4_sage_fp32", ["--model", "sage", "--nodes", "2450000", "--edges", "61900000", "--in-channels", "100",
                                "--hidden", "256", "--out-channels", "47", "--train-frac", "0.08", "--bits", "32", "--epochs", "5"]),
         ("config4_sage_int2", ["--model", "sage", "--nodes", "2450000", "--edges", "61900000", "--in-channels", "100",
-                               "--hidden", "256", "--out-channels", "47", "--train-frac", "0.08", "--bits", "2", "--epochs", "5"]),
+                               "--hidden", "256", "--out-channels", "47", "--train-frac", "0.08", "--bits", "2", "--epochs", "5",
+                               "--lean-halo", "0"]),  # memory is no issue here: keep the fp32 halo buffers (faster kernels)
         ("config5_gcn_int2", ["--model", "gcn", "--nodes", str(111_000_000 * world // 8), "--edges",
                               str(1_600_000_000 * world // 8), "--in-channels", "128", "--hidden", "256", "--out-channels",
                               "172", "--train-frac", "0.01", "--bits", "2", "--epochs", "4"]),
