@@ -259,7 +259,7 @@ def main():
     ap.add_argument("--pre", action="store_true", help="N > 1: pre/post-aggregation plan instead of the plain halo")
     ap.add_argument("--exchange", default="pipelined", choices=["pipelined", "all_to_all"],
                     help="N > 1: peer-by-peer exchange with each peer's rows aggregated on arrival, or one all-to-all")
-    ap.add_argument("--push-engine", default="kernel", choices=["kernel", "copy", "auto"],
+    ap.add_argument("--push-engine", default="auto", choices=["kernel", "copy", "auto"],
                     help="N > 1, pipelined exchange: rows moved by the store kernel, or by device-to-device copies")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer leg (profiler captures)")

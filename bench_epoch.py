@@ -70,7 +70,7 @@ def make_parser():
                          "device-time table to this file (a breakdown, never a timing)")
     ap.add_argument("--transport", default="all_to_all", choices=["all_to_all", "push"],
                     help="halo exchange: one NCCL collective per aggregation, or rows stored straight into the receivers' buffers")
-    ap.add_argument("--push-engine", default="kernel", choices=["kernel", "copy", "auto"],
+    ap.add_argument("--push-engine", default="auto", choices=["kernel", "copy", "auto"],
                     help="push transport: rows moved by the store kernel, or by device-to-device copies")
     return ap
 

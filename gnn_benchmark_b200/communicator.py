@@ -39,7 +39,7 @@ class Communicator(object):
     ctx = None
 
     def __init__(self, num_bits=32, is_async=True, use_barrier=False, pipeline_peers=False, transport="all_to_all",
-                 push_groups=3, push_engine="kernel") -> None:
+                 push_groups=3, push_engine="auto") -> None:
         """transport (an addition): "all_to_all" -- the reference's exchange, one collective per aggregation
         (NCCL here); "push" -- rows are stored straight into the receivers' buffers over NVLink by the
         kernel that gathers / produces them (peer.py, aggregator_push.py; one node, NCCL process group).
@@ -49,8 +49,10 @@ class Communicator(object):
         push_engine: "kernel" -- the store kernel moves the rows (gather fused in, a few SMs busy for the
         length of the exchange); "copy" -- rows are gathered into the send buffer when they are not already
         contiguous and every peer's block travels as one device-to-device copy on the copy engines (no SM);
-        "auto" -- copies for blocks that are contiguous as they are (backward, packed halo, pre/post), the store
-        kernel where the rows must be gathered (forward, plain plan, fp32)."""
+        "auto" (default) -- copies for blocks that are contiguous as they are (backward, packed halo, pre/post),
+        the store kernel where the rows must be gathered (forward, plain plan, fp32).  Measured per step of the
+        aggregation benchmark: kernel / copy / auto 53.4 / 54.5 / 54.0 ms on 2 GPUs, 63.4 / 64.8 / 63.6 on 4,
+        88.8 / 83.0 / 82.7 on 8."""
         if transport not in ("all_to_all", "push"):
             raise ValueError("transport must be 'all_to_all' or 'push'")
         if push_engine not in ("kernel", "copy", "auto"):

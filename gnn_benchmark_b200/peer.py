@@ -38,7 +38,7 @@ def _prefix_i32(counts, device) -> torch.Tensor:
 class NcclPeers(object):
     """One process per GPU on one node, NCCL process group initialised."""
 
-    def __init__(self, device, engine="kernel"):
+    def __init__(self, device, engine="auto"):
         self.device = torch.device(device)
         # "kernel": the store kernel moves everything (gather fused in); "copy": device-to-device copies per
         # peer, rows gathered into the send buffer first where needed; "auto": copies for blocks that are

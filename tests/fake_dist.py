@@ -33,7 +33,7 @@ class ThreadPeers:
 
     def __init__(self, world: "FakeWorld", rank: int):
         self.w, self.rank, self.world = world, rank, world.P
-        self.engine = getattr(world, "push_engine", "kernel")
+        self.engine = getattr(world, "push_engine", "auto")
         self._bufs = []
 
     def gather_objects(self, obj):
@@ -56,7 +56,7 @@ class ThreadPeers:
 
 
 class FakeWorld:
-    def __init__(self, world_size: int, push_engine: str = "kernel"):
+    def __init__(self, world_size: int, push_engine: str = "auto"):
         self._objs = [None] * world_size
         self.P = world_size
         self.push_engine = push_engine
