@@ -411,9 +411,12 @@ def run_multi_gpu(args):
         cfg = bench.workload_config(world, args.scale, widths)
         cfg.update({"rows_per_gpu": n, "nnz_total": int(nnz_total), "partitions": world,
                     "halo_rows_sent_total": halo_rows, "halo": f"{num_bits}-bit" + (" pre/post" if is_pre else ""),
-                    "exchange": (("rows stored straight into the receivers' buffers (gnnagg_push_rows)"
-                                  if comm.push_engine == "kernel" else
-                                  "rows copied straight into the receivers' buffers (gnnagg_push_block, copy engines)")
+                    "exchange": ({"kernel": "rows stored straight into the receivers' buffers (gnnagg_push_rows)",
+                                  "copy": "rows gathered, then copied straight into the receivers' buffers "
+                                          "(gnnagg_push_block, copy engines)",
+                                  "auto": "forward rows stored straight into the receivers' buffers by the kernel that "
+                                          "gathers them (gnnagg_push_rows), backward blocks copied there "
+                                          "(gnnagg_push_block, copy engines)"}[comm.push_engine]
                                  + f", peers served in {min(comm.push_groups, world - 1)} groups, each aggregated on arrival"
                                  if transport == "push" else "one NCCL all-to-all per aggregation"),
                     "setup_s": round(setup_s, 1), "parallelism": f"1-D vertex partition x{world}"})
