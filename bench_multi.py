@@ -396,6 +396,16 @@ def run_multi_gpu(args):
             variants["push_engine_" + other] = {"ms_per_step": ms_o, "value": edges_per_step / (ms_o / 1e3),
                                                 "unit": "edges/s", "int2_halo_ms_per_step": ms_o2, "note": notes[other]}
         plan.peers.engine = mine
+        if num_bits == 32 and not is_pre:  # how finely the peers are grouped (fp32 halo, plain plan only)
+            mine_g = comm.push_groups
+            for g in sorted({1, 2, 4, world - 1}):
+                if g == min(mine_g, world - 1) or g > world - 1:
+                    continue
+                comm.push_groups = g
+                ms_g = time_variant(num_bits)
+                variants[f"push_groups_{g}"] = {"ms_per_step": ms_g, "value": edges_per_step / (ms_g / 1e3), "unit": "edges/s",
+                                                "note": f"peers served in {g} group(s) instead of {min(mine_g, world - 1)}"}
+            comm.push_groups = mine_g
         ms_a2a = time_variant(num_bits, exchange="all_to_all")
         variants["nccl_all_to_all"] = {"ms_per_step": ms_a2a, "value": edges_per_step / (ms_a2a / 1e3), "unit": "edges/s",
                                        "note": "same graph and kernels, one NCCL all-to-all per aggregation instead of "
