@@ -267,7 +267,7 @@ def run_multi_gpu(args):
 
     num_bits, is_pre = args.bits, bool(args.pre)
     transport = "push" if args.exchange == "pipelined" else "all_to_all"
-    comm = Communicator(num_bits, is_async=True, transport=transport, push_groups=3, push_engine=args.push_engine)
+    comm = Communicator(num_bits, is_async=True, transport=transport, push_groups=7, push_engine=args.push_engine)
     rank, world = comm.init_dist_group("nccl")
     device = torch.device("cuda", torch.cuda.current_device())
     TimeRecorder(1, 1, enabled=False)
@@ -398,7 +398,7 @@ def run_multi_gpu(args):
         plan.peers.engine = mine
         if num_bits == 32 and not is_pre:  # how finely the peers are grouped (fp32 halo, plain plan only)
             mine_g = comm.push_groups
-            for g in sorted({1, 2, 4, world - 1}):
+            for g in sorted({1, 2, 3, 4, world - 1}):
                 if g == min(mine_g, world - 1) or g > world - 1:
                     continue
                 comm.push_groups = g
