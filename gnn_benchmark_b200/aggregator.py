@@ -387,22 +387,6 @@ def _send_idx(graph) -> torch.Tensor:
     return graph.idx_nodes_send_to_others_i32
 
 
-def _scatter_parts(graph, world_size):
-    """The scatter matrix cut into one matrix per peer (columns = the rows sent to that peer, renumbered from
-    0): the halo gradients a peer sends back can then be added as soon as that peer's block is in, while the
-    other peers' blocks are still on their way.  Built on first use and cached on the graph."""
-    parts = getattr(graph, "_scatter_parts", None)
-    if parts is None:
-        from .data_manager.DataLoader import _scatter_matrix
-        offs = _prefix(graph.comm_splits.send_splits)
-        n = graph.local_adj_t.sparse_size(0)
-        idx = graph.idx_nodes_send_to_others
-        parts = [None if offs[p + 1] == offs[p] else _scatter_matrix(idx[offs[p]:offs[p + 1]], n)
-                 for p in range(world_size)]
-        graph._scatter_parts = parts
-    return parts
-
-
 def _scatter_adj(graph):
     if getattr(graph, "scatter_adj_t", None) is None:
         from .data_manager.DataLoader import _scatter_matrix

@@ -11,7 +11,6 @@ side stream, and a 4-byte all-reduce queued behind the stores tells every rank t
             wait signal -> remote / post SpMM -> raise "free" for the next forward            (compute)
   backward  transposed receive-side SpMM (packs in its epilogue when the halo is packed) ->
             push -> signal; local transposed SpMM; wait -> scatter-add / transposed pre-aggregation
-            (group by group on per-peer slices of the scatter matrix when the peers are served in groups)
 
 With the fp32 halo on the plain path the peers are served in `Communicator.push_groups` groups
 (group g = the peers rank+1+g*k ... ), each with its own signal, and the receive-side SpMM runs
@@ -155,7 +154,7 @@ def forward(graph, x, feat_len, num_bits, is_pre_delay, packed, world_size, rec)
 
 def backward(graph, g, feat_len, num_bits, is_pre_delay, packed, world_size, rec):
     from .aggregator import (_fuse_pack as fuse_pack, _prefix as prefix, _remote_parts as remote_parts,
-                             _resize as resize, _scatter_adj as scatter_adj, _scatter_parts as scatter_parts)
+                             _resize as resize, _scatter_adj as scatter_adj)
 
     plan = graph.push_plan
     P, r = world_size, plan.rank
@@ -206,19 +205,6 @@ def backward(graph, g, feat_len, num_bits, is_pre_delay, packed, world_size, rec
         rec.record_local_aggregate_time(t)
 
     t = rec.start() if rec else None
-    if len(groups) > 1:
-        # each group's halo gradients are added as soon as that group's blocks are in
-        sparts = scatter_parts(graph, P)
-        soffs = prefix(graph.comm_splits.send_splits)
-        for (_, _, sources), sig in zip(groups, signals):
-            sig.wait()
-            for src in sources:
-                if sparts[src] is not None:
-                    SPMM_forward(sparts[src], graph.comm_buf.send_buf[soffs[src]:soffs[src + 1]], grad)
-        plan.free["backward"] = plan.peers.signal()
-        if rec:
-            rec.record_remote_aggregate_time(t)
-        return grad
     for sig in signals:
         sig.wait()
     if sum(graph.comm_splits.send_splits) != 0:
