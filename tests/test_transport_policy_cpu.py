@@ -54,3 +54,60 @@ def test_communicator_rejects_unknown_transport_and_engine():
         assert (c.transport, c.push_groups, c.push_engine) == ("push", 2, "auto")
     finally:
         Communicator.ctx = saved
+
+
+class _FakePeers(object):
+    """Peer service without any device: every rank's buffer 'lives' at a made-up base address."""
+    engine = "auto"
+
+    def __init__(self, rank, world, info):
+        self.rank, self.world, self._info = rank, world, info
+
+    def gather_objects(self, obj):
+        assert obj == self._info[self.rank]
+        return list(self._info)
+
+    def share(self, nbytes):
+        import torch
+        self.nbytes = nbytes
+        return torch.zeros(nbytes, dtype=torch.uint8), [(p + 1) << 40 for p in range(self.world)]
+
+
+@pytest.mark.parametrize("bits", [32, 2, 8])
+def test_push_plan_blocks_tile_every_receive_buffer(bits):
+    """The destination tables of the push transport: for every peer p, the blocks the other ranks store into
+    p's receive buffer must tile it in rank order without overlap -- forward rows into recv_buf (or the packed
+    pair), backward rows into send_buf -- and every rank must compute the same region layout."""
+    from gnn_benchmark_b200.peer import PushPlan
+
+    P, F = 4, 24
+    # rows[r][q]: rows r sends to q in forward (= rows q receives from r); some peers exchange nothing
+    rows = [[0, 5, 0, 9], [7, 0, 3, 1], [2, 2, 0, 0], [4, 0, 6, 0]]
+    info = [([rows[q][r] for q in range(P)], list(rows[r])) for r in range(P)]   # (recv_splits, send_splits) of rank r
+    epb = 8 // bits if bits in (2, 4, 8) else 1
+    pk = lambda n: (n + epb - 1) // epb
+    plans = []
+    for r in range(P):
+        splits = SimpleNamespace(recv_splits=info[r][0], send_splits=info[r][1])
+        plans.append(PushPlan(_FakePeers(r, P, info), splits, F, bits, lean=False))
+    assert len({tuple(sorted(pl.offset.items())) for pl in plans}) == 1 and len({pl.peers.nbytes for pl in plans}) == 1
+    cases = [("forward", "rows", "recv_buf", 4 * F, lambda src, dst: rows[src][dst], False),
+             ("backward", "rows", "send_buf", 4 * F, lambda src, dst: rows[dst][src], False)]
+    if bits != 32:
+        cases += [("forward", "codes", "q_recv_data", F, lambda src, dst: rows[src][dst], True),
+                  ("backward", "codes", "q_send_data", F, lambda src, dst: rows[dst][src], True),
+                  ("forward", "params", "q_recv_params", 4, lambda src, dst: rows[src][dst], False),
+                  ("backward", "params", "q_send_params", 4, lambda src, dst: rows[dst][src], False)]
+    for direction, payload, region, ld, count, packed_rows in cases:
+        for p in range(P):   # the receiver
+            base = ((p + 1) << 40) + plans[0].offset[region]
+            cursor = base
+            for r in range(P):   # senders in rank order
+                n = count(r, p)
+                n = pk(n) if packed_rows else n
+                assert int(plans[r].dst_table(direction, payload, ld)[p]) == cursor, (direction, payload, p, r)
+                assert plans[r].counts[direction, payload][p] == n
+                cursor += n * ld
+            # the region is large enough for what lands in it
+            nxt = min([o for o in plans[0].offset.values() if o > plans[0].offset[region]] + [plans[0].peers.nbytes])
+            assert cursor - base <= nxt - plans[0].offset[region]
